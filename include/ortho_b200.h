@@ -1,0 +1,139 @@
+/*
+ * ortho_b200 -- C ABI of the B200 (sm_100a) OrthoLinear forward
+ *
+ *     Y[M,N] = X[M,K] . dequant(W_base_int4[N,K])^T  +  alpha . X[M,K] . W_ortho[N,K]^T
+ *
+ * Plain pointers and sizes only; no C++ or torch types.  Every pointer is a DEVICE pointer
+ * unless a comment says "host".  `stream` is a cudaStream_t passed as void* (NULL = the legacy
+ * default stream).  All calls are asynchronous on `stream` and perform no host synchronisation
+ * except where stated.  Every function returns ORTHO_B200_OK (0) or a positive status code;
+ * nothing traps on the device.
+ *
+ * Weight layout (kept from the reference, include/ortho.h:22-28,41-53,63-71):
+ *   q_weight   u8  [N, K/2] row-major; element idx = n*K + k lives in byte idx/2, low nibble for
+ *              even idx, high nibble for odd; nibble = 4-bit two's complement in [-8, 7]
+ *              (src/ortho.c:315-325)
+ *   q_scales   f16 [N]   one scale per output row (module buffer, torch_bind/ortho_linear.py:60)
+ *   CSR ortho  row_ptr i32 [N+1], col_indices i32 [nnz] (row-major sorted, unique),
+ *              values f16 [nnz]            (torch_bind/ortho_linear.py:63-65, tools/sieve.py:119-152)
+ *   alpha      float kill switch; the ortho term contributes only when alpha > 0 and nnz > 0
+ *              (src/ortho.c:343)
+ *   X f16 [M,K] row-major contiguous, Y f16 [M,N] row-major contiguous (ortho_linear.py:130-168)
+ *
+ * Constraints (violations return a status, there is no slow path): K a multiple of 32,
+ * K <= 65536, q_weight / X / Y 16-byte aligned, M, N >= 1 (M == 0 is a no-op).
+ */
+#ifndef ORTHO_B200_H
+#define ORTHO_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ORTHO_B200_VERSION 100
+
+#if defined(__GNUC__)
+#define ORTHO_B200_API __attribute__((visibility("default")))
+#else
+#define ORTHO_B200_API
+#endif
+
+enum {
+    ORTHO_B200_OK = 0,
+    ORTHO_B200_ERR_NULL = 1,        /* a required pointer is NULL                                  */
+    ORTHO_B200_ERR_SHAPE = 2,       /* M/K/N/nnz outside the supported range (K%32, K<=65536, ...) */
+    ORTHO_B200_ERR_ALIGN = 3,       /* a base pointer is not 16-byte aligned                       */
+    ORTHO_B200_ERR_PLAN = 4,        /* plan does not belong to this layer (shape or nnz mismatch)  */
+    ORTHO_B200_ERR_WORKSPACE = 5,   /* workspace missing or smaller than ortho_b200_workspace_bytes */
+    ORTHO_B200_ERR_CUDA = 6,        /* a CUDA call failed; see ortho_b200_last_cuda_error()        */
+    ORTHO_B200_ERR_DEVICE = 7,      /* the current device is not compute capability 10.x           */
+    ORTHO_B200_ERR_KERNEL = 8,      /* a kernel reported a bounded wait that ran out               */
+    ORTHO_B200_ERR_ALLOC = 9        /* host or device allocation failed                            */
+};
+
+/* Replaces: the 0 / -1 convention of the reference C API (include/ortho.h:76-79,132-135). */
+ORTHO_B200_API const char *ortho_b200_strerror(int status);
+ORTHO_B200_API int ortho_b200_version(void);
+/* cudaError_t value recorded by the last call on this host thread that returned ERR_CUDA. */
+ORTHO_B200_API int ortho_b200_last_cuda_error(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * Plan: the GPU-side re-layout of one layer's sparse ortho component, built once per layer.
+ * Has no counterpart in the reference (its kernels read CSR directly,
+ * src/dual_gemm.cu:106-130); it takes the place of the per-call orth_layer_t the binding builds
+ * on its stack (torch_bind/bindings.cpp:19-36).  The plan owns only its own device copies
+ * (packed {col16|f16 value} entries in row order, per-entry row ids, per-128-row-tile ranges);
+ * it never retains the caller's pointers.  Creation allocates device memory, launches the
+ * re-layout kernels on `stream` and synchronises that stream once.  A plan is immutable after
+ * creation and may be shared by concurrent forwards.  nnz == 0 yields a valid empty plan.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct ortho_b200_plan ortho_b200_plan;
+
+ORTHO_B200_API int ortho_b200_plan_create(ortho_b200_plan **plan_out,
+                           const int32_t *row_ptr, const int32_t *col_indices,
+                           const void *values_f16, int64_t nnz,
+                           int64_t in_features, int64_t out_features, void *stream);
+ORTHO_B200_API int ortho_b200_plan_destroy(ortho_b200_plan *plan);
+ORTHO_B200_API int64_t ortho_b200_plan_nnz(const ortho_b200_plan *plan);
+/* largest number of stored entries in one output row (host value cached at creation) */
+ORTHO_B200_API int64_t ortho_b200_plan_max_row_nnz(const ortho_b200_plan *plan);
+
+/* Decodes the re-laid-out entries back to (row, col, f16 value) triplets, entry i of the plan
+ * to slot i of the outputs (each sized nnz).  Exists so that a test can prove the sparse index
+ * decode bit-exact against the CSR arrays (row-major order, tools/sieve.py:131-136). */
+ORTHO_B200_API int ortho_b200_plan_decode_dump(const ortho_b200_plan *plan, int32_t *rows_out, int32_t *cols_out,
+                                void *values_f16_out, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Bit-exactness probe for the base: writes, for every element, the raw integer produced by the
+ * same in-register INT4 unpack the forward kernels use, and (float)w_int * (float)scale[n].
+ * Follows src/ortho.c:315-325 (unpack) and :363 (scale application).  Either output may be NULL.
+ * ------------------------------------------------------------------------------------------- */
+ORTHO_B200_API int ortho_b200_dequant_dump(const void *q_weight, const void *q_scales_f16,
+                            int64_t out_features, int64_t in_features,
+                            int8_t *w_int_out, float *w_deq_out, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Forward.  Replaces orth_layer_forward_cuda (include/ortho.h:141-144, src/dual_gemm.cu:295-372)
+ * as reached from the binding's forward(q_weight, q_scales, ortho_values, ortho_col_indices,
+ * ortho_row_ptr, input, output, alpha) (torch_bind/bindings.cpp:9-18, call site
+ * torch_bind/ortho_linear.py:142-151); same argument order and meaning, plus explicit sizes,
+ * the optional plan, a caller-owned workspace and the stream.
+ *
+ *   M <= ORTHO_B200_DECODE_MAX_M : memory-bound streaming kernel (no workspace needed).
+ *   larger M                     : tcgen05 / TMEM tensor-core kernel; needs
+ *                                  ortho_b200_workspace_bytes(M, K, N) bytes of workspace when
+ *                                  the ortho term is active, none otherwise.
+ * plan may be NULL: the kernels then read the CSR arrays directly.  With a plan the CSR
+ * pointers may be NULL.  alpha <= 0 or nnz == 0 skips the sparse stream entirely, so the output
+ * is bit-identical to the base-only result (src/ortho.c:343 and the reference null test,
+ * tests/benchmark_null_test.c:127-131).  Borrowed pointers are only used until the launched
+ * kernels finish.
+ * ------------------------------------------------------------------------------------------- */
+#define ORTHO_B200_DECODE_MAX_M 64
+
+ORTHO_B200_API int64_t ortho_b200_workspace_bytes(int64_t M, int64_t K, int64_t N);
+
+ORTHO_B200_API int ortho_b200_forward(const void *q_weight, const void *q_scales_f16,
+                       const void *ortho_values_f16, const int32_t *ortho_col_indices,
+                       const int32_t *ortho_row_ptr, int64_t nnz,
+                       const void *x_f16, void *y_f16,
+                       int64_t M, int64_t K, int64_t N, float alpha,
+                       const ortho_b200_plan *plan,
+                       void *workspace, int64_t workspace_bytes, void *stream);
+
+/* Benchmark/tuning hook: overrides the decode kernel's tile choice for later forwards from this
+ * process.  Arguments are (row groups per CTA, k groups per CTA, loads in flight, k split);
+ * any value <= 0 restores the built-in choice.  Returns ERR_SHAPE for an unsupported tuple. */
+ORTHO_B200_API int ortho_b200_set_decode_config(int row_groups, int k_groups, int unroll, int k_split);
+
+/* Number of kernel launches issued by this library from this process (all threads). */
+ORTHO_B200_API int64_t ortho_b200_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ORTHO_B200_H */

@@ -1,0 +1,139 @@
+"""Function-level operator with the signature of the reference binding.
+
+``forward(q_weight, q_scales, ortho_values, ortho_col_indices, ortho_row_ptr, input, output,
+alpha) -> None`` writes ``output`` in place, like ``libortho._C_ops.forward`` declared in
+``torch_bind/bindings.cpp:9-18,46-49`` and called from ``torch_bind/ortho_linear.py:142-151``.
+Differences, all deliberate: the buffers really are FP16 (the reference binding asks for
+``float*`` from FP16 tensors and cannot run), the call is asynchronous on the current CUDA
+stream, and any failure raises instead of being dropped.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+
+class Plan:
+    """Owns one ``ortho_b200_plan`` (GPU-side re-layout of a layer's CSR ortho component)."""
+
+    def __init__(self, row_ptr: torch.Tensor, col_indices: torch.Tensor, values: torch.Tensor,
+                 in_features: int, out_features: int):
+        import ctypes
+        self._h = ctypes.c_void_p()
+        nnz = int(values.numel())
+        if nnz:
+            assert row_ptr.is_cuda and col_indices.is_cuda and values.is_cuda
+            assert row_ptr.dtype == torch.int32 and col_indices.dtype == torch.int32
+            assert values.dtype == torch.float16
+            assert row_ptr.numel() == out_features + 1 and col_indices.numel() == nnz
+            row_ptr, col_indices, values = row_ptr.contiguous(), col_indices.contiguous(), values.contiguous()
+        dev = values.device if nnz else torch.device("cuda", torch.cuda.current_device())
+        with torch.cuda.device(dev):
+            st = _lib.lib().ortho_b200_plan_create(
+                ctypes.byref(self._h),
+                row_ptr.data_ptr() if nnz else None, col_indices.data_ptr() if nnz else None,
+                values.data_ptr() if nnz else None, nnz, in_features, out_features,
+                torch.cuda.current_stream(dev).cuda_stream)
+        _lib.check(st, "ortho_b200_plan_create")
+        self.nnz = nnz
+        self.device = dev
+        self.in_features, self.out_features = in_features, out_features
+
+    @property
+    def handle(self):
+        return self._h
+
+    @property
+    def max_row_nnz(self) -> int:
+        return int(_lib.lib().ortho_b200_plan_max_row_nnz(self._h))
+
+    def decode_dump(self):
+        """(rows, cols, values) of every stored entry, decoded on the GPU from the plan."""
+        rows = torch.empty(self.nnz, dtype=torch.int32, device=self.device)
+        cols = torch.empty(self.nnz, dtype=torch.int32, device=self.device)
+        vals = torch.empty(self.nnz, dtype=torch.float16, device=self.device)
+        with torch.cuda.device(self.device):
+            st = _lib.lib().ortho_b200_plan_decode_dump(
+                self._h, rows.data_ptr(), cols.data_ptr(), vals.data_ptr(),
+                torch.cuda.current_stream(self.device).cuda_stream)
+        _lib.check(st, "ortho_b200_plan_decode_dump")
+        return rows, cols, vals
+
+    def close(self):
+        if self._h is not None and self._h.value:
+            _lib.lib().ortho_b200_plan_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def workspace_bytes(M: int, K: int, N: int) -> int:
+    return int(_lib.lib().ortho_b200_workspace_bytes(M, K, N))
+
+
+def dequant_dump(q_weight: torch.Tensor, q_scales: torch.Tensor):
+    """(w_int int8 [N,K], w_deq float32 [N,K]) produced by the kernels' own INT4 unpack."""
+    assert q_weight.is_cuda and q_weight.dtype == torch.uint8 and q_scales.dtype == torch.float16
+    q_weight, q_scales = q_weight.contiguous(), q_scales.contiguous()
+    N, kh = q_weight.shape
+    wi = torch.empty(N, kh * 2, dtype=torch.int8, device=q_weight.device)
+    wd = torch.empty(N, kh * 2, dtype=torch.float32, device=q_weight.device)
+    with torch.cuda.device(q_weight.device):
+        st = _lib.lib().ortho_b200_dequant_dump(
+            q_weight.data_ptr(), q_scales.data_ptr(), N, kh * 2, wi.data_ptr(), wd.data_ptr(),
+            torch.cuda.current_stream(q_weight.device).cuda_stream)
+    _lib.check(st, "ortho_b200_dequant_dump")
+    return wi, wd
+
+
+def forward(q_weight: torch.Tensor, q_scales: torch.Tensor, ortho_values: torch.Tensor,
+            ortho_col_indices: torch.Tensor, ortho_row_ptr: torch.Tensor,
+            input: torch.Tensor, output: torch.Tensor, alpha: float,
+            plan: Optional[Plan] = None, workspace: Optional[torch.Tensor] = None) -> None:
+    """In-place ``output[M,N] = input[M,K] @ dequant(q_weight)^T + alpha * input @ W_ortho^T``."""
+    if not input.is_cuda:
+        raise RuntimeError("libortho_b200 has no CPU path: `input` must be a CUDA tensor")
+    if input.dtype != torch.float16 or output.dtype != torch.float16:
+        raise TypeError("input and output must be float16")
+    if q_weight.dtype != torch.uint8 or q_scales.dtype != torch.float16:
+        raise TypeError("q_weight must be uint8 (packed INT4) and q_scales float16")
+    if input.dim() != 2 or output.dim() != 2 or not input.is_contiguous() or not output.is_contiguous():
+        raise ValueError("input [M,K] and output [M,N] must be contiguous 2-D tensors")
+    M, K = input.shape
+    N = output.shape[1]
+    if output.shape[0] != M or tuple(q_weight.shape) != (N, K // 2) or q_scales.numel() != N:
+        raise ValueError("shape mismatch between q_weight/q_scales/input/output")
+    dev = input.device
+    for t in (q_weight, q_scales, output):
+        if t.device != dev:
+            raise RuntimeError("all tensors must live on the input's device")
+    nnz = int(ortho_values.numel()) if ortho_values is not None else 0
+    if nnz and plan is None:
+        if (ortho_values.dtype != torch.float16 or ortho_col_indices.dtype != torch.int32
+                or ortho_row_ptr.dtype != torch.int32):
+            raise TypeError("ortho buffers must be float16 / int32 / int32")
+        if ortho_row_ptr.numel() != N + 1 or ortho_col_indices.numel() != nnz:
+            raise ValueError("CSR arrays have inconsistent sizes")
+    need = workspace_bytes(M, K, N) if (nnz and alpha > 0) else 0
+    ws_ptr, ws_bytes = None, 0
+    if need:
+        if workspace is None or workspace.numel() * workspace.element_size() < need:
+            workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+        ws_ptr, ws_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
+    with torch.cuda.device(dev):
+        st = _lib.lib().ortho_b200_forward(
+            q_weight.data_ptr(), q_scales.data_ptr(),
+            ortho_values.data_ptr() if nnz else None,
+            ortho_col_indices.data_ptr() if nnz else None,
+            ortho_row_ptr.data_ptr() if nnz else None, nnz,
+            input.data_ptr(), output.data_ptr(), M, K, N, float(alpha),
+            plan.handle if plan is not None else None, ws_ptr, ws_bytes,
+            torch.cuda.current_stream(dev).cuda_stream)
+    _lib.check(st, "ortho_b200_forward")

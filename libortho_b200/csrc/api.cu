@@ -1,0 +1,120 @@
+// extern "C" surface: argument validation, status plumbing and the decode / prefill regime split.
+//
+// Takes the place of forward_cuda_wrapper (torch_bind/bindings.cpp:9-44) and of the host
+// dispatcher orth_layer_forward_cuda (src/dual_gemm.cu:295-372) of the reference.  Unlike the
+// reference dispatcher it never synchronises the device and it reports failures as status
+// codes instead of dropping them.
+#include <atomic>
+
+#include "common.cuh"
+
+namespace ob {
+
+static thread_local int tl_last_cuda_error = 0;
+static std::atomic<long long> g_launches{0};
+
+void note_cuda_error(cudaError_t e) { tl_last_cuda_error = (int)e; (void)cudaGetLastError(); }
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+static int check_device()
+{
+    static thread_local int checked_device = -1;
+    int dev = 0;
+    OB_CUDA(cudaGetDevice(&dev));
+    if (dev == checked_device) return ORTHO_B200_OK;
+    int major = 0;
+    OB_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+    if (major != 10) return ORTHO_B200_ERR_DEVICE;
+    checked_device = dev;
+    return ORTHO_B200_OK;
+}
+
+}  // namespace ob
+
+using namespace ob;
+
+extern "C" const char *ortho_b200_strerror(int status)
+{
+    switch (status) {
+        case ORTHO_B200_OK: return "ok";
+        case ORTHO_B200_ERR_NULL: return "a required pointer is NULL";
+        case ORTHO_B200_ERR_SHAPE: return "unsupported shape (need M,N >= 1, K a multiple of 32 and <= 65536)";
+        case ORTHO_B200_ERR_ALIGN: return "q_weight, x and y must be 16-byte aligned";
+        case ORTHO_B200_ERR_PLAN: return "plan is invalid or was built for another layer";
+        case ORTHO_B200_ERR_WORKSPACE: return "workspace missing or smaller than ortho_b200_workspace_bytes()";
+        case ORTHO_B200_ERR_CUDA: return "a CUDA call failed (see ortho_b200_last_cuda_error)";
+        case ORTHO_B200_ERR_DEVICE: return "current device is not a compute capability 10.x GPU";
+        case ORTHO_B200_ERR_KERNEL: return "a kernel gave up on a bounded wait";
+        case ORTHO_B200_ERR_ALLOC: return "allocation failed";
+        default: return "unknown status";
+    }
+}
+
+extern "C" int ortho_b200_version(void) { return ORTHO_B200_VERSION; }
+extern "C" int ortho_b200_last_cuda_error(void) { return tl_last_cuda_error; }
+extern "C" int64_t ortho_b200_launch_count(void) { return (int64_t)g_launches.load(); }
+
+extern "C" int ortho_b200_set_decode_config(int row_groups, int k_groups, int unroll, int k_split)
+{
+    return set_decode_config(row_groups, k_groups, unroll, k_split);
+}
+
+extern "C" int64_t ortho_b200_workspace_bytes(int64_t M, int64_t K, int64_t N)
+{
+    if (M <= ORTHO_B200_DECODE_MAX_M) return 0;
+    return prefill_workspace_bytes(M, K, N);
+}
+
+extern "C" int ortho_b200_forward(const void *q_weight, const void *q_scales_f16,
+                                  const void *ortho_values_f16, const int32_t *ortho_col_indices,
+                                  const int32_t *ortho_row_ptr, int64_t nnz,
+                                  const void *x_f16, void *y_f16,
+                                  int64_t M, int64_t K, int64_t N, float alpha,
+                                  const ortho_b200_plan *plan,
+                                  void *workspace, int64_t workspace_bytes, void *stream)
+{
+    if (M == 0) return ORTHO_B200_OK;
+    if (!q_weight || !q_scales_f16 || !x_f16 || !y_f16) return ORTHO_B200_ERR_NULL;
+    if (M < 0 || N <= 0 || K <= 0 || (K % 32) != 0 || K > 65536 || nnz < 0 ||
+        M > 0x7fffffffLL || N > 0x7fffff00LL || nnz > 0x7fffffffLL)
+        return ORTHO_B200_ERR_SHAPE;
+    if ((((uintptr_t)q_weight | (uintptr_t)x_f16 | (uintptr_t)y_f16) & 15u) != 0) return ORTHO_B200_ERR_ALIGN;
+    if (((uintptr_t)q_scales_f16 & 1u) != 0) return ORTHO_B200_ERR_ALIGN;
+
+    const Plan *pl = reinterpret_cast<const Plan *>(plan);
+    if (pl) {
+        if (pl->magic != kPlanMagic || pl->K != K || pl->N != N) return ORTHO_B200_ERR_PLAN;
+        if (ortho_values_f16 && pl->nnz != nnz) return ORTHO_B200_ERR_PLAN;
+        nnz = pl->nnz;
+    }
+    // the ortho stream is gated exactly like the reference: alpha > 0 and a non-empty list
+    // (src/ortho.c:343, src/dual_gemm.cu:212)
+    const bool has_ortho = (alpha > 0.0f) && (nnz > 0);
+    if (has_ortho && !pl && (!ortho_values_f16 || !ortho_col_indices || !ortho_row_ptr)) return ORTHO_B200_ERR_NULL;
+
+    int st = check_device();
+    if (st != ORTHO_B200_OK) return st;
+
+    FwdArgs a;
+    a.w = (const uint8_t *)q_weight;
+    a.scales = (const __half *)q_scales_f16;
+    a.x = (const __half *)x_f16;
+    a.y = (__half *)y_f16;
+    a.has_ortho = has_ortho ? 1 : 0;
+    a.alpha = alpha;
+    a.M = M; a.K = K; a.N = N; a.nnz = nnz;
+    a.plan = pl;
+    if (has_ortho && pl) {
+        a.ortho.row_ptr = pl->row_ptr; a.ortho.entries = pl->entries; a.ortho.col = nullptr; a.ortho.val = nullptr;
+    } else if (has_ortho) {
+        a.ortho.row_ptr = ortho_row_ptr; a.ortho.entries = nullptr;
+        a.ortho.col = ortho_col_indices; a.ortho.val = (const __half *)ortho_values_f16;
+    } else {
+        a.ortho.row_ptr = nullptr; a.ortho.entries = nullptr; a.ortho.col = nullptr; a.ortho.val = nullptr;
+    }
+    a.workspace = workspace; a.workspace_bytes = workspace_bytes;
+    a.stream = (cudaStream_t)stream;
+
+    if (M <= ORTHO_B200_DECODE_MAX_M) return launch_decode(a);
+    return launch_prefill(a);
+}

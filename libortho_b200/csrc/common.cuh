@@ -1,0 +1,145 @@
+// Shared device/host helpers of the sm_100a OrthoLinear forward.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/ortho_b200.h"
+
+namespace ob {
+
+// ---- host-side status plumbing -----------------------------------------------------------------
+void note_cuda_error(cudaError_t e);   // remembers e for ortho_b200_last_cuda_error()
+void count_launch(int n = 1);          // feeds ortho_b200_launch_count()
+
+#define OB_CUDA(call)                                                     \
+    do {                                                                  \
+        cudaError_t e__ = (call);                                         \
+        if (e__ != cudaSuccess) { ::ob::note_cuda_error(e__); return ORTHO_B200_ERR_CUDA; } \
+    } while (0)
+
+static inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// ---- the plan (definition shared by plan.cu / decode.cu / prefill.cu) -------------------------
+// entries[i] = (f16 bits of value << 16) | column   for CSR entry i (row-major order kept)
+// erow[i]    = output row of entry i
+// tile_ptr[t]= first entry of 128-row tile t (== row_ptr[min(128 t, N)]), t in [0, ceil(N/128)]
+struct Plan {
+    uint32_t magic;
+    int device;
+    int64_t K, N, nnz;
+    int64_t max_row_nnz;
+    int32_t *row_ptr;     // [N+1] device copy
+    uint32_t *entries;    // [nnz]
+    int32_t *erow;        // [nnz]
+    int32_t *tile_ptr;    // [ceil(N/128)+1]
+};
+constexpr uint32_t kPlanMagic = 0x0B200A17u;
+
+// view of the ortho component handed to kernels: either packed plan entries or raw CSR
+struct OrthoView {
+    const int32_t *row_ptr;
+    const uint32_t *entries;   // non-null -> packed path
+    const int32_t *col;        // raw CSR path
+    const __half *val;
+};
+
+// ---- INT4 -> FP16 in registers ------------------------------------------------------------------
+// One 32-bit word holds 8 consecutive elements e0..e7 (e_i in bits [4i, 4i+4), low nibble = even
+// element; src/ortho.c:315-320).  A nibble r is a 4-bit two's complement integer s (:321-323);
+// r ^ 8 == s + 8.  OR-ing the exponent pattern 0x6400 (=1024.0) under the nibble yields the half
+// 1024 + s + 8 for a nibble in bits 0-3, or 1024 + 16 (s + 8) for a nibble in bits 4-7.  Both are
+// exact, so one subtract (or one fma by 1/16) gives s exactly.  Output pairs are
+// (e0,e4) (e1,e5) (e2,e6) (e3,e7): the caller contracts them against activations stored in the
+// same pair order, so no element ever has to be moved across a 16-bit boundary.
+__device__ __forceinline__ uint32_t lop3_and_xor(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0x6a;" : "=r"(d) : "r"(a), "r"(b), "r"(c));  // (a & b) ^ c
+    return d;
+}
+
+__device__ __forceinline__ void int4x8_to_half2x4(uint32_t w, uint32_t (&h)[4]) {
+    const uint32_t kLoMask = 0x000F000Fu, kHiMask = 0x00F000F0u;
+    const uint32_t kLoMagic = 0x64086408u;   // 1024 | sign flip of a low nibble
+    const uint32_t kHiMagic = 0x64806480u;   // 1024 | sign flip of a high nibble
+    const __half2 kSubLo = __half2half2(__ushort_as_half((unsigned short)0x6408));   // 1032
+    const __half2 kMulHi = __half2half2(__ushort_as_half((unsigned short)0x2C00));   // 1/16
+    const __half2 kAddHi = __half2half2(__ushort_as_half((unsigned short)0xD480));   // -72
+    uint32_t w8 = w >> 8;
+    uint32_t a0 = lop3_and_xor(w, kLoMask, kLoMagic);
+    uint32_t a1 = lop3_and_xor(w, kHiMask, kHiMagic);
+    uint32_t a2 = lop3_and_xor(w8, kLoMask, kLoMagic);
+    uint32_t a3 = lop3_and_xor(w8, kHiMask, kHiMagic);
+    __half2 r0 = __hsub2(*reinterpret_cast<__half2 *>(&a0), kSubLo);
+    __half2 r1 = __hfma2(*reinterpret_cast<__half2 *>(&a1), kMulHi, kAddHi);
+    __half2 r2 = __hsub2(*reinterpret_cast<__half2 *>(&a2), kSubLo);
+    __half2 r3 = __hfma2(*reinterpret_cast<__half2 *>(&a3), kMulHi, kAddHi);
+    h[0] = *reinterpret_cast<uint32_t *>(&r0);
+    h[1] = *reinterpret_cast<uint32_t *>(&r1);
+    h[2] = *reinterpret_cast<uint32_t *>(&r2);
+    h[3] = *reinterpret_cast<uint32_t *>(&r3);
+}
+
+// natural element order variant: pairs (e0,e1) (e2,e3) (e4,e5) (e6,e7).  A byte holds the pair
+// (low nibble = even element).  prmt replicates byte i into both 16-bit halves under the 0x64
+// exponent byte, the mask keeps bits 0-3 in the low half and bits 4-7 (now bits 20-23) in the high
+// half, and one fma per pair applies {x - 1032, x/16 - 72} to the two halves.
+__device__ __forceinline__ void int4x8_to_half2x4_natural(uint32_t w, uint32_t (&h)[4]) {
+    const uint32_t kExp = 0x64646464u;
+    const uint32_t kMask = 0xFFF0FF0Fu;      // keep exponent bytes, low nibble (lo half), high nibble (hi half)
+    const uint32_t kFlip = 0x00800008u;
+    __half2 mul, add;
+    {
+        uint32_t m = 0x2C003C00u;            // hi = 1/16, lo = 1
+        uint32_t a = 0xD480E408u;            // hi = -72,  lo = -1032
+        mul = *reinterpret_cast<__half2 *>(&m);
+        add = *reinterpret_cast<__half2 *>(&a);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        uint32_t v;
+        // bytes of result (high..low): 0x64, byte i of w, 0x64, byte i of w
+        uint32_t sel = 0x4040u | (uint32_t)i | ((uint32_t)i << 8);
+        asm("prmt.b32 %0, %1, %2, %3;" : "=r"(v) : "r"(w), "r"(kExp), "r"(sel));
+        v = lop3_and_xor(v, kMask, kFlip);
+        __half2 r = __hfma2(*reinterpret_cast<__half2 *>(&v), mul, add);
+        h[i] = *reinterpret_cast<uint32_t *>(&r);
+    }
+}
+
+// mma.sync m16n8k16, f16 x f16 -> f32 (legacy tensor path; used by the memory-bound decode kernel
+// where the 16-row operand is the weight tile and the 8-column operand is the token block)
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// streaming 128-bit load of read-once weight bytes: bypass L1 allocation
+__device__ __forceinline__ uint4 ldg_stream(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::128B.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+}  // namespace ob
+
+// launchers implemented in the kernel translation units
+namespace ob {
+struct FwdArgs {
+    const uint8_t *w; const __half *scales; const __half *x; __half *y;
+    OrthoView ortho; int has_ortho; float alpha;
+    int64_t M, K, N, nnz;
+    const Plan *plan;
+    void *workspace; int64_t workspace_bytes;
+    cudaStream_t stream;
+};
+int launch_decode(const FwdArgs &a);
+int launch_prefill(const FwdArgs &a);
+int64_t prefill_workspace_bytes(int64_t M, int64_t K, int64_t N);
+int set_decode_config(int wr, int wk, int u, int s);
+}  // namespace ob

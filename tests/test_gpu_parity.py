@@ -1,0 +1,219 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle.  All tests need a B200."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import assert_close, errors, golden, layer_oracle
+from cases import SMALL_CASES
+from libortho_b200 import OrthoLinear, _C_ops, _lib, workloads as wl
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def run_layer(layer, x, alpha, plan=True, ws=None):
+    """Forward through the C ABI for a workloads.Layer living on the GPU."""
+    y = torch.empty(x.shape[0], layer.N, dtype=torch.float16, device=x.device)
+    p = _C_ops.Plan(layer.row_ptr, layer.col, layer.vals, layer.K, layer.N) if (plan and layer.nnz) else None
+    _C_ops.forward(layer.base_weight, layer.base_scales, layer.vals, layer.col, layer.row_ptr, x, y, alpha,
+                   plan=p, workspace=ws)
+    torch.cuda.synchronize()
+    return y
+
+
+def test_native_library_is_loaded_and_counts_launches():
+    assert _lib.lib().ortho_b200_version() == 100
+    n0 = _lib.lib().ortho_b200_launch_count()
+    layer = wl.make_layer(64, 64, 0.05, seed=1).to(DEV)
+    run_layer(layer, wl.make_input(2, 64, seed=1).to(DEV), 1.0)
+    assert _lib.lib().ortho_b200_launch_count() > n0
+
+
+def test_int4_unpack_and_scale_bit_exact(oracle_mod):
+    """Every byte value in every position, and a seeded layer: the kernels' in-register unpack and
+    (float)w_int*scale must equal the oracle's integers and FP32 products bit for bit."""
+    packed = torch.arange(256, dtype=torch.uint8).repeat(8, 2).reshape(8, 512).contiguous()
+    scales = torch.tensor([0.5, 0.013, 1.0, 3e-4, 0.25, 7.1, 0.099, 1e-6], dtype=torch.float16)
+    wi, wd = _C_ops.dequant_dump(packed.to(DEV), scales.to(DEV))
+    oi, od = oracle_mod.dequant(packed.numpy(), scales.float().numpy())
+    assert np.array_equal(wi.cpu().numpy(), oi)
+    assert np.array_equal(wd.cpu().numpy().view(np.uint32), od.view(np.uint32))
+    layer = wl.make_layer(512, 96, 0.0, seed=21)
+    wi, wd = _C_ops.dequant_dump(layer.base_weight.to(DEV), layer.base_scales.to(DEV))
+    oi, od = oracle_mod.dequant(layer.base_weight.numpy(), layer.base_scales.float().numpy())
+    assert np.array_equal(wi.cpu().numpy(), oi)
+    assert np.array_equal(wd.cpu().numpy().view(np.uint32), od.view(np.uint32))
+
+
+@pytest.mark.parametrize("kind,K,N,d", [("gauss", 256, 300, 0.03), ("zipf", 512, 257, 0.01), ("gauss", 4096, 128, 0.005)])
+def test_sparse_index_decode_bit_exact(kind, K, N, d):
+    layer = wl.make_layer(K, N, d, seed=31, ortho=kind).to(DEV)
+    plan = _C_ops.Plan(layer.row_ptr, layer.col, layer.vals, K, N)
+    rows, cols, vals = plan.decode_dump()
+    torch.cuda.synchronize()
+    counts = (layer.row_ptr[1:] - layer.row_ptr[:-1]).long()
+    exp_rows = torch.repeat_interleave(torch.arange(N, device=DEV), counts).to(torch.int32)
+    assert torch.equal(rows, exp_rows) and torch.equal(cols, layer.col)
+    assert torch.equal(vals.view(torch.int16), layer.vals.view(torch.int16))
+    assert plan.max_row_nnz == int(counts.max())
+
+
+def _kat_csr(g):
+    """The reference test's coordinate draw as CSR: duplicates merged by summation (what the
+    oracle's one-entry-at-a-time accumulation amounts to)."""
+    dense = np.zeros(64 * 64, dtype=np.float32)
+    np.add.at(dense, g["idx16"].astype(np.int64), g["vals"])
+    w = torch.from_numpy(dense.reshape(64, 64))
+    from libortho_b200.sieve import pack_ortho_sparse
+    rp, col, val = pack_ortho_sparse(w, "csr")
+    return rp, col, val.to(torch.float16)
+
+
+def test_known_answer_cases_of_the_reference_test(oracle_mod):
+    """tests/test_cpu_forward.c replayed through the CUDA path: alpha=1, alpha=0, empty ortho."""
+    g = golden("kat_cpu_forward.npz")
+    rp, col, val = _kat_csr(g)
+    layer = wl.Layer(64, 64, torch.from_numpy(g["packed"]), torch.from_numpy(g["scales"]).to(torch.float16),
+                     rp, col, val, 1.0)
+    x = torch.from_numpy(g["x"]).to(torch.float16)
+    ld = layer.to(DEV)
+    for alpha, key in ((1.0, "y_alpha1"), (0.0, "y_alpha0")):
+        y = run_layer(ld, x.to(DEV), alpha).float().cpu().numpy()
+        # against the oracle fed the same FP16-rounded operands
+        assert_close(y, layer_oracle(oracle_mod, layer, x, alpha), key)
+        # and against the reference's recorded FP32 outputs (inputs differ by FP16 rounding only)
+        rel, mx = errors(y, g[key])
+        assert rel <= 2e-3 and mx <= 5e-2, (key, rel, mx)
+    empty = wl.Layer(64, 64, ld.base_weight, ld.base_scales, torch.zeros(65, dtype=torch.int32, device=DEV),
+                     ld.col[:0], ld.vals[:0], 1.0)
+    y_e = run_layer(empty, x.to(DEV), 1.0)
+    y_0 = run_layer(ld, x.to(DEV), 0.0)
+    assert torch.equal(y_e, y_0)
+
+
+def test_null_test_base_only(oracle_mod):
+    g = golden("null_test_small.npz")
+    m = OrthoLinear(128, 128).to(DEV)
+    m.base_weight = torch.from_numpy(g["packed"]).to(DEV)
+    m.base_scales = torch.from_numpy(g["scales"]).to(torch.float16).to(DEV)
+    x = torch.from_numpy(g["x"]).to(torch.float16)
+    y = m(x.to(DEV)).float().cpu().numpy()
+    ref = oracle_mod.forward_csr(g["packed"], m.base_scales.float().cpu().numpy(), None, None, None,
+                                 x.float().numpy(), 0.0)
+    assert_close(y, ref, "null test")
+
+
+@pytest.mark.parametrize("name", list(SMALL_CASES))
+@pytest.mark.parametrize("plan", [True, False])
+def test_seeded_small_layers_against_golden(name, plan):
+    K, N, M, d, kind, seed, alphas = SMALL_CASES[name]
+    g = golden("cfg_small.npz")
+    layer = wl.make_layer(K, N, d, seed=seed, ortho=kind).to(DEV)
+    x = wl.make_input(M, K, seed=seed).to(DEV)
+    for a in alphas:
+        y = run_layer(layer, x, a, plan=plan)
+        assert_close(y.float().cpu().numpy(), g[f"{name}_a{a}"], f"{name} alpha={a} plan={plan}")
+
+
+def test_single_layer_config_against_golden():
+    """4096x4096, M=8, 1 % residual ortho, alpha in {0, 1}: the reference's CPU-runnable case."""
+    g = golden("cfg0_y.npz")
+    layer = wl.make_layer(4096, 4096, 0.01, seed=0, ortho="residual10").to(DEV)
+    x = wl.make_input(8, 4096, seed=0).to(DEV)
+    m = layer.to_module()
+    for a, key in ((1.0, "y_alpha1"), (0.0, "y_alpha0")):
+        m.set_alpha(a)
+        assert_close(m(x).float().cpu().numpy(), g[key], key)
+    # alpha = 0 must equal the base-only output exactly (bitwise), with or without stored entries
+    m.set_alpha(0.0)
+    y0 = m(x)
+    base_only = wl.Layer(4096, 4096, layer.base_weight, layer.base_scales,
+                         torch.zeros(4097, dtype=torch.int32, device=DEV), layer.col[:0], layer.vals[:0], 1.0)
+    assert torch.equal(y0, run_layer(base_only, x, 1.0))
+    m.set_alpha(-2.0)
+    assert torch.equal(y0, m(x))
+
+
+@pytest.mark.parametrize("cfg", [(1, 8, 4, 1), (1, 8, 2, 2), (2, 4, 4, 4), (4, 2, 2, 8), (8, 1, 4, 2),
+                                 (1, 4, 4, 1), (2, 2, 2, 4), (1, 8, 4, 8)])
+@pytest.mark.parametrize("M", [1, 5, 16, 33, 64])
+def test_every_decode_tiling_agrees_with_the_oracle(oracle_mod, cfg, M):
+    K, N = 1184, 210                      # ragged in both directions (K % 128 != 0, N % 16 != 0)
+    layer = wl.make_layer(K, N, 0.02, seed=41)
+    x = wl.make_input(M, K, seed=41)
+    ref = layer_oracle(oracle_mod, layer, x, 0.75)
+    try:
+        assert _lib.lib().ortho_b200_set_decode_config(*cfg) == 0
+        y = run_layer(layer.to(DEV), x.to(DEV), 0.75)
+    finally:
+        _lib.lib().ortho_b200_set_decode_config(0, 0, 0, 0)
+    assert_close(y.float().cpu().numpy(), ref, f"cfg={cfg} M={M}")
+
+
+@pytest.mark.parametrize("K,N", wl.CFG1_SHAPES)
+def test_decode_sweep_shapes_against_oracle(oracle_mod, K, N):
+    """Llama-7B-style shapes at M in {1,4,16}: full output against the oracle for a row sample
+    (rows are independent: a row subset of the layer is a smaller layer with the same arithmetic)."""
+    layer = wl.make_layer(K, N, wl.CFG1_DENSITY, seed=51, device=DEV)
+    rows = sorted({0, 1, 15, 16, 127, N // 2, N - 17, N - 1} | set(range(N // 3, N // 3 + 40)))
+    cpu = layer.to("cpu")
+    for M in wl.CFG1_M:
+        x = wl.make_input(M, K, seed=M, device=DEV)
+        y = run_layer(layer, x, 1.0).float().cpu().numpy()
+        sub = [cpu.rows(r, r + 1) for r in rows]
+        ref = np.concatenate([layer_oracle(oracle_mod, s, x.cpu(), 1.0, threads=1) for s in sub], axis=1)
+        assert_close(y[:, rows], ref, f"{K}->{N} M={M}")
+        assert np.isfinite(y).all()
+
+
+def test_linearity_and_alpha_properties_at_full_size():
+    """Size-independent properties on a full decode-sweep layer: Y(alpha) - Y(0) is linear in alpha,
+    and the forward is additive over token rows (each row is computed independently)."""
+    layer = wl.make_layer(4096, 12288, wl.CFG1_DENSITY, seed=61, device=DEV)
+    x = wl.make_input(16, 4096, seed=61, device=DEV)
+    y0 = run_layer(layer, x, 0.0).float()
+    y1 = run_layer(layer, x, 1.0).float()
+    yh = run_layer(layer, x, 0.5).float()
+    d1, dh = (y1 - y0), (yh - y0)
+    assert (d1.abs().max() > 0.05)
+    assert torch.allclose(dh, 0.5 * d1, atol=1.5e-2, rtol=0)
+    for M in (1, 4):
+        ym = run_layer(layer, x[:M].contiguous(), 1.0).float()
+        assert torch.allclose(ym, y1[:M], atol=4e-3, rtol=2e-3)
+
+
+def test_module_forward_shapes_bias_and_dtype():
+    layer = wl.make_layer(256, 96, 0.05, seed=71, device=DEV)
+    m = layer.to_module()
+    x = wl.make_input(6, 256, seed=71, device=DEV).reshape(2, 3, 256)
+    y = m(x)
+    assert y.shape == (2, 3, 96) and y.dtype == torch.float16
+    mb = OrthoLinear(256, 96, bias=True).to(DEV)
+    mb.load_state_dict({**m.state_dict(), "bias": torch.full((96,), 0.5)})
+    assert torch.allclose(mb(x).float(), y.float() + 0.5, atol=2e-3)
+    yb = m(x.to(torch.bfloat16))
+    assert yb.dtype == torch.bfloat16
+    assert m(x[:0]).shape == (0, 3, 96)
+    # fresh module (zero-length ortho buffers) is legal: base only, all-zero weights -> zeros
+    fresh = OrthoLinear(256, 96).to(DEV)
+    assert torch.count_nonzero(fresh(x)) == 0
+
+
+def test_error_statuses_surface_as_exceptions():
+    layer = wl.make_layer(64, 32, 0.05, seed=81, device=DEV)
+    x = wl.make_input(2, 64, seed=81, device=DEV)
+    y = torch.empty(2, 32, dtype=torch.float16, device=DEV)
+    other = _C_ops.Plan(layer.row_ptr[:17].contiguous(), layer.col[:int(layer.row_ptr[16])].contiguous(),
+                        layer.vals[:int(layer.row_ptr[16])].contiguous(), 64, 16)
+    with pytest.raises(_lib.OrthoB200Error, match="plan"):
+        _C_ops.forward(layer.base_weight, layer.base_scales, layer.vals, layer.col, layer.row_ptr, x, y, 1.0, plan=other)
+    with pytest.raises(TypeError):
+        _C_ops.forward(layer.base_weight, layer.base_scales, layer.vals, layer.col, layer.row_ptr, x.float(), y, 1.0)
+    xm = torch.empty(2, 65, dtype=torch.float16, device=DEV)[:, 1:]
+    with pytest.raises(ValueError):
+        _C_ops.forward(layer.base_weight, layer.base_scales, layer.vals, layer.col, layer.row_ptr, xm, y, 1.0)
+    # K not a multiple of 32 is rejected by the library, not silently handled
+    st = _lib.lib().ortho_b200_forward(layer.base_weight.data_ptr(), layer.base_scales.data_ptr(), None, None, None, 0,
+                                       x.data_ptr(), y.data_ptr(), 2, 48, 32, 1.0, None, None, 0, None)
+    assert st == 2
+    torch.cuda.synchronize()
