@@ -1,0 +1,403 @@
+"""Benchmark of the OrthoLinear forward on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (``config.workload``): the Llama-7B-style decode sweep -- four layers (in->out:
+4096->12288, 4096->4096, 4096->22016, 11008->4096), M in {1, 4, 16} FP16 tokens each, INT4 base
+from W~N(0,0.02^2), 0.5 % uniform FP16 ortho ~N(0,0.05^2), alpha=1, seeded synthetic tensors.
+One "step" is one pass over the sweep (12 forwards).  Steps rotate over several distinct copies
+of the four layers so that every forward streams its weights from HBM rather than from L2.
+
+``value``   decode GB/s = algorithmic bytes of the step / device time, inputs resident in HBM, the
+            step replayed as a CUDA graph (kernels back to back, timed with CUDA events).
+``e2e``     the same metric through ``OrthoLinear.forward`` with host buffers: per forward, X is
+            copied from pinned host memory, and Y is copied back, inside the timed region.
+``roofline`` HBM roofline of the decode kernel from the same timed region.
+``cpu_baseline`` the reference's own CPU forward timed on this host (N=1 only).
+``prefill`` (extra) tensor-core regime, 8192x8192 with Zipf-row ortho, TFLOP/s per M.
+With N > 1 (launched by torch.distributed.run) every layer is sharded over output rows, each
+rank runs its shard and the outputs are all-gathered with NCCL; ``scaling`` is "strong".
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "OrthoLinear decode GB/s (% HBM peak) & prefill TFLOP/s at 1/2/4/8 B200"
+WORKLOAD = "decode sweep: (4096->12288, 4096->4096, 4096->22016, 11008->4096) x M{1,4,16}, 0.5% ortho, alpha=1"
+N_COPIES = 6          # distinct weight sets rotated through (6 x ~100 MB >> 126 MB of L2)
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "tf_burst": d["bf16_tflops"], "tf_sustained": d["bf16_tflops_sustained"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tf_burst": 1590.0, "tf_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            parts = [s.strip() for s in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for nme, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(nme)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def sweep_items():
+    from libortho_b200 import workloads as wl
+    return [(K, N, M) for M in wl.CFG1_M for (K, N) in wl.CFG1_SHAPES]
+
+
+# ------------------------------------------------------------------------------------------------
+def run_reference(args):
+    """The reference's own CPU forward (unmodified src/ortho.c behind oracle/_ref, built with the
+    reference's flags) on this host's cores; each step is one pass over the same decode sweep."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import numpy as np
+    import oracle
+    from libortho_b200 import workloads as wl
+    impl, kind = ("reference_fast", "reference") if oracle.available("reference_fast") else ("port", "port")
+    if impl == "port":
+        oracle.build()
+    threads = oracle.host_threads()
+    layers = {}
+    for (K, N) in wl.CFG1_SHAPES:
+        L = wl.make_layer(K, N, wl.CFG1_DENSITY, seed=0)
+        layers[(K, N)] = (L, L.base_weight.numpy(), L.base_scales.float().numpy(), L.row_ptr.numpy(), L.col.numpy(),
+                          L.vals.float().numpy())
+    xs = {(K, M): wl.make_input(M, K, seed=M).float().numpy() for (K, N, M) in sweep_items()}
+    step_bytes = sum(layers[(K, N)][0].algorithmic_bytes(M) for (K, N, M) in sweep_items())
+
+    def step():
+        for (K, N, M) in sweep_items():
+            _, pw, sc, rp, co, va = layers[(K, N)]
+            oracle.forward_csr(pw, sc, rp, co, va, xs[(K, M)], 1.0, impl=impl, threads=threads)
+
+    for _ in range(max(0, args.warmup)):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = time.perf_counter() - t0
+    val = step_bytes * args.steps / dt / 1e9
+    sample = f"{args.steps} full passes of the decode sweep (12 forwards each), {threads} threads"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "device": "host CPU"},
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from libortho_b200 import _C_ops, _lib, workloads as wl
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    pk = peaks()
+    lib = _lib.lib()
+
+    items = sweep_items()
+    # ---- build N_COPIES sets of (sharded) layers, plans and output buffers ------------------
+    sets = []
+    full_bytes = 0
+    for c in range(N_COPIES):
+        layers = {}
+        for (K, N) in wl.CFG1_SHAPES:
+            L = wl.make_layer(K, N, wl.CFG1_DENSITY, seed=c, device=dev)
+            if c == 0:
+                pass
+            if world > 1:
+                n0, n1 = N * rank // world, N * (rank + 1) // world
+                full = L
+                L = full.rows(n0, n1)
+                L._full_bytes = {M: full.algorithmic_bytes(M) for M in wl.CFG1_M}
+                del full
+            else:
+                L._full_bytes = {M: L.algorithmic_bytes(M) for M in wl.CFG1_M}
+            plan = _C_ops.Plan(L.row_ptr, L.col, L.vals, L.K, L.N)
+            layers[(K, N)] = (L, plan)
+        sets.append(layers)
+    torch.cuda.empty_cache()
+    step_bytes = sum(sets[0][(K, N)][0]._full_bytes[M] for (K, N, M) in items)
+    xs = {(K, M): wl.make_input(M, K, seed=M, device=dev) for (K, N, M) in items}
+    ys = {(K, N, M): torch.empty(M, sets[0][(K, N)][0].N, dtype=torch.float16, device=dev) for (K, N, M) in items}
+    yg = {(K, N, M): torch.empty(world, M, sets[0][(K, N)][0].N, dtype=torch.float16, device=dev)
+          for (K, N, M) in items} if world > 1 else None
+
+    def run_step(c):
+        for (K, N, M) in items:
+            L, plan = sets[c][(K, N)]
+            _C_ops.forward(L.base_weight, L.base_scales, L.vals, L.col, L.row_ptr, xs[(K, M)], ys[(K, N, M)], 1.0, plan=plan)
+            if world > 1:
+                dist.all_gather_into_tensor(yg[(K, N, M)], ys[(K, N, M)])
+
+    # ---- capture one CUDA graph per weight set --------------------------------------------------
+    stream = torch.cuda.Stream(dev)
+    graphs = []
+    launches_per_step = 0
+    with torch.cuda.stream(stream):
+        run_step(0)
+        stream.synchronize()
+        for c in range(N_COPIES):
+            g = torch.cuda.CUDAGraph()
+            l0 = lib.ortho_b200_launch_count()
+            with torch.cuda.graph(g, stream=stream):
+                run_step(c)
+            launches_per_step = lib.ortho_b200_launch_count() - l0
+            graphs.append(g)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    with torch.cuda.stream(stream):
+        for i in range(max(3, args.warmup)):
+            graphs[i % N_COPIES].replay()
+        barrier()
+        sampler = ClockSampler(local) if rank == 0 else None
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record(stream)
+        for i in range(args.steps):
+            graphs[i % N_COPIES].replay()
+        ev1.record(stream)
+        barrier()
+        ms = ev0.elapsed_time(ev1)
+    tms = torch.tensor([ms], device=dev)
+    if world > 1:
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+    ms = float(tms.item())
+    clocks = sampler.stop() if sampler else None
+    value = step_bytes * args.steps / (ms * 1e-3) / 1e9
+
+    # ---- end to end through OrthoLinear.forward with host buffers -------------------------------
+    mods = [{kn: sets[c][kn][0].to_module() for kn in sets[c]} for c in range(N_COPIES)]
+    hx = {(K, M): xs[(K, M)].cpu().pin_memory() for (K, N, M) in items}
+    hy = {(K, N, M): torch.empty(M, N, dtype=torch.float16).pin_memory() for (K, N, M) in items}
+    h2d = sum(hx[(K, M)].numel() * 2 for (K, N, M) in items)
+    d2h = sum(hy[k].numel() * 2 for k in hy)
+
+    def e2e_step(c):
+        for (K, N, M) in items:
+            xd = hx[(K, M)].to(dev, non_blocking=True)
+            y = mods[c][(K, N)](xd)
+            if world > 1:
+                dist.all_gather_into_tensor(yg[(K, N, M)], y)
+                hy[(K, N, M)].copy_(yg[(K, N, M)].permute(1, 0, 2).reshape(M, -1), non_blocking=True)
+            else:
+                hy[(K, N, M)].copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for i in range(3):
+        e2e_step(i % N_COPIES)
+    barrier()
+    e2e_steps = max(3, min(args.steps, 20))
+    l_before = lib.ortho_b200_launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for i in range(e2e_steps):
+        e2e_step(i % N_COPIES)
+    ev1.record()
+    barrier()
+    e2e_launches = lib.ortho_b200_launch_count() - l_before
+    tms = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
+    if world > 1:
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+    e2e_val = step_bytes * e2e_steps / (float(tms.item()) * 1e-3) / 1e9
+
+    # ---- per-(shape, M) detail and the prefill regime (rank 0 / single GPU extras) ---------------
+    detail, prefill = {}, {}
+    if world == 1:
+        for (K, N, M) in items:
+            us = time_forward_us(lambda c: sets[c][(K, N)], xs[(K, M)], ys[(K, N, M)], stream)
+            gbs = sets[0][(K, N)][0].algorithmic_bytes(M) / us / 1e3
+            detail[f"{K}x{N}:M{M}"] = {"us": round(us, 2), "GB/s": round(gbs, 1), "frac_hbm": round(gbs / pk["hbm_gbs"], 3)}
+        if not args.no_prefill:
+            del sets, mods
+            torch.cuda.empty_cache()
+            prefill = bench_prefill(dev, pk)
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "parallelism": f"N-sharded x{world} + all-gather" if world > 1 else "single GPU",
+                       "l2": f"rotation over {N_COPIES} distinct weight sets (~100 MB each) > 126 MB L2",
+                       "timing": "CUDA graph replay per step, CUDA events on the launch stream, max over ranks"},
+            "clocks": clocks,
+            "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": e2e_steps, "api": "OrthoLinear.forward, pinned host X in, Y out, per forward"},
+            "gpu_launches": int(launches_per_step * args.steps + e2e_launches),
+            "roofline": {"bound": "hbm", "achieved": value if world == 1 else value / world, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                         "frac": (value if world == 1 else value / world) / pk["hbm_gbs"], "traffic": None,
+                         "peak_source": pk["source"], "kernel": "ob::decode_kernel",
+                         "launches_per_step": launches_per_step,
+                         "algorithmic_bytes_per_launch": step_bytes / max(1, len(items)) / world},
+            "percent_of_nominal_8TBs": value / world / 8000.0 * 100.0,
+        }
+        if detail:
+            line["decode_detail"] = detail
+        if prefill:
+            line["prefill"] = prefill
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_baseline()
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def time_forward_us(get_layer, x, y, stream, reps=2, replays=5):
+    """Median device time of one forward, from a CUDA graph of reps*N_COPIES back-to-back launches
+    that rotate over the weight copies (so that each launch streams from HBM)."""
+    import torch
+    from libortho_b200 import _C_ops
+    with torch.cuda.stream(stream):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            for r in range(reps * N_COPIES):
+                L, plan = get_layer(r % N_COPIES)
+                _C_ops.forward(L.base_weight, L.base_scales, L.vals, L.col, L.row_ptr, x, y, 1.0, plan=plan)
+        g.replay()
+        stream.synchronize()
+        ts = []
+        for _ in range(replays):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            g.replay()
+            e1.record(stream)
+            e1.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3 / (reps * N_COPIES))
+    return statistics.median(ts)
+
+
+def bench_prefill(dev, pk):
+    import torch
+    from libortho_b200 import _C_ops, workloads as wl
+    K, N = wl.CFG2_SHAPE
+    L = wl.make_zipf_layer(K, N, wl.CFG2_DENSITY, seed=0, device=dev, alpha=wl.CFG2_ALPHA)
+    plan = _C_ops.Plan(L.row_ptr, L.col, L.vals, K, N)
+    out = {}
+    for M in wl.CFG2_M:
+        x = wl.make_input(M, K, seed=M, device=dev)
+        y = torch.empty(M, N, dtype=torch.float16, device=dev)
+        ws_bytes = _C_ops.workspace_bytes(M, K, N)
+        ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
+        for alpha, tag in ((wl.CFG2_ALPHA, "fused"), (0.0, "base_only")):
+            for _ in range(3):
+                _C_ops.forward(L.base_weight, L.base_scales, L.vals, L.col, L.row_ptr, x, y, alpha, plan=plan, workspace=ws)
+            torch.cuda.synchronize()
+            reps = 10 if M <= 2048 else 4
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                _C_ops.forward(L.base_weight, L.base_scales, L.vals, L.col, L.row_ptr, x, y, alpha, plan=plan, workspace=ws)
+            e1.record()
+            e1.synchronize()
+            ms = e0.elapsed_time(e1) / reps
+            tf = L.algorithmic_flops(M, alpha) / (ms * 1e-3) / 1e12
+            out[f"M{M}:{tag}"] = {"ms": round(ms, 4), "TFLOP/s": round(tf, 1),
+                                  "frac_of_measured_sustained": round(tf / pk["tf_sustained"], 3),
+                                  "frac_of_nominal_2250": round(tf / 2250.0, 3)}
+    out["config"] = "8192x8192, 0.1% ortho with Zipf(1.2) row loads, alpha=0.5; X (M x 8192 FP16) larger than L2 only for M=8192"
+    return out
+
+
+def cpu_baseline():
+    """Reference CPU forward (oracle/_ref, reference flags) on this host: one pass over the sweep."""
+    import oracle
+    from libortho_b200 import workloads as wl
+    impl, kind = ("reference_fast", "reference") if oracle.available("reference_fast") else ("port", "port")
+    if impl == "port":
+        oracle.build()
+    threads = oracle.host_threads()
+    total_bytes, t_total = 0, 0.0
+    for (K, N) in wl.CFG1_SHAPES:
+        L = wl.make_layer(K, N, wl.CFG1_DENSITY, seed=0)
+        a = (L.base_weight.numpy(), L.base_scales.float().numpy(), L.row_ptr.numpy(), L.col.numpy(), L.vals.float().numpy())
+        for M in wl.CFG1_M:
+            x = wl.make_input(M, K, seed=M).float().numpy()
+            t0 = time.perf_counter()
+            oracle.forward_csr(*a, x, 1.0, impl=impl, threads=threads)
+            t_total += time.perf_counter() - t0
+            total_bytes += L.algorithmic_bytes(M)
+    return {"value": total_bytes / t_total / 1e9, "unit": "GB/s", "cores": threads, "kind": kind,
+            "sample": f"one full pass of the decode sweep (12 forwards), {t_total:.2f} s wall",
+            "ms_per_step": t_total * 1e3}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -125,9 +125,19 @@ ORTHO_B200_API int ortho_b200_forward(const void *q_weight, const void *q_scales
                        const ortho_b200_plan *plan,
                        void *workspace, int64_t workspace_bytes, void *stream);
 
-/* Benchmark/tuning hook: overrides the decode kernel's tile choice for later forwards from this
- * process.  Arguments are (row groups per CTA, k groups per CTA, loads in flight, k split);
- * any value <= 0 restores the built-in choice.  Returns ERR_SHAPE for an unsupported tuple. */
+/* Synchronises the device and reports whether any kernel of this library gave up on a bounded
+ * wait since the last query (ERR_KERNEL, and the flag is cleared) or not (OK).  Replaces the
+ * cudaDeviceSynchronize + error check at the end of the reference dispatcher
+ * (src/dual_gemm.cu:361-371), as an explicit call instead of a cost on every forward. */
+ORTHO_B200_API int ortho_b200_query_kernel_status(void);
+
+/* Benchmark/tuning hook: overrides the decode kernels' tiling for later forwards from this process.
+ *   row_groups > 0 : generic kernel with (row groups per CTA, k groups per CTA, loads in flight,
+ *                    k split over the cluster);
+ *   row_groups == -1: streaming TMA kernel (M <= 16) with k_split CTAs per cluster and `unroll`
+ *                    ring slots per warp (either may be 0 for the built-in choice);
+ *   row_groups == 0 : restore the built-in choice.
+ * Returns ERR_SHAPE for an unsupported tuple. */
 ORTHO_B200_API int ortho_b200_set_decode_config(int row_groups, int k_groups, int unroll, int k_split);
 
 /* Number of kernel launches issued by this library from this process (all threads). */

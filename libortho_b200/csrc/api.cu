@@ -16,6 +16,26 @@ static std::atomic<long long> g_launches{0};
 void note_cuda_error(cudaError_t e) { tl_last_cuda_error = (int)e; (void)cudaGetLastError(); }
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
+// device word that kernels set when a bounded wait gives up; reset and read by
+// ortho_b200_query_kernel_status()
+__device__ int g_kernel_status_word;
+
+int *kernel_status_word()
+{
+    static thread_local int cached_dev = -1;
+    static thread_local int *cached = nullptr;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+    if (dev != cached_dev) {
+        void *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_kernel_status_word);
+        if (e != cudaSuccess) { note_cuda_error(e); return nullptr; }
+        cached = (int *)p;
+        cached_dev = dev;
+    }
+    return cached;
+}
+
 static int check_device()
 {
     static thread_local int checked_device = -1;
@@ -57,6 +77,20 @@ extern "C" int64_t ortho_b200_launch_count(void) { return (int64_t)g_launches.lo
 extern "C" int ortho_b200_set_decode_config(int row_groups, int k_groups, int unroll, int k_split)
 {
     return set_decode_config(row_groups, k_groups, unroll, k_split);
+}
+
+extern "C" int ortho_b200_query_kernel_status(void)
+{
+    int *w = kernel_status_word();
+    if (!w) return ORTHO_B200_ERR_CUDA;
+    int h = 0;
+    OB_CUDA(cudaMemcpy(&h, w, sizeof(int), cudaMemcpyDeviceToHost));
+    if (h != 0) {
+        int zero = 0;
+        OB_CUDA(cudaMemcpy(w, &zero, sizeof(int), cudaMemcpyHostToDevice));
+        return ORTHO_B200_ERR_KERNEL;
+    }
+    return ORTHO_B200_OK;
 }
 
 extern "C" int64_t ortho_b200_workspace_bytes(int64_t M, int64_t K, int64_t N)

@@ -257,9 +257,21 @@ decode_kernel(const DecodeParams p)
 
 struct DecodeCfg { int wr, wk, u, s; };
 static DecodeCfg g_override = {0, 0, 0, 0};
+static bool g_force_stream = false;
+int launch_decode_stream(const FwdArgs &a);          // decode_stream.cu
+void set_stream_config(int s, int stages);
 
 int set_decode_config(int wr, int wk, int u, int s)
 {
+    if (wr == -1) {
+        if ((s != 0 && s != 1 && s != 2 && s != 4 && s != 8) || u < 0 || u > 12 || u == 1) return ORTHO_B200_ERR_SHAPE;
+        g_override = {0, 0, 0, 0};
+        g_force_stream = true;
+        set_stream_config(s, u);
+        return ORTHO_B200_OK;
+    }
+    g_force_stream = false;
+    set_stream_config(0, 0);
     if (wr <= 0 || wk <= 0 || u <= 0 || s <= 0) { g_override = {0, 0, 0, 0}; return ORTHO_B200_OK; }
     const bool shape_ok = (wr == 1 && wk == 8) || (wr == 2 && wk == 4) || (wr == 4 && wk == 2) ||
                           (wr == 8 && wk == 1) || (wr == 1 && wk == 4) || (wr == 2 && wk == 2);
@@ -345,6 +357,8 @@ static int launch_mt(const FwdArgs &a, const DecodeCfg &c)
 int launch_decode(const FwdArgs &a)
 {
     if (a.M > ORTHO_B200_DECODE_MAX_M) return ORTHO_B200_ERR_SHAPE;
+    // M <= 16: persistent TMA streaming kernel, unless the generic tiling was asked for explicitly
+    if (a.M <= 16 && (g_force_stream || g_override.wr == 0)) return launch_decode_stream(a);
     const DecodeCfg c = choose(a.M, a.K, a.N);
     if (a.M <= 8) return launch_mt<1>(a, c);
     if (a.M <= 16) return launch_mt<2>(a, c);

@@ -1,0 +1,434 @@
+// Persistent streaming kernel for the decode regime (M <= 16): the kernel that has to run at HBM
+// speed.  Same arithmetic as decode.cu (weights as the 16-row operand of mma.sync m16n8k16, token
+// block as the 8-column operand, exact small-integer weights, per-row scale applied once in the
+// FP32 epilogue, ortho term from packed entries), but organised around memory-level parallelism:
+//
+//  * the packed INT4 base is fetched by TMA (cp.async.bulk.tensor.2d, 128-byte swizzle) in boxes of
+//    16 rows x 128 bytes (256 weights per row); every warp owns a private ring of such boxes with
+//    one mbarrier per slot and keeps `stages` boxes in flight, across tile boundaries;
+//  * a cluster of S CTAs (8 warps each) owns a 16-row output tile; the K range is split over the
+//    8*S warps.  Clusters are persistent and walk the tiles round-robin; the activation slab of a
+//    CTA's fixed K range is staged in shared memory once, in the pair order the unpack produces;
+//  * partial sums are exchanged through distributed shared memory with a split-phase cluster
+//    barrier: a tile's arrive is followed by the next tile's main loop, and the wait + finalize of
+//    tile i happen after tile i+1 has been accumulated, so no warp idles at a barrier;
+//  * the sparse stream is software-pipelined the same way: row pointers are fetched two tiles
+//    ahead, packed entries one tile ahead, so that the dependent row_ptr -> entry -> activation
+//    chain never sits on the critical path.  One warp handles one output row at a time; the
+//    per-token sums are combined with a halving butterfly of warp shuffles (fixed order).
+//
+// No global scratch, no atomics: results are bitwise reproducible, and with alpha <= 0 or nnz == 0
+// the sparse stream is not touched at all, so the output equals the base-only output exactly.
+#include <cstdlib>
+
+#include "common.cuh"
+#include "tma.cuh"
+
+namespace ob {
+
+constexpr int kBoxBytes = 16 * 128;   // one TMA box: 16 rows x 128 packed bytes
+constexpr int kWarps = 8;
+
+struct StreamParams {
+    const __half *scales; const __half *x; __half *y;
+    OrthoView ov; int has_ortho; float alpha;
+    int M, K, N;
+    int nboxes;    // ceil(K / 256)
+    int ntiles;    // ceil(N / 16)
+    int pitch;     // bytes between token rows of the staged activation slab
+    int stages;    // ring depth per warp
+    int *status;   // device word: set to 1 if a bounded wait gave up
+    int dbg;
+};
+
+__device__ __forceinline__ uint32_t prmt_b32(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+
+// Reduce V per-lane values over the 32 lanes with a halving butterfly: V/2 + V/4 + ... + 1
+// exchanges, then plain xor steps.  Returns the total of value index (lane >> (5 - log2 V)), valid
+// in every lane of that index group.  The order of additions is fixed.
+template <int V>
+__device__ __forceinline__ float butterfly_reduce(float (&v)[V], int lane)
+{
+    int off = 16;
+#pragma unroll
+    for (int half = V / 2; half >= 1; half >>= 1) {
+        const bool up = (lane & off) != 0;
+#pragma unroll
+        for (int j = 0; j < half; j++) {
+            const float send = up ? v[j] : v[j + half];
+            const float keep = up ? v[j + half] : v[j];
+            v[j] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+        }
+        off >>= 1;
+    }
+    float r = v[0];
+    for (; off >= 1; off >>= 1) r += __shfl_xor_sync(0xffffffffu, r, off);
+    return r;
+}
+
+template <int MT>
+__global__ void __launch_bounds__(kWarps * 32, 1)
+decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParams p)
+{
+    constexpr int TOK = 8 * MT;
+    extern __shared__ __align__(1024) unsigned char smem[];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int S = (int)cluster_nctarank();
+    const int rank = (int)cluster_ctarank();
+    const int cid = blockIdx.y, G = gridDim.y;
+    const int K = p.K, N = p.N, M = p.M;
+
+    // ---- shared memory carve-up ----------------------------------------------------------------
+    // the 128-byte TMA swizzle is a function of the shared-memory address: ring slots sit on 1 KB
+    unsigned char *ring = smem + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);    // kWarps * stages * 2 KB
+    uint64_t *bars = reinterpret_cast<uint64_t *>(ring + (size_t)kWarps * p.stages * kBoxBytes);
+    float *red = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(bars) + ((kWarps * p.stages * 8 + 127) & ~127));
+    float *osm = red + 2 * kWarps * 16 * TOK;                                     // [2][16*TOK]
+    unsigned char *xs = reinterpret_cast<unsigned char *>(osm + 2 * 16 * TOK);    // M * pitch
+
+    // ---- this warp's share of the K range, in boxes of 256 weights -----------------------------
+    const int cb0 = (p.nboxes * rank) / S, cb1 = (p.nboxes * (rank + 1)) / S;
+    const int wb0 = cb0 + ((cb1 - cb0) * warp) / kWarps, wb1 = cb0 + ((cb1 - cb0) * (warp + 1)) / kWarps;
+    const int nbw = wb1 - wb0;
+    const int nt = (p.ntiles - cid + G - 1) / G;          // tiles walked by this cluster
+    const int total = nt * nbw;                           // boxes this warp consumes
+    const int k_lo = cb0 * 256, k_hi = min(cb1 * 256, K); // activation slab of this CTA
+
+    unsigned char *my_ring = ring + (size_t)warp * p.stages * kBoxBytes;
+    uint64_t *my_bars = bars + warp * p.stages;
+
+    auto issue = [&](int idx) {   // lane 0 only
+        const int ti = idx / nbw, bi = idx - ti * nbw;
+        const int st = idx % p.stages;
+        mbar_arrive_expect_tx(&my_bars[st], kBoxBytes);
+        tma_load_2d(my_ring + (size_t)st * kBoxBytes, &wmap, &my_bars[st], (wb0 + bi) * 128, (cid + ti * G) * 16);
+    };
+
+    if (lane == 0) {
+        prefetch_tensormap(&wmap);
+        for (int s = 0; s < p.stages; s++) mbar_init(&my_bars[s], 1);
+        fence_mbar_init();
+        const int pre = min(p.stages, total);
+        for (int i = 0; i < pre; i++) issue(i);
+    }
+
+    // ---- sparse stream prologue: row pointers of the first two tiles, entries of the first ------
+    // every CTA walks all 16 rows of a tile (2 per warp) and keeps the entries inside its K range
+    int rp_cur[2][2] = {{0, 0}, {0, 0}}, rp_nxt[2][2] = {{0, 0}, {0, 0}};
+    uint32_t ent[2][2] = {{0, 0}, {0, 0}};
+    auto load_rp = [&](int ti, int (&rp)[2][2]) {
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            const int n = (cid + ti * G) * 16 + warp + 8 * r;
+            rp[r][0] = rp[r][1] = 0;
+            if (ti < nt && n < N) { rp[r][0] = p.ov.row_ptr[n]; rp[r][1] = p.ov.row_ptr[n + 1]; }
+        }
+    };
+    auto load_entry = [&](int e) -> uint32_t {
+        if (p.ov.entries) return p.ov.entries[e];
+        const int c = p.ov.col[e];
+        const unsigned short vb = __half_as_ushort(p.ov.val[e]);
+        return ((unsigned)c >= (unsigned)K) ? 0u : (((uint32_t)vb << 16) | (uint32_t)c);
+    };
+    auto load_ent = [&](const int (&rp)[2][2], uint32_t (&en)[2][2]) {
+#pragma unroll
+        for (int r = 0; r < 2; r++)
+#pragma unroll
+            for (int q = 0; q < 2; q++) {
+                const int e = rp[r][0] + q * 32 + lane;
+                en[r][q] = (e < rp[r][1]) ? load_entry(e) : 0u;
+            }
+    };
+    if (p.has_ortho) {
+        load_rp(0, rp_cur);
+        load_rp(1, rp_nxt);
+        load_ent(rp_cur, ent);
+    }
+
+    // ---- stage X[:, k_lo:k_hi) once, in unpack pair order ---------------------------------------
+    // 16-byte chunk (x0..x7) is stored as (x0,x4,x1,x5,x2,x6,x3,x7); inside a 128-element step the 16
+    // chunks are laid out [j][t] so that the 4 lanes of a row group read 64 contiguous bytes.
+    {
+        const int chunks_per_row = (cb1 - cb0) * 32;
+        const int totalc = M * chunks_per_row;
+        for (int idx = tid; idx < totalc; idx += kWarps * 32) {
+            const int r = idx / chunks_per_row, q = idx - r * chunks_per_row;
+            const int k = k_lo + q * 8;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (k < K) v = *reinterpret_cast<const uint4 *>(p.x + (size_t)r * K + k);
+            uint4 o;
+            o.x = prmt_b32(v.x, v.z, 0x5410);
+            o.y = prmt_b32(v.x, v.z, 0x7632);
+            o.z = prmt_b32(v.y, v.w, 0x5410);
+            o.w = prmt_b32(v.y, v.w, 0x7632);
+            const int sl = q >> 4, c16 = q & 15, tt = c16 >> 2, j = c16 & 3;
+            *reinterpret_cast<uint4 *>(xs + (size_t)r * p.pitch + sl * 256 + j * 64 + tt * 16) = o;
+        }
+    }
+    __syncthreads();
+
+    // box rows are permuted so that the two rows met in one shared-memory phase differ in bit 2 of
+    // (row & 7): mma row g <-> box row rho(g); with the 128-byte swizzle every phase is conflict free
+    const int brow0 = (g >> 1) | ((g & 1) << 2), brow1 = brow0 + 8;
+    const uint32_t sw0 = (uint32_t)(brow0 & 7), sw1 = (uint32_t)(brow1 & 7);
+
+    bool dead = false;
+    int idx = 0;
+    constexpr int NCH = (MT == 1) ? 4 : 2;   // independent accumulator chains per token block
+    float acc[NCH][MT][4];
+    uint32_t dummy = 0;
+
+    auto finalize = [&](int ti) {
+        const int buf = ti & 1;
+        const int RB = 16 / S;
+        const int n_el = RB * M;
+        const uint32_t red_base = smem_u32(red + (size_t)buf * kWarps * 16 * TOK);
+        const uint32_t osm_base = smem_u32(osm + (size_t)buf * 16 * TOK);
+        for (int e = tid; e < n_el; e += kWarps * 32) {
+            const int m = e / RB, i = rank * RB + (e - m * RB);
+            const int n = (cid + ti * G) * 16 + i;
+            if (n < N) {
+                float s = 0.f, o = 0.f;
+                for (int r2 = 0; r2 < S; r2++) {
+                    const uint32_t rb = mapa_shared(red_base, (uint32_t)r2);
+#pragma unroll
+                    for (int w = 0; w < kWarps; w++) s += ld_dsmem_f32(rb + (uint32_t)((w * 16 * TOK + i * TOK + m) * 4));
+                    if (p.has_ortho) o += ld_dsmem_f32(mapa_shared(osm_base, (uint32_t)r2) + (uint32_t)((i * TOK + m) * 4));
+                }
+                float v = __half2float(p.scales[n]) * s;
+                if (p.has_ortho) v = fmaf(p.alpha, o, v);
+                p.y[(size_t)m * N + n] = __float2half_rn(v);
+            }
+        }
+    };
+
+    for (int ti = 0; ti < nt; ti++) {
+#pragma unroll
+        for (int c = 0; c < NCH; c++)
+#pragma unroll
+            for (int i = 0; i < MT; i++) { acc[c][i][0] = acc[c][i][1] = acc[c][i][2] = acc[c][i][3] = 0.f; }
+
+        // sparse stream, pipeline stage A/B: row pointers two tiles ahead, entries one tile ahead
+        int rp_fut[2][2] = {{0, 0}, {0, 0}};
+        uint32_t ent_nxt[2][2] = {{0, 0}, {0, 0}};
+        if (p.has_ortho) {
+            load_rp(ti + 2, rp_fut);
+            load_ent(rp_nxt, ent_nxt);
+        }
+
+        // ---- base: consume this warp's boxes of the tile ---------------------------------------
+        for (int bi = 0; bi < nbw; bi++, idx++) {
+            const int st = idx % p.stages;
+            const uint32_t ph = (uint32_t)((idx / p.stages) & 1);
+            if (!dead && !mbar_wait(&my_bars[st], ph)) { dead = true; if (lane == 0) atomicExch(p.status, 1); }
+            const unsigned char *box = my_ring + (size_t)st * kBoxBytes;
+            const int sl_base = (wb0 + bi - cb0) * 2;
+            if (p.dbg == 3) { dummy ^= *reinterpret_cast<const uint32_t *>(box + lane * 64); }
+            else
+#pragma unroll
+            for (int s2 = 0; s2 < 2; s2++) {
+                const uint32_t c = (uint32_t)(4 * s2 + t);
+                const uint4 wa = *reinterpret_cast<const uint4 *>(box + brow0 * 128 + ((c ^ sw0) << 4));
+                const uint4 wb = *reinterpret_cast<const uint4 *>(box + brow1 * 128 + ((c ^ sw1) << 4));
+                const uint32_t wwa[4] = {wa.x, wa.y, wa.z, wa.w};
+                const uint32_t wwb[4] = {wb.x, wb.y, wb.z, wb.w};
+                const int sl = sl_base + s2;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    uint32_t ha[4], hb[4];
+                    int4x8_to_half2x4(wwa[j], ha);
+                    int4x8_to_half2x4(wwb[j], hb);
+                    const uint32_t A0[4] = {ha[0], hb[0], ha[1], hb[1]};
+                    const uint32_t A1[4] = {ha[2], hb[2], ha[3], hb[3]};
+#pragma unroll
+                    for (int mt = 0; mt < MT; mt++) {
+                        const int tok = 8 * mt + g;
+                        uint4 xb = make_uint4(0, 0, 0, 0);
+                        if (tok < M)
+                            xb = *reinterpret_cast<const uint4 *>(xs + (size_t)tok * p.pitch + sl * 256 + j * 64 + t * 16);
+                        if (p.dbg == 1) {
+                            dummy ^= A0[0] ^ A0[1] ^ A0[2] ^ A0[3] ^ A1[0] ^ A1[1] ^ A1[2] ^ A1[3] ^ xb.x ^ xb.y ^ xb.z ^ xb.w;
+                        } else if (p.dbg == 2) {
+                            mma_16816(acc[0][mt], A0, xb.x, xb.y);
+                            mma_16816(acc[0][mt], A1, xb.z, xb.w);
+                        } else {
+                            mma_16816(acc[(2 * j) % NCH][mt], A0, xb.x, xb.y);
+                            mma_16816(acc[(2 * j + 1) % NCH][mt], A1, xb.z, xb.w);
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0 && idx + p.stages < total) issue(idx + p.stages);
+        }
+
+        // ---- sparse stream, stage C: this tile's rows from the prefetched entries ---------------
+        float osum[2] = {0.f, 0.f};
+        if (p.has_ortho) {
+#pragma unroll
+            for (int r = 0; r < 2; r++) {
+                float a[TOK];
+#pragma unroll
+                for (int m = 0; m < TOK; m++) a[m] = 0.f;
+                const int e0 = rp_cur[r][0], e1 = rp_cur[r][1];
+                auto apply = [&](uint32_t pk) {
+                    const int c = (int)(pk & 0xFFFFu);
+                    if (c >= k_lo && c < k_hi) {
+                        const float v = __half2float(__ushort_as_half((unsigned short)(pk >> 16)));
+                        const int kk = c - k_lo;
+                        const int q = kk >> 3, e = kk & 7;
+                        const int sl = q >> 4, c16 = q & 15;
+                        const unsigned char *px = xs + sl * 256 + (c16 & 3) * 64 + (c16 >> 2) * 16 + (((e & 3) << 1) | (e >> 2)) * 2;
+#pragma unroll
+                        for (int m = 0; m < TOK; m++)
+                            if (m < M) a[m] = fmaf(v, __half2float(*reinterpret_cast<const __half *>(px + (size_t)m * p.pitch)), a[m]);
+                    }
+                };
+                if (e0 + lane < e1) apply(ent[r][0]);
+                if (e0 + 32 + lane < e1) apply(ent[r][1]);
+                for (int e = e0 + 64 + lane; e < e1; e += 32) apply(load_entry(e));
+                osum[r] = butterfly_reduce<TOK>(a, lane);
+            }
+        }
+
+        // ---- deferred exchange: finish the previous tile, then publish this one -----------------
+        if (ti > 0) { cluster_wait(); finalize(ti - 1); }
+        {
+            float *mine = red + ((size_t)(ti & 1) * kWarps + warp) * 16 * TOK;
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++) {
+                const int col = 8 * mt + 2 * t;
+                float r[4];
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    r[q] = acc[0][mt][q];
+#pragma unroll
+                    for (int c = 1; c < NCH; c++) r[q] += acc[c][mt][q];
+                }
+                *reinterpret_cast<float2 *>(mine + brow0 * TOK + col) = make_float2(r[0], r[1]);
+                *reinterpret_cast<float2 *>(mine + brow1 * TOK + col) = make_float2(r[2], r[3]);
+            }
+            if (p.has_ortho) {
+                constexpr int SH = (TOK == 8) ? 2 : 1;          // lanes per token-index group: 32 / TOK
+                if ((lane & ((1 << SH) - 1)) == 0) {
+                    float *o = osm + (size_t)(ti & 1) * 16 * TOK;
+                    o[(warp)*TOK + (lane >> SH)] = osum[0];
+                    o[(warp + 8) * TOK + (lane >> SH)] = osum[1];
+                }
+            }
+        }
+        cluster_arrive();
+
+        if (p.has_ortho) {
+#pragma unroll
+            for (int r = 0; r < 2; r++) {
+                rp_cur[r][0] = rp_nxt[r][0]; rp_cur[r][1] = rp_nxt[r][1];
+                rp_nxt[r][0] = rp_fut[r][0]; rp_nxt[r][1] = rp_fut[r][1];
+                ent[r][0] = ent_nxt[r][0]; ent[r][1] = ent_nxt[r][1];
+            }
+        }
+    }
+    if (dummy == 0x12345u) atomicExch(p.status, 2);
+    cluster_wait();
+    finalize(nt - 1);
+    // nobody may leave while a peer can still read its shared memory
+    cluster_arrive();
+    cluster_wait();
+}
+
+// ---- host ------------------------------------------------------------------------------------
+int *kernel_status_word();   // api.cu
+
+static int g_stream_cfg[2] = {0, 0};   // {k_split, stages}; 0 = built-in choice
+void set_stream_config(int s, int stages) { g_stream_cfg[0] = s; g_stream_cfg[1] = stages; }
+
+template <int MT>
+static int launch_stream_mt(const FwdArgs &a, const CUtensorMap &map, int S, int stages)
+{
+    constexpr int TOK = 8 * MT;
+    StreamParams p;
+    p.scales = a.scales; p.x = a.x; p.y = a.y; p.ov = a.ortho; p.has_ortho = a.has_ortho; p.alpha = a.alpha;
+    p.M = (int)a.M; p.K = (int)a.K; p.N = (int)a.N;
+    p.nboxes = (int)ceil_div(a.K, 256);
+    p.ntiles = (int)ceil_div(a.N, 16);
+    const int boxes_per_cta = (int)ceil_div(p.nboxes, S);
+    p.pitch = boxes_per_cta * 512 + 64;
+    p.stages = stages;
+    p.status = kernel_status_word();
+    { const char *e = getenv("ORTHO_B200_DBG"); p.dbg = e ? atoi(e) : 0; }
+    if (!p.status) return ORTHO_B200_ERR_CUDA;
+    const size_t smem = 1024 + (size_t)kWarps * stages * kBoxBytes + ((kWarps * stages * 8 + 127) & ~127) +
+                        (size_t)2 * kWarps * 16 * TOK * 4 + (size_t)2 * 16 * TOK * 4 + (size_t)a.M * p.pitch;
+    if (smem > 227 * 1024) return ORTHO_B200_ERR_SHAPE;
+    auto kern = decode_stream_kernel<MT>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        OB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        OB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+        attr_set = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(kWarps * 32, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = a.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)S;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    // persistent grid: as many clusters as can be co-resident, never more than there are tiles
+    // (cached per cluster size and shared-memory footprint)
+    static struct { int s; size_t smem; int n; } cache[16];
+    static int cache_n = 0;
+    int mc = 0;
+    for (int i = 0; i < cache_n; i++)
+        if (cache[i].s == S && cache[i].smem == smem) mc = cache[i].n;
+    if (mc == 0) {
+        cfg.gridDim = dim3((unsigned)S, 148, 1);
+        int n = 0;
+        cudaError_t e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
+        if (e != cudaSuccess || n <= 0) { (void)cudaGetLastError(); n = 148 / S; }
+        mc = n;
+        cache[cache_n % 16] = {S, smem, n};
+        if (cache_n < 16) cache_n++;
+    }
+    int Gc = mc < p.ntiles ? mc : p.ntiles;
+    cfg.gridDim = dim3((unsigned)S, (unsigned)Gc, 1);
+    OB_CUDA(cudaLaunchKernelEx(&cfg, kern, map, p));
+    count_launch();
+    return ORTHO_B200_OK;
+}
+
+int launch_decode_stream(const FwdArgs &a)
+{
+    if (a.M > 16) return ORTHO_B200_ERR_SHAPE;
+    const int nboxes = (int)ceil_div(a.K, 256);
+    int S = g_stream_cfg[0], stages = g_stream_cfg[1];
+    if (S <= 0) {
+        // split K over the cluster until a warp has at most ~2 boxes per tile, and until the
+        // activation slab of a CTA fits comfortably
+        S = 1;
+        while (S < 8 && (nboxes > 16 * S || (size_t)a.M * (ceil_div(nboxes, S) * 512 + 64) > 96 * 1024)) S *= 2;
+    }
+    if (S > 8) S = 8;
+    if (stages <= 0) stages = 6;
+    const size_t xbytes = (size_t)a.M * (ceil_div(nboxes, S) * 512 + 64);
+    while (stages > 2 && (size_t)kWarps * stages * kBoxBytes + xbytes + 26 * 1024 > 227 * 1024) stages--;
+
+    CUtensorMap map;
+    if (!make_tensor_map_2d(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.w, (uint64_t)a.N, (uint64_t)(a.K / 2),
+                            (uint64_t)(a.K / 2), 16, 128, CU_TENSOR_MAP_SWIZZLE_128B))
+        return ORTHO_B200_ERR_CUDA;
+    if (a.M <= 8) return launch_stream_mt<1>(a, map, S, stages);
+    return launch_stream_mt<2>(a, map, S, stages);
+}
+
+}  // namespace ob
