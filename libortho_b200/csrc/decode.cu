@@ -358,7 +358,8 @@ int launch_decode(const FwdArgs &a)
 {
     if (a.M > ORTHO_B200_DECODE_MAX_M) return ORTHO_B200_ERR_SHAPE;
     // M <= 16: persistent TMA streaming kernel, unless the generic tiling was asked for explicitly
-    if (a.M <= 16 && (g_force_stream || g_override.wr == 0)) return launch_decode_stream(a);
+    // (its TMA view needs whole 128-byte column blocks per row: K a multiple of 256)
+    if (a.M <= 16 && (a.K % 256) == 0 && (g_force_stream || g_override.wr == 0)) return launch_decode_stream(a);
     const DecodeCfg c = choose(a.M, a.K, a.N);
     if (a.M <= 8) return launch_mt<1>(a, c);
     if (a.M <= 16) return launch_mt<2>(a, c);

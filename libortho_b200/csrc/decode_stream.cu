@@ -4,7 +4,7 @@
 // FP32 epilogue, ortho term from packed entries), but organised around memory-level parallelism:
 //
 //  * the packed INT4 base is fetched by TMA (cp.async.bulk.tensor.2d, 128-byte swizzle) in boxes of
-//    16 rows x 128 bytes (256 weights per row); every warp owns a private ring of such boxes with
+//    16 rows x 256 bytes (512 weights per row); every warp owns a private ring of such boxes with
 //    one mbarrier per slot and keeps `stages` boxes in flight, across tile boundaries;
 //  * a cluster of S CTAs (8 warps each) owns a 16-row output tile; the K range is split over the
 //    8*S warps.  Clusters are persistent and walk the tiles round-robin; the activation slab of a
@@ -26,19 +26,20 @@
 
 namespace ob {
 
-constexpr int kBoxBytes = 16 * 128;   // one TMA box: 16 rows x 128 packed bytes
+constexpr int kKbx = 2;                       // 128-byte column blocks per TMA box
+constexpr int kBoxBytes = 16 * kKbx * 128;    // one TMA box: 16 rows x kKbx x 128 packed bytes
+constexpr int kBoxK = 256 * kKbx;             // weights per row in one box
 constexpr int kWarps = 8;
 
 struct StreamParams {
     const __half *scales; const __half *x; __half *y;
     OrthoView ov; int has_ortho; float alpha;
     int M, K, N;
-    int nboxes;    // ceil(K / 256)
+    int nboxes;    // ceil(K / kBoxK)
     int ntiles;    // ceil(N / 16)
     int pitch;     // bytes between token rows of the staged activation slab
     int stages;    // ring depth per warp
     int *status;   // device word: set to 1 if a bounded wait gave up
-    int dbg;
 };
 
 __device__ __forceinline__ uint32_t prmt_b32(uint32_t a, uint32_t b, uint32_t sel) {
@@ -66,15 +67,25 @@ __device__ __forceinline__ float butterfly_reduce(float (&v)[V], int lane)
         off >>= 1;
     }
     float r = v[0];
-    for (; off >= 1; off >>= 1) r += __shfl_xor_sync(0xffffffffu, r, off);
+#pragma unroll
+    for (int o2 = 16; o2 >= 1; o2 >>= 1)
+        if (o2 <= off) r += __shfl_xor_sync(0xffffffffu, r, o2);
     return r;
 }
 
-template <int MT>
-__global__ void __launch_bounds__(kWarps * 32, 1)
+
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// MV = token slots kept per output row (M <= MV, power of two).  One CTA = 8 warps that split the
+// CTA's K range of a 16-row tile; a cluster of S CTAs splits K further.
+template <int MV>
+__global__ void __launch_bounds__(kWarps * 32, (MV <= 8) ? 3 : 2)
 decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParams p)
 {
-    constexpr int TOK = 8 * MT;
+    constexpr int MT = (MV + 7) / 8;              // mma n=8 token blocks
+    constexpr int NCH = 2;                        // independent accumulator chains
+    constexpr int LPG = 32 / MV;                  // lanes per token index after the butterfly
     extern __shared__ __align__(1024) unsigned char smem[];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -88,9 +99,10 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
     // the 128-byte TMA swizzle is a function of the shared-memory address: ring slots sit on 1 KB
     unsigned char *ring = smem + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);    // kWarps * stages * 2 KB
     uint64_t *bars = reinterpret_cast<uint64_t *>(ring + (size_t)kWarps * p.stages * kBoxBytes);
-    float *red = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(bars) + ((kWarps * p.stages * 8 + 127) & ~127));
-    float *osm = red + 2 * kWarps * 16 * TOK;                                     // [2][16*TOK]
-    unsigned char *xs = reinterpret_cast<unsigned char *>(osm + 2 * 16 * TOK);    // M * pitch
+    uint64_t *tbar = bars + kWarps * p.stages;                                    // tile barrier (S == 1)
+    float *red = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(bars) + (((kWarps * p.stages + 1) * 8 + 127) & ~127));
+    float *osm = red + 2 * kWarps * 16 * MV;                                      // [2][16*MV]
+    unsigned char *xs = reinterpret_cast<unsigned char *>(osm + 2 * 16 * MV);     // M * pitch
 
     // ---- this warp's share of the K range, in boxes of 256 weights -----------------------------
     const int cb0 = (p.nboxes * rank) / S, cb1 = (p.nboxes * (rank + 1)) / S;
@@ -98,24 +110,31 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
     const int nbw = wb1 - wb0;
     const int nt = (p.ntiles - cid + G - 1) / G;          // tiles walked by this cluster
     const int total = nt * nbw;                           // boxes this warp consumes
-    const int k_lo = cb0 * 256, k_hi = min(cb1 * 256, K); // activation slab of this CTA
+    const int k_lo = cb0 * kBoxK, k_hi = min(cb1 * kBoxK, K); // activation slab of this CTA
 
     unsigned char *my_ring = ring + (size_t)warp * p.stages * kBoxBytes;
     uint64_t *my_bars = bars + warp * p.stages;
 
-    auto issue = [&](int idx) {   // lane 0 only
-        const int ti = idx / nbw, bi = idx - ti * nbw;
-        const int st = idx % p.stages;
-        mbar_arrive_expect_tx(&my_bars[st], kBoxBytes);
-        tma_load_2d(my_ring + (size_t)st * kBoxBytes, &wmap, &my_bars[st], (wb0 + bi) * 128, (cid + ti * G) * 16);
+    // producer cursor (meaningful in lane 0): next box to fetch = (tile i_ti, box i_bi) into slot i_st.
+    // All ring indices advance by increment-and-wrap; there is no division in the steady state.
+    int i_ti = 0, i_bi = 0, i_st = 0, i_left = total;
+    auto issue = [&]() {   // lane 0 only
+        mbar_arrive_expect_tx(&my_bars[i_st], kBoxBytes);
+        tma_load_3d(my_ring + (size_t)i_st * kBoxBytes, &wmap, &my_bars[i_st], 0, (wb0 + i_bi) * kKbx, (cid + i_ti * G) * 16);
+        if (++i_bi == nbw) { i_bi = 0; ++i_ti; }
+        if (++i_st == p.stages) i_st = 0;
+        --i_left;
     };
 
+    // weights and the sparse structure are constants of the layer: they are prefetched before the
+    // grid dependency is resolved; activations are only touched after griddep_wait()
     if (lane == 0) {
         prefetch_tensormap(&wmap);
         for (int s = 0; s < p.stages; s++) mbar_init(&my_bars[s], 1);
+        if (warp == 0) mbar_init(tbar, kWarps * 32);
         fence_mbar_init();
         const int pre = min(p.stages, total);
-        for (int i = 0; i < pre; i++) issue(i);
+        for (int i = 0; i < pre; i++) issue();
     }
 
     // ---- sparse stream prologue: row pointers of the first two tiles, entries of the first ------
@@ -151,11 +170,13 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
         load_ent(rp_cur, ent);
     }
 
+    griddep_wait();
+
     // ---- stage X[:, k_lo:k_hi) once, in unpack pair order ---------------------------------------
     // 16-byte chunk (x0..x7) is stored as (x0,x4,x1,x5,x2,x6,x3,x7); inside a 128-element step the 16
     // chunks are laid out [j][t] so that the 4 lanes of a row group read 64 contiguous bytes.
     {
-        const int chunks_per_row = (cb1 - cb0) * 32;
+        const int chunks_per_row = (cb1 - cb0) * (kBoxK / 8);
         const int totalc = M * chunks_per_row;
         for (int idx = tid; idx < totalc; idx += kWarps * 32) {
             const int r = idx / chunks_per_row, q = idx - r * chunks_per_row;
@@ -172,36 +193,64 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
         }
     }
     __syncthreads();
+    griddep_launch();
 
-    // box rows are permuted so that the two rows met in one shared-memory phase differ in bit 2 of
-    // (row & 7): mma row g <-> box row rho(g); with the 128-byte swizzle every phase is conflict free
-    const int brow0 = (g >> 1) | ((g & 1) << 2), brow1 = brow0 + 8;
-    const uint32_t sw0 = (uint32_t)(brow0 & 7), sw1 = (uint32_t)(brow1 & 7);
+    // A box is laid out [row][column block][128 B]; the 128-byte swizzle XORs the 16-byte chunk index
+    // with bits 7..9 of the shared-memory address, i.e. with (row * kKbx + block) & 7.  mma row g is
+    // mapped to box row rho(g) = g with bits 0 and 1 swapped, so that the two rows met in one
+    // shared-memory phase (g = 2q, 2q+1) differ in bit 2 of that XOR term: every phase is conflict free.
+    const int brow0 = (g & 4) | ((g & 1) << 1) | ((g >> 1) & 1), brow1 = brow0 + 8;
+    // token row read by this lane for the mma column g of block mt.  Columns >= M are never stored,
+    // and mma columns are independent, so those lanes may read any valid row: clamp, no predicate.
+    const unsigned char *xrow[MT];
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++) xrow[mt] = xs + (size_t)min(8 * mt + g, M - 1) * p.pitch + t * 16;
+
+    // split-phase tile barrier: mbarrier inside one CTA, hardware cluster barrier across CTAs
+    auto tile_arrive = [&]() { if (S == 1) mbar_arrive(tbar); else cluster_arrive(); };
+    auto tile_wait = [&](int ti) -> bool {
+        if (S == 1) return mbar_wait(tbar, (uint32_t)(ti & 1));
+        cluster_wait();
+        return true;
+    };
 
     bool dead = false;
-    int idx = 0;
-    constexpr int NCH = (MT == 1) ? 4 : 2;   // independent accumulator chains per token block
+    int c_st = 0;              // consumer cursor: ring slot and its phase parity
+    uint32_t c_ph = 0;
     float acc[NCH][MT][4];
-    uint32_t dummy = 0;
 
+    // element of a tile finalized by this thread (fixed for the whole kernel)
+    const int RB = 16 / S;
+    const bool fin_on = tid < RB * M;
+    const int fin_m = fin_on ? tid / RB : 0;
+    const int fin_i = rank * RB + (fin_on ? tid - fin_m * RB : 0);
+
+    // the row scale a finalizing thread needs is fetched one tile early, so that the finalize of
+    // tile i (executed while tile i+1 is in flight) never waits on global memory
+    float sc_prev = 0.f;
     auto finalize = [&](int ti) {
         const int buf = ti & 1;
-        const int RB = 16 / S;
-        const int n_el = RB * M;
-        const uint32_t red_base = smem_u32(red + (size_t)buf * kWarps * 16 * TOK);
-        const uint32_t osm_base = smem_u32(osm + (size_t)buf * 16 * TOK);
-        for (int e = tid; e < n_el; e += kWarps * 32) {
-            const int m = e / RB, i = rank * RB + (e - m * RB);
+        if (fin_on) {
+            const int m = fin_m, i = fin_i;
             const int n = (cid + ti * G) * 16 + i;
             if (n < N) {
+                const uint32_t red_base = smem_u32(red + (size_t)buf * kWarps * 16 * MV);
+                const uint32_t osm_base = smem_u32(osm + (size_t)buf * 16 * MV);
                 float s = 0.f, o = 0.f;
-                for (int r2 = 0; r2 < S; r2++) {
-                    const uint32_t rb = mapa_shared(red_base, (uint32_t)r2);
+                if (S == 1) {
+                    const float *rb = red + (size_t)buf * kWarps * 16 * MV + i * MV + m;
 #pragma unroll
-                    for (int w = 0; w < kWarps; w++) s += ld_dsmem_f32(rb + (uint32_t)((w * 16 * TOK + i * TOK + m) * 4));
-                    if (p.has_ortho) o += ld_dsmem_f32(mapa_shared(osm_base, (uint32_t)r2) + (uint32_t)((i * TOK + m) * 4));
+                    for (int w = 0; w < kWarps; w++) s += rb[w * 16 * MV];
+                    if (p.has_ortho) o = osm[(size_t)buf * 16 * MV + i * MV + m];
+                } else {
+                    for (int r2 = 0; r2 < S; r2++) {
+                        const uint32_t rb = mapa_shared(red_base, (uint32_t)r2);
+#pragma unroll
+                        for (int w = 0; w < kWarps; w++) s += ld_dsmem_f32(rb + (uint32_t)((w * 16 * MV + i * MV + m) * 4));
+                        if (p.has_ortho) o += ld_dsmem_f32(mapa_shared(osm_base, (uint32_t)r2) + (uint32_t)((i * MV + m) * 4));
+                    }
                 }
-                float v = __half2float(p.scales[n]) * s;
+                float v = sc_prev * s;
                 if (p.has_ortho) v = fmaf(p.alpha, o, v);
                 p.y[(size_t)m * N + n] = __float2half_rn(v);
             }
@@ -209,12 +258,17 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
     };
 
     for (int ti = 0; ti < nt; ti++) {
+        float sc_new = 0.f;
+        if (fin_on) {
+            const int n = (cid + ti * G) * 16 + fin_i;
+            if (n < N) sc_new = __half2float(p.scales[n]);
+        }
 #pragma unroll
         for (int c = 0; c < NCH; c++)
 #pragma unroll
             for (int i = 0; i < MT; i++) { acc[c][i][0] = acc[c][i][1] = acc[c][i][2] = acc[c][i][3] = 0.f; }
 
-        // sparse stream, pipeline stage A/B: row pointers two tiles ahead, entries one tile ahead
+        // sparse stream, pipeline stages A/B: row pointers two tiles ahead, entries one tile ahead
         int rp_fut[2][2] = {{0, 0}, {0, 0}};
         uint32_t ent_nxt[2][2] = {{0, 0}, {0, 0}};
         if (p.has_ortho) {
@@ -223,22 +277,21 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
         }
 
         // ---- base: consume this warp's boxes of the tile ---------------------------------------
-        for (int bi = 0; bi < nbw; bi++, idx++) {
-            const int st = idx % p.stages;
-            const uint32_t ph = (uint32_t)((idx / p.stages) & 1);
-            if (!dead && !mbar_wait(&my_bars[st], ph)) { dead = true; if (lane == 0) atomicExch(p.status, 1); }
-            const unsigned char *box = my_ring + (size_t)st * kBoxBytes;
-            const int sl_base = (wb0 + bi - cb0) * 2;
-            if (p.dbg == 3) { dummy ^= *reinterpret_cast<const uint32_t *>(box + lane * 64); }
-            else
+        for (int bi = 0; bi < nbw; bi++) {
+            if (!mbar_try_wait(&my_bars[c_st], c_ph)) {
+                if (!dead && !mbar_wait(&my_bars[c_st], c_ph)) { dead = true; if (lane == 0) atomicExch(p.status, 1); }
+            }
+            const unsigned char *box = my_ring + (size_t)c_st * kBoxBytes;
+            if (++c_st == p.stages) { c_st = 0; c_ph ^= 1u; }
+            const int xoff = (wb0 + bi - cb0) * (kBoxK * 2);
 #pragma unroll
-            for (int s2 = 0; s2 < 2; s2++) {
-                const uint32_t c = (uint32_t)(4 * s2 + t);
-                const uint4 wa = *reinterpret_cast<const uint4 *>(box + brow0 * 128 + ((c ^ sw0) << 4));
-                const uint4 wb = *reinterpret_cast<const uint4 *>(box + brow1 * 128 + ((c ^ sw1) << 4));
+            for (int s2 = 0; s2 < 2 * kKbx; s2++) {
+                const uint32_t c = (uint32_t)(4 * (s2 & 1) + t);
+                const int line0 = brow0 * kKbx + (s2 >> 1), line1 = brow1 * kKbx + (s2 >> 1);
+                const uint4 wa = *reinterpret_cast<const uint4 *>(box + line0 * 128 + ((c ^ (uint32_t)(line0 & 7)) << 4));
+                const uint4 wb = *reinterpret_cast<const uint4 *>(box + line1 * 128 + ((c ^ (uint32_t)(line1 & 7)) << 4));
                 const uint32_t wwa[4] = {wa.x, wa.y, wa.z, wa.w};
                 const uint32_t wwb[4] = {wb.x, wb.y, wb.z, wb.w};
-                const int sl = sl_base + s2;
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
                     uint32_t ha[4], hb[4];
@@ -248,24 +301,14 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
                     const uint32_t A1[4] = {ha[2], hb[2], ha[3], hb[3]};
 #pragma unroll
                     for (int mt = 0; mt < MT; mt++) {
-                        const int tok = 8 * mt + g;
-                        uint4 xb = make_uint4(0, 0, 0, 0);
-                        if (tok < M)
-                            xb = *reinterpret_cast<const uint4 *>(xs + (size_t)tok * p.pitch + sl * 256 + j * 64 + t * 16);
-                        if (p.dbg == 1) {
-                            dummy ^= A0[0] ^ A0[1] ^ A0[2] ^ A0[3] ^ A1[0] ^ A1[1] ^ A1[2] ^ A1[3] ^ xb.x ^ xb.y ^ xb.z ^ xb.w;
-                        } else if (p.dbg == 2) {
-                            mma_16816(acc[0][mt], A0, xb.x, xb.y);
-                            mma_16816(acc[0][mt], A1, xb.z, xb.w);
-                        } else {
-                            mma_16816(acc[(2 * j) % NCH][mt], A0, xb.x, xb.y);
-                            mma_16816(acc[(2 * j + 1) % NCH][mt], A1, xb.z, xb.w);
-                        }
+                        const uint4 xb = *reinterpret_cast<const uint4 *>(xrow[mt] + xoff + s2 * 256 + j * 64);
+                        mma_16816(acc[0][mt], A0, xb.x, xb.y);
+                        mma_16816(acc[1][mt], A1, xb.z, xb.w);
                     }
                 }
             }
             __syncwarp();
-            if (lane == 0 && idx + p.stages < total) issue(idx + p.stages);
+            if (lane == 0 && i_left > 0) issue();
         }
 
         // ---- sparse stream, stage C: this tile's rows from the prefetched entries ---------------
@@ -273,9 +316,9 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
         if (p.has_ortho) {
 #pragma unroll
             for (int r = 0; r < 2; r++) {
-                float a[TOK];
+                float a[MV];
 #pragma unroll
-                for (int m = 0; m < TOK; m++) a[m] = 0.f;
+                for (int m = 0; m < MV; m++) a[m] = 0.f;
                 const int e0 = rp_cur[r][0], e1 = rp_cur[r][1];
                 auto apply = [&](uint32_t pk) {
                     const int c = (int)(pk & 0xFFFFu);
@@ -286,44 +329,45 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
                         const int sl = q >> 4, c16 = q & 15;
                         const unsigned char *px = xs + sl * 256 + (c16 & 3) * 64 + (c16 >> 2) * 16 + (((e & 3) << 1) | (e >> 2)) * 2;
 #pragma unroll
-                        for (int m = 0; m < TOK; m++)
-                            if (m < M) a[m] = fmaf(v, __half2float(*reinterpret_cast<const __half *>(px + (size_t)m * p.pitch)), a[m]);
+                        for (int m = 0; m < MV; m++) {
+                            const int mm = (MV == 1) ? 0 : min(m, M - 1);   // slots >= M are never stored
+                            a[m] = fmaf(v, __half2float(*reinterpret_cast<const __half *>(px + (size_t)mm * p.pitch)), a[m]);
+                        }
                     }
                 };
                 if (e0 + lane < e1) apply(ent[r][0]);
                 if (e0 + 32 + lane < e1) apply(ent[r][1]);
                 for (int e = e0 + 64 + lane; e < e1; e += 32) apply(load_entry(e));
-                osum[r] = butterfly_reduce<TOK>(a, lane);
+                osum[r] = butterfly_reduce<MV>(a, lane);
             }
         }
 
         // ---- deferred exchange: finish the previous tile, then publish this one -----------------
-        if (ti > 0) { cluster_wait(); finalize(ti - 1); }
+        if (ti > 0) {
+            if (!tile_wait(ti - 1) && !dead) { dead = true; if (lane == 0) atomicExch(p.status, 1); }
+            finalize(ti - 1);
+        }
         {
-            float *mine = red + ((size_t)(ti & 1) * kWarps + warp) * 16 * TOK;
+            float *mine = red + ((size_t)(ti & 1) * kWarps + warp) * 16 * MV;
 #pragma unroll
             for (int mt = 0; mt < MT; mt++) {
-                const int col = 8 * mt + 2 * t;
-                float r[4];
 #pragma unroll
-                for (int q = 0; q < 4; q++) {
-                    r[q] = acc[0][mt][q];
-#pragma unroll
-                    for (int c = 1; c < NCH; c++) r[q] += acc[c][mt][q];
+                for (int q = 0; q < 2; q++) {
+                    const int col = 8 * mt + 2 * t + q;
+                    if (col < MV) {
+                        mine[brow0 * MV + col] = acc[0][mt][q] + acc[1][mt][q];
+                        mine[brow1 * MV + col] = acc[0][mt][2 + q] + acc[1][mt][2 + q];
+                    }
                 }
-                *reinterpret_cast<float2 *>(mine + brow0 * TOK + col) = make_float2(r[0], r[1]);
-                *reinterpret_cast<float2 *>(mine + brow1 * TOK + col) = make_float2(r[2], r[3]);
             }
-            if (p.has_ortho) {
-                constexpr int SH = (TOK == 8) ? 2 : 1;          // lanes per token-index group: 32 / TOK
-                if ((lane & ((1 << SH) - 1)) == 0) {
-                    float *o = osm + (size_t)(ti & 1) * 16 * TOK;
-                    o[(warp)*TOK + (lane >> SH)] = osum[0];
-                    o[(warp + 8) * TOK + (lane >> SH)] = osum[1];
-                }
+            if (p.has_ortho && (lane & (LPG - 1)) == 0) {
+                float *o = osm + (size_t)(ti & 1) * 16 * MV;
+                o[warp * MV + lane / LPG] = osum[0];
+                o[(warp + 8) * MV + lane / LPG] = osum[1];
             }
         }
-        cluster_arrive();
+        tile_arrive();
+        sc_prev = sc_new;
 
         if (p.has_ortho) {
 #pragma unroll
@@ -334,12 +378,10 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
             }
         }
     }
-    if (dummy == 0x12345u) atomicExch(p.status, 2);
-    cluster_wait();
+    if (!tile_wait(nt - 1) && !dead) { if (lane == 0) atomicExch(p.status, 1); }
     finalize(nt - 1);
     // nobody may leave while a peer can still read its shared memory
-    cluster_arrive();
-    cluster_wait();
+    if (S > 1) { cluster_arrive(); cluster_wait(); }
 }
 
 // ---- host ------------------------------------------------------------------------------------
@@ -348,42 +390,48 @@ int *kernel_status_word();   // api.cu
 static int g_stream_cfg[2] = {0, 0};   // {k_split, stages}; 0 = built-in choice
 void set_stream_config(int s, int stages) { g_stream_cfg[0] = s; g_stream_cfg[1] = stages; }
 
-template <int MT>
-static int launch_stream_mt(const FwdArgs &a, const CUtensorMap &map, int S, int stages)
+static size_t stream_smem_bytes(int MV, int64_t M, int boxes_per_cta, int stages)
 {
-    constexpr int TOK = 8 * MT;
+    return 1024 + (size_t)kWarps * stages * kBoxBytes + (((kWarps * stages + 1) * 8 + 127) & ~127) +
+           (size_t)2 * kWarps * 16 * MV * 4 + (size_t)2 * 16 * MV * 4 + (size_t)M * (boxes_per_cta * kBoxK * 2 + 64);
+}
+
+template <int MV>
+static int launch_stream_mv(const FwdArgs &a, const CUtensorMap &map, int S, int stages)
+{
     StreamParams p;
     p.scales = a.scales; p.x = a.x; p.y = a.y; p.ov = a.ortho; p.has_ortho = a.has_ortho; p.alpha = a.alpha;
     p.M = (int)a.M; p.K = (int)a.K; p.N = (int)a.N;
-    p.nboxes = (int)ceil_div(a.K, 256);
+    p.nboxes = (int)ceil_div(a.K, kBoxK);
     p.ntiles = (int)ceil_div(a.N, 16);
     const int boxes_per_cta = (int)ceil_div(p.nboxes, S);
-    p.pitch = boxes_per_cta * 512 + 64;
+    p.pitch = boxes_per_cta * kBoxK * 2 + 64;
     p.stages = stages;
     p.status = kernel_status_word();
-    { const char *e = getenv("ORTHO_B200_DBG"); p.dbg = e ? atoi(e) : 0; }
     if (!p.status) return ORTHO_B200_ERR_CUDA;
-    const size_t smem = 1024 + (size_t)kWarps * stages * kBoxBytes + ((kWarps * stages * 8 + 127) & ~127) +
-                        (size_t)2 * kWarps * 16 * TOK * 4 + (size_t)2 * 16 * TOK * 4 + (size_t)a.M * p.pitch;
+    const size_t smem = stream_smem_bytes(MV, a.M, boxes_per_cta, stages);
     if (smem > 227 * 1024) return ORTHO_B200_ERR_SHAPE;
-    auto kern = decode_stream_kernel<MT>;
+    auto kern = decode_stream_kernel<MV>;
     static bool attr_set = false;
     if (!attr_set) {
         OB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        OB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
         attr_set = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(kWarps * 32, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = a.stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = (unsigned)S;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    // programmatic dependent launch: this grid may start (and prefetch weights) while the previous
+    // kernel of the stream drains; the kernel waits for that kernel before touching activations
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     // persistent grid: as many clusters as can be co-resident, never more than there are tiles
     // (cached per cluster size and shared-memory footprint)
     static struct { int s; size_t smem; int n; } cache[16];
@@ -393,9 +441,11 @@ static int launch_stream_mt(const FwdArgs &a, const CUtensorMap &map, int S, int
         if (cache[i].s == S && cache[i].smem == smem) mc = cache[i].n;
     if (mc == 0) {
         cfg.gridDim = dim3((unsigned)S, 148, 1);
+        cfg.numAttrs = 1;
         int n = 0;
         cudaError_t e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
         if (e != cudaSuccess || n <= 0) { (void)cudaGetLastError(); n = 148 / S; }
+        cfg.numAttrs = 2;
         mc = n;
         cache[cache_n % 16] = {S, smem, n};
         if (cache_n < 16) cache_n++;
@@ -410,25 +460,29 @@ static int launch_stream_mt(const FwdArgs &a, const CUtensorMap &map, int S, int
 int launch_decode_stream(const FwdArgs &a)
 {
     if (a.M > 16) return ORTHO_B200_ERR_SHAPE;
-    const int nboxes = (int)ceil_div(a.K, 256);
+    const int nboxes = (int)ceil_div(a.K, kBoxK);
+    const int MV = a.M <= 1 ? 1 : a.M <= 2 ? 2 : a.M <= 4 ? 4 : a.M <= 8 ? 8 : 16;
     int S = g_stream_cfg[0], stages = g_stream_cfg[1];
     if (S <= 0) {
-        // split K over the cluster until a warp has at most ~2 boxes per tile, and until the
-        // activation slab of a CTA fits comfortably
+        // split K over the cluster until the activation slab of a CTA is at most 64 KB
         S = 1;
-        while (S < 8 && (nboxes > 16 * S || (size_t)a.M * (ceil_div(nboxes, S) * 512 + 64) > 96 * 1024)) S *= 2;
+        while (S < 8 && (size_t)a.M * (ceil_div(nboxes, S) * kBoxK * 2 + 64) > 64 * 1024) S *= 2;
     }
     if (S > 8) S = 8;
-    if (stages <= 0) stages = 6;
-    const size_t xbytes = (size_t)a.M * (ceil_div(nboxes, S) * 512 + 64);
-    while (stages > 2 && (size_t)kWarps * stages * kBoxBytes + xbytes + 26 * 1024 > 227 * 1024) stages--;
+    if (stages <= 0) stages = 2;
+    while (stages > 2 && stream_smem_bytes(MV, a.M, (int)ceil_div(nboxes, S), stages) > 227 * 1024) stages--;
 
     CUtensorMap map;
-    if (!make_tensor_map_2d(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.w, (uint64_t)a.N, (uint64_t)(a.K / 2),
-                            (uint64_t)(a.K / 2), 16, 128, CU_TENSOR_MAP_SWIZZLE_128B))
+    // [N][ceil(K/2 / 128)][128 B] view of the packed base; bytes past the end of a row read as zero
+    if (!make_tensor_map_rows_of_128B(&map, a.w, (uint64_t)a.N, (uint64_t)(a.K / 2), 16, kKbx))
         return ORTHO_B200_ERR_CUDA;
-    if (a.M <= 8) return launch_stream_mt<1>(a, map, S, stages);
-    return launch_stream_mt<2>(a, map, S, stages);
+    switch (MV) {
+        case 1: return launch_stream_mv<1>(a, map, S, stages);
+        case 2: return launch_stream_mv<2>(a, map, S, stages);
+        case 4: return launch_stream_mv<4>(a, map, S, stages);
+        case 8: return launch_stream_mv<8>(a, map, S, stages);
+        default: return launch_stream_mv<16>(a, map, S, stages);
+    }
 }
 
 }  // namespace ob

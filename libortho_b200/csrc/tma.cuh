@@ -43,6 +43,25 @@ inline bool make_tensor_map_2d(CUtensorMap *map, CUtensorMapDataType dt, int ele
               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Byte matrix [rows][row_bytes] (row pitch == row_bytes) viewed as [rows][row_bytes/128][128] so
+// that one box can span several 128-byte column blocks while keeping the 128-byte swizzle; box =
+// {128, col_blocks, box_rows}.  Requires row_bytes % 128 == 0 (the caller checks); column blocks
+// past the end of a row and rows past the end of the matrix are zero-filled by the hardware.
+inline bool make_tensor_map_rows_of_128B(CUtensorMap *map, const void *base, uint64_t rows, uint64_t row_bytes,
+                                         uint32_t box_rows, uint32_t col_blocks)
+{
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    if (row_bytes % 128 != 0) return false;
+    cuuint64_t gdim[3] = {128, row_bytes / 128, rows};
+    cuuint64_t gstr[2] = {128, row_bytes};
+    cuuint32_t box[3] = {128, col_blocks, box_rows};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(base), gdim, gstr, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // ---- device ------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -80,6 +99,12 @@ __device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *m
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *map, uint64_t *bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
         : "memory");
 }
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *map) {
