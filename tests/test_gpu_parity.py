@@ -217,3 +217,16 @@ def test_error_statuses_surface_as_exceptions():
                                        x.data_ptr(), y.data_ptr(), 2, 48, 32, 1.0, None, None, 0, None)
     assert st == 2
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("K,N,M", [(384, 200, 200), (1024, 272, 130), (4096, 512, 257), (64, 64, 65), (2048, 1024, 1024)])
+def test_tensor_core_path_base_only_against_oracle(oracle_mod, K, N, M):
+    """M > 64 takes the tcgen05 kernel.  alpha = 0: base term only, ragged tiles in M, N and K."""
+    layer = wl.make_layer(K, N, 0.01, seed=91)
+    x = wl.make_input(M, K, seed=91)
+    y = run_layer(layer.to(DEV), x.to(DEV), 0.0).float().cpu().numpy()
+    assert _lib.lib().ortho_b200_query_kernel_status() == 0
+    assert_close(y, layer_oracle(oracle_mod, layer, x, 0.0), f"prefill base {K}x{N} M={M}")
+    # the same rows through the streaming kernel (64-token calls) agree to FP16 rounding
+    y64 = run_layer(layer.to(DEV), x[:64].contiguous().to(DEV), 0.0).float().cpu().numpy()
+    assert np.abs(y[:64] - y64).max() <= 2e-2
