@@ -339,7 +339,7 @@ def bench_prefill(dev, pk):
     for M in wl.CFG2_M:
         x = wl.make_input(M, K, seed=M, device=dev)
         y = torch.empty(M, N, dtype=torch.float16, device=dev)
-        ws_bytes = _C_ops.workspace_bytes(M, K, N)
+        ws_bytes = _C_ops.workspace_bytes(M, K, N, plan)
         ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
         for alpha, tag in ((wl.CFG2_ALPHA, "fused"), (0.0, "base_only")):
             for _ in range(3):

@@ -116,6 +116,9 @@ ORTHO_B200_API int ortho_b200_dequant_dump(const void *q_weight, const void *q_s
 #define ORTHO_B200_DECODE_MAX_M 64
 
 ORTHO_B200_API int64_t ortho_b200_workspace_bytes(int64_t M, int64_t K, int64_t N);
+/* Workspace for forwards that pass this plan (its long rows are split into extra output slots, so it
+ * needs slightly more than the plan-less bound); 0 in the decode regime or for an empty plan. */
+ORTHO_B200_API int64_t ortho_b200_plan_workspace_bytes(const ortho_b200_plan *plan, int64_t M);
 
 ORTHO_B200_API int ortho_b200_forward(const void *q_weight, const void *q_scales_f16,
                        const void *ortho_values_f16, const int32_t *ortho_col_indices,

@@ -74,7 +74,9 @@ class Plan:
             pass
 
 
-def workspace_bytes(M: int, K: int, N: int) -> int:
+def workspace_bytes(M: int, K: int, N: int, plan: Optional["Plan"] = None) -> int:
+    if plan is not None:
+        return int(_lib.lib().ortho_b200_plan_workspace_bytes(plan.handle, M))
     return int(_lib.lib().ortho_b200_workspace_bytes(M, K, N))
 
 
@@ -121,7 +123,7 @@ def forward(q_weight: torch.Tensor, q_scales: torch.Tensor, ortho_values: torch.
             raise TypeError("ortho buffers must be float16 / int32 / int32")
         if ortho_row_ptr.numel() != N + 1 or ortho_col_indices.numel() != nnz:
             raise ValueError("CSR arrays have inconsistent sizes")
-    need = workspace_bytes(M, K, N) if (nnz and alpha > 0) else 0
+    need = workspace_bytes(M, K, N, plan) if (nnz and alpha > 0) else 0
     ws_ptr, ws_bytes = None, 0
     if need:
         if workspace is None or workspace.numel() * workspace.element_size() < need:

@@ -50,6 +50,8 @@ def _declare(l):
     l.ortho_b200_dequant_dump.argtypes = [vp, vp, i64, i64, vp, vp, vp]
     l.ortho_b200_workspace_bytes.restype = i64
     l.ortho_b200_workspace_bytes.argtypes = [i64, i64, i64]
+    l.ortho_b200_plan_workspace_bytes.restype = i64
+    l.ortho_b200_plan_workspace_bytes.argtypes = [vp, i64]
     l.ortho_b200_forward.restype = c.c_int
     l.ortho_b200_forward.argtypes = [vp, vp, vp, i32p, i32p, i64, vp, vp, i64, i64, i64, c.c_float,
                                      vp, vp, i64, vp]
@@ -66,7 +68,7 @@ EXPORTS = [
     "ortho_b200_strerror", "ortho_b200_version", "ortho_b200_last_cuda_error",
     "ortho_b200_plan_create", "ortho_b200_plan_destroy", "ortho_b200_plan_nnz",
     "ortho_b200_plan_max_row_nnz", "ortho_b200_plan_decode_dump", "ortho_b200_dequant_dump",
-    "ortho_b200_workspace_bytes", "ortho_b200_forward", "ortho_b200_set_decode_config",
+    "ortho_b200_workspace_bytes", "ortho_b200_plan_workspace_bytes", "ortho_b200_forward", "ortho_b200_set_decode_config",
     "ortho_b200_launch_count", "ortho_b200_query_kernel_status",
 ]
 

@@ -34,7 +34,14 @@ struct Plan {
     uint32_t *entries;    // [nnz]
     int32_t *erow;        // [nnz]
     int32_t *tile_ptr;    // [ceil(N/128)+1]
+    // rows longer than kPlanHeavy entries are split into segments of at most kPlanSeg entries
+    // for the prefill SpMM: segment v covers entries [vbeg[v], vend[v]); long row h (h < n_long) is
+    // output row hrow[h] and owns segments [hptr[h], hptr[h+1]).  Built on the host at plan creation.
+    int64_t n_virtual, n_long;
+    int32_t *vbeg, *vend, *hrow, *hptr;
 };
+constexpr int kPlanHeavy = 128;
+constexpr int kPlanSeg = 128;
 constexpr uint32_t kPlanMagic = 0x0B200A17u;
 
 // view of the ortho component handed to kernels: either packed plan entries or raw CSR

@@ -8,6 +8,7 @@
 // entry range can be processed without a row search, and records the entry range of every
 // 128-row tile for the tensor-core kernel's epilogue.
 #include <new>
+#include <vector>
 
 #include "common.cuh"
 
@@ -111,6 +112,7 @@ extern "C" int ortho_b200_plan_create(ortho_b200_plan **plan_out, const int32_t 
     if (!pl) return ORTHO_B200_ERR_ALLOC;
     pl->magic = kPlanMagic; pl->K = K; pl->N = N; pl->nnz = nnz; pl->max_row_nnz = 0;
     pl->row_ptr = nullptr; pl->entries = nullptr; pl->erow = nullptr; pl->tile_ptr = nullptr;
+    pl->n_virtual = 0; pl->n_long = 0; pl->vbeg = nullptr; pl->vend = nullptr; pl->hrow = nullptr; pl->hptr = nullptr;
     cudaError_t e = cudaGetDevice(&pl->device);
     if (e != cudaSuccess) { note_cuda_error(e); delete pl; return ORTHO_B200_ERR_CUDA; }
     if (nnz > 0) {
@@ -143,6 +145,39 @@ extern "C" int ortho_b200_plan_create(ortho_b200_plan **plan_out, const int32_t 
             return ORTHO_B200_ERR_CUDA;
         }
         pl->max_row_nnz = h_max;
+        if (h_max > kPlanHeavy) {
+            // split the long rows into segments on the host (one pass over the row pointers)
+            std::vector<int32_t> rp((size_t)N + 1), vb, ve, hr, hp;
+            e = cudaMemcpy(rp.data(), row_ptr, sizeof(int32_t) * (N + 1), cudaMemcpyDeviceToHost);
+            if (e == cudaSuccess) {
+                for (int64_t n = 0; n < N; n++) {
+                    const int32_t b = rp[n], en = rp[n + 1];
+                    if (en - b <= kPlanHeavy) continue;
+                    hr.push_back((int32_t)n);
+                    hp.push_back((int32_t)vb.size());
+                    for (int32_t s0 = b; s0 < en; s0 += kPlanSeg) {
+                        vb.push_back(s0); ve.push_back(s0 + kPlanSeg < en ? s0 + kPlanSeg : en);
+                    }
+                }
+                hp.push_back((int32_t)vb.size());
+                const size_t nv = vb.size(), nl = hr.size();
+                e = cudaMalloc(&pl->vbeg, sizeof(int32_t) * nv);
+                if (e == cudaSuccess) e = cudaMalloc(&pl->vend, sizeof(int32_t) * nv);
+                if (e == cudaSuccess) e = cudaMalloc(&pl->hrow, sizeof(int32_t) * nl);
+                if (e == cudaSuccess) e = cudaMalloc(&pl->hptr, sizeof(int32_t) * (nl + 1));
+                if (e == cudaSuccess) e = cudaMemcpy(pl->vbeg, vb.data(), sizeof(int32_t) * nv, cudaMemcpyHostToDevice);
+                if (e == cudaSuccess) e = cudaMemcpy(pl->vend, ve.data(), sizeof(int32_t) * nv, cudaMemcpyHostToDevice);
+                if (e == cudaSuccess) e = cudaMemcpy(pl->hrow, hr.data(), sizeof(int32_t) * nl, cudaMemcpyHostToDevice);
+                if (e == cudaSuccess) e = cudaMemcpy(pl->hptr, hp.data(), sizeof(int32_t) * (nl + 1), cudaMemcpyHostToDevice);
+                pl->n_virtual = (int64_t)nv;
+                pl->n_long = (int64_t)nl;
+            }
+            if (e != cudaSuccess) {
+                note_cuda_error(e);
+                ortho_b200_plan_destroy(reinterpret_cast<ortho_b200_plan *>(pl));
+                return ORTHO_B200_ERR_CUDA;
+            }
+        }
     }
     *plan_out = reinterpret_cast<ortho_b200_plan *>(pl);
     return ORTHO_B200_OK;
@@ -157,6 +192,10 @@ extern "C" int ortho_b200_plan_destroy(ortho_b200_plan *plan)
     if (pl->entries) cudaFree(pl->entries);
     if (pl->erow) cudaFree(pl->erow);
     if (pl->tile_ptr) cudaFree(pl->tile_ptr);
+    if (pl->vbeg) cudaFree(pl->vbeg);
+    if (pl->vend) cudaFree(pl->vend);
+    if (pl->hrow) cudaFree(pl->hrow);
+    if (pl->hptr) cudaFree(pl->hptr);
     pl->magic = 0;
     delete pl;
     return ORTHO_B200_OK;
@@ -172,6 +211,14 @@ extern "C" int64_t ortho_b200_plan_max_row_nnz(const ortho_b200_plan *plan)
 {
     const Plan *pl = reinterpret_cast<const Plan *>(plan);
     return (pl && pl->magic == kPlanMagic) ? pl->max_row_nnz : -1;
+}
+
+extern "C" int64_t ortho_b200_plan_workspace_bytes(const ortho_b200_plan *plan, int64_t M)
+{
+    const Plan *pl = reinterpret_cast<const Plan *>(plan);
+    if (!pl || pl->magic != kPlanMagic) return -1;
+    if (M <= ORTHO_B200_DECODE_MAX_M || pl->nnz == 0) return 0;
+    return prefill_workspace_bytes(M, pl->K, pl->N + pl->n_virtual);
 }
 
 extern "C" int ortho_b200_plan_decode_dump(const ortho_b200_plan *plan, int32_t *rows_out, int32_t *cols_out,

@@ -8,18 +8,21 @@
 //     y[m, n] = scale[n] * D[n, m]  (+ alpha * ortho[m, n])
 //
 // The weight tile is the M operand of the MMA and lives in TENSOR MEMORY: TMA brings the packed
-// INT4 bytes of 128 output rows x 64 k into shared memory, four converter warps (one thread per
+// INT4 bytes (128 bytes = 256 k per row and load) into shared memory, converter warps (one thread per
 // output row) unpack them in registers to exact small-integer halves and write them with
 // tcgen05.st, so the converted weights never touch shared memory.  The token tile (128 tokens x
 // 64 k, FP16, 128-byte swizzle) is the N operand and goes from global to shared memory by TMA and
-// from there straight into the MMA.  One elected thread issues the MMAs; accumulators are double
-// buffered in TMEM (2 x 128 columns) so that the epilogue of a tile runs while the next tile is
-// being accumulated.  The per-row scale is applied in the FP32 epilogue (it factors out of the K
-// sum, src/ortho.c:356,363), outputs are transposed through shared memory and stored coalesced.
+// from there straight into the MMA.  A tile is 256 output rows x 128 tokens: two accumulators of
+// 128 rows share every token stage, which halves the shared-memory fill per flop (the token tile is
+// by far the larger operand) and doubles the time one ring slot covers.  One elected thread issues
+// the MMAs.  The per-row scale is applied in the FP32 epilogue (it factors out of the K sum,
+// src/ortho.c:356,363); outputs are transposed through shared memory and stored coalesced.
 //
+// TMEM columns: [0,256) two accumulators, [256,512) ring of 4 converted weight stages.
 // Warp roles (CTA = 1 SM, persistent over tiles):
-//   warp 0      TMA producer          warp 1      MMA issuer, TMEM allocator
-//   warps 2-5   INT4 -> FP16 -> TMEM  warps 6-9   epilogue (TMEM -> scale -> FP16 -> global)
+//   warp 0       TMA producer           warp 1       MMA issuer, TMEM allocator
+//   warps 2-9    INT4 -> FP16 -> TMEM (one thread per output row of the tile)
+//   warps 10-17  epilogue (TMEM -> scale -> FP16 -> global), one set of 4 warps per accumulator
 #include "common.cuh"
 #include "umma.cuh"
 
@@ -29,33 +32,46 @@ int launch_decode(const FwdArgs &a);
 int *kernel_status_word();
 
 namespace pf {
-constexpr int TN = 128;            // output rows per tile   (MMA M)
-constexpr int TM = 128;            // tokens per tile        (MMA N)
+constexpr int TH = 128;            // output rows per MMA (one TMEM accumulator, MMA M)
+constexpr int NH = 1;              // accumulators per tile that share one token tile
+constexpr int TN = TH * NH;        // output rows per tile
+constexpr int TM = 256;            // tokens per tile        (MMA N)
 constexpr int KB = 64;             // k per pipeline stage
-constexpr int STAGES = 6;
+constexpr int STAGES = 5;
 constexpr int ASTAGES = 4;
 constexpr int X_BYTES = TM * KB * 2;     // 16 KB
-constexpr int W_BYTES = TN * KB / 2;     // 4 KB
-constexpr int YS_PITCH = TN + 8;         // halves per staged token row (pad against bank conflicts)
-constexpr int NWARPS = 10;
+constexpr int WKB = 4;                   // k-blocks covered by one packed-weight load (128 bytes per row)
+constexpr int WSTAGES = 2;
+constexpr int W_BYTES = TN * 128;        // 32 KB: 256 rows x 128 B (256 k), 128-byte swizzle
+constexpr int YS_PITCH = TH + 8;         // halves per staged token row (pad against bank conflicts)
+constexpr int YS_BYTES = 32 * YS_PITCH * 2;
+constexpr int CONV_WARPS = 4 * NH;       // one converter thread per output row of the tile
+constexpr int EPI_WARP0 = 2 + CONV_WARPS;
+constexpr int EPI_WARPS = 4 * NH;        // one epilogue warp set per accumulator
+constexpr int NWARPS = EPI_WARP0 + EPI_WARPS;
 constexpr int TMEM_COLS = 512;
-constexpr int A_COL0 = 2 * TM;           // accumulators occupy [0, 2*TM), converted weights follow
+constexpr int A_COL0 = NH * TM;          // accumulators occupy [0, NH*TM); converted weights follow
+constexpr int A_STAGE_COLS = NH * (KB / 2);
 
 struct Params {
     const __half *scales; __half *y;
     int M, K, N;
     int tiles_n, tiles_m, kblocks;
     int *status;
+    // sparse term computed ahead by spmm_ortho_kernel: O[n][m] FP32 with row pitch Mp (rows without
+    // entries are never written and never read)
+    const int32_t *row_ptr; const float *o; int Mp; float alpha; int has_ortho;
 };
 
 struct Smem {
     uint64_t x_full[STAGES], x_empty[STAGES];
+    uint64_t w_full[WSTAGES], w_empty[WSTAGES];
     uint64_t a_full[ASTAGES], a_empty[ASTAGES];
-    uint64_t d_full[2], d_empty[2];
+    uint64_t d_full, d_empty;
     uint32_t tmem_base;
 };
 
-constexpr size_t kSmemBytes = 1024 + (size_t)STAGES * (X_BYTES + W_BYTES) + 32 * YS_PITCH * 2 + sizeof(Smem) + 256;
+constexpr size_t kSmemBytes = 1024 + (size_t)STAGES * X_BYTES + (size_t)WSTAGES * W_BYTES + NH * YS_BYTES + sizeof(Smem) + 256;
 }  // namespace pf
 
 __global__ void __launch_bounds__(pf::NWARPS * 32, 1)
@@ -65,17 +81,19 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char *base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     unsigned char *xs = base;                                       // STAGES x 16 KB, 1 KB aligned
-    unsigned char *ws = xs + (size_t)STAGES * X_BYTES;              // STAGES x 4 KB
-    __half *ys = reinterpret_cast<__half *>(ws + (size_t)STAGES * W_BYTES);
-    Smem *sm = reinterpret_cast<Smem *>(reinterpret_cast<unsigned char *>(ys) + 32 * YS_PITCH * 2);
+    unsigned char *ws = xs + (size_t)STAGES * X_BYTES;              // WSTAGES x 32 KB, 1 KB aligned
+    unsigned char *ys_base = ws + (size_t)WSTAGES * W_BYTES;        // NH staging tiles for the transposed store
+    Smem *sm = reinterpret_cast<Smem *>(ys_base + NH * YS_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ntiles = p.tiles_n * p.tiles_m;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; s++) { mbar_init(&sm->x_full[s], 1); mbar_init(&sm->x_empty[s], 1 + 4); }
-        for (int s = 0; s < ASTAGES; s++) { mbar_init(&sm->a_full[s], 4); mbar_init(&sm->a_empty[s], 1); }
-        for (int b = 0; b < 2; b++) { mbar_init(&sm->d_full[b], 1); mbar_init(&sm->d_empty[b], 4); }
+        for (int s = 0; s < STAGES; s++) { mbar_init(&sm->x_full[s], 1); mbar_init(&sm->x_empty[s], 1); }
+        for (int s = 0; s < WSTAGES; s++) { mbar_init(&sm->w_full[s], 1); mbar_init(&sm->w_empty[s], CONV_WARPS); }
+        for (int s = 0; s < ASTAGES; s++) { mbar_init(&sm->a_full[s], CONV_WARPS); mbar_init(&sm->a_empty[s], 1); }
+        mbar_init(&sm->d_full, 1);
+        mbar_init(&sm->d_empty, EPI_WARPS);
         fence_mbar_init();
         prefetch_tensormap(&xmap);
         prefetch_tensormap(&wmap);
@@ -94,14 +112,19 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     if (warp == 0) {
         // ================= TMA producer =================
         if (lane == 0) {
-            int s = 0; uint32_t ph = 0;
+            int s = 0, wsi = 0; uint32_t ph = 0, wph = 0;
             for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
                 const int nt = t % p.tiles_n, mt = t / p.tiles_n;
                 for (int kb = 0; kb < p.kblocks; kb++) {
+                    if ((kb % WKB) == 0) {      // packed weights: one 128-byte-wide load per WKB k-blocks
+                        wait(&sm->w_empty[wsi], wph ^ 1u);
+                        mbar_arrive_expect_tx(&sm->w_full[wsi], W_BYTES);
+                        tma_load_2d(ws + (size_t)wsi * W_BYTES, &wmap, &sm->w_full[wsi], kb * (KB / 2), nt * TN);
+                        if (++wsi == WSTAGES) { wsi = 0; wph ^= 1u; }
+                    }
                     wait(&sm->x_empty[s], ph ^ 1u);
-                    mbar_arrive_expect_tx(&sm->x_full[s], X_BYTES + W_BYTES);
+                    mbar_arrive_expect_tx(&sm->x_full[s], X_BYTES);
                     tma_load_2d(xs + (size_t)s * X_BYTES, &xmap, &sm->x_full[s], kb * KB, mt * TM);
-                    tma_load_2d(ws + (size_t)s * W_BYTES, &wmap, &sm->x_full[s], kb * (KB / 2), nt * TN);
                     if (++s == STAGES) { s = 0; ph ^= 1u; }
                 }
             }
@@ -109,87 +132,120 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     } else if (warp == 1) {
         // ================= MMA issuer =================
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc_f16(TN, TM);
+            const uint32_t idesc = umma_idesc_f16(TH, TM);
+            const uint64_t desc0 = umma_desc_sw128(smem_u32(xs));     // stage s, k step kk: + s*X_BYTES/16 + 2*kk
             int s = 0, as = 0; uint32_t ph = 0, aph = 0;
             int it = 0;
             for (int t = blockIdx.x; t < ntiles; t += gridDim.x, it++) {
-                const int b = it & 1;
-                wait(&sm->d_empty[b], (uint32_t)(((it >> 1) & 1) ^ 1));
+                wait(&sm->d_empty, (uint32_t)((it & 1) ^ 1));     // the epilogue has drained the accumulators
                 tc_fence_after();
-                const uint32_t d_tmem = tmem + (uint32_t)(b * TM);
                 for (int kb = 0; kb < p.kblocks; kb++) {
                     wait(&sm->x_full[s], ph);
                     wait(&sm->a_full[as], aph);
                     tc_fence_after();
-                    const uint32_t a_tmem = tmem + (uint32_t)(A_COL0 + as * (KB / 2));
-                    const uint32_t xaddr = smem_u32(xs + (size_t)s * X_BYTES);
+                    const uint32_t a_tmem = tmem + (uint32_t)(A_COL0 + as * A_STAGE_COLS);
+                    const uint64_t bdesc = desc0 + (uint64_t)(s * (X_BYTES >> 4));
+                    const uint32_t acc0 = (uint32_t)(kb != 0);
 #pragma unroll
-                    for (int kk = 0; kk < KB / 16; kk++)
-                        umma_f16_ts(d_tmem, a_tmem + (uint32_t)(kk * 8), umma_desc_sw128(xaddr + (uint32_t)(kk * 32)), idesc,
-                                    (uint32_t)((kb | kk) != 0));
+                    for (int kk = 0; kk < KB / 16; kk++) {
+#pragma unroll
+                        for (int h = 0; h < NH; h++)
+                            umma_f16_ts(tmem + (uint32_t)(h * TM), a_tmem + (uint32_t)(h * (KB / 2) + kk * 8),
+                                        bdesc + (uint64_t)(2 * kk), idesc, kk == 0 ? acc0 : 1u);
+                    }
                     umma_commit(&sm->x_empty[s]);
                     umma_commit(&sm->a_empty[as]);
                     if (++s == STAGES) { s = 0; ph ^= 1u; }
                     if (++as == ASTAGES) { as = 0; aph ^= 1u; }
                 }
-                umma_commit(&sm->d_full[b]);
+                umma_commit(&sm->d_full);
             }
         }
-    } else if (warp < 6) {
+    } else if (warp < EPI_WARP0) {
         // ================= converters: packed INT4 (smem) -> FP16 (TMEM, A operand) =================
         const int q = warp & 3;                        // TMEM lane quarter this warp may touch
-        const int row = q * 32 + lane;                 // output row inside the tile == TMEM lane
-        int s = 0, as = 0; uint32_t ph = 0, aph = 0;
+        const int h = (warp - 2) >> 2;                 // which accumulator's rows
+        const int row = h * TH + q * 32 + lane;        // output row inside the tile
+        int wsi = 0, as = 0; uint32_t wph = 0, aph = 0;
+        const uint32_t swz = (uint32_t)(row & 7);      // 128-byte swizzle: 16-byte chunk c sits at c ^ (row & 7)
         for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
             for (int kb = 0; kb < p.kblocks; kb++) {
-                wait(&sm->x_full[s], ph);
-                const uint4 *wrow = reinterpret_cast<const uint4 *>(ws + (size_t)s * W_BYTES + row * (KB / 2));
-                const uint4 w0 = wrow[0], w1 = wrow[1];
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&sm->x_empty[s]);
-                uint32_t h[32];
+                const int sub = kb % WKB;                   // which 32-byte slice of the 128-byte weight row
+                if (sub == 0) wait(&sm->w_full[wsi], wph);
+                const unsigned char *wrow = ws + (size_t)wsi * W_BYTES + row * 128;
+                const uint4 w0 = *reinterpret_cast<const uint4 *>(wrow + ((((uint32_t)(2 * sub)) ^ swz) << 4));
+                const uint4 w1 = *reinterpret_cast<const uint4 *>(wrow + ((((uint32_t)(2 * sub + 1)) ^ swz) << 4));
+                if (sub == WKB - 1 || kb == p.kblocks - 1) {   // last slice of this weight stage: hand it back
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sm->w_empty[wsi]);
+                    if (++wsi == WSTAGES) { wsi = 0; wph ^= 1u; }
+                }
+                uint32_t hreg[32];
                 const uint32_t ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
                     uint32_t o[4];
                     int4x8_to_half2x4_natural(ww[j], o);
-                    h[4 * j] = o[0]; h[4 * j + 1] = o[1]; h[4 * j + 2] = o[2]; h[4 * j + 3] = o[3];
+                    hreg[4 * j] = o[0]; hreg[4 * j + 1] = o[1]; hreg[4 * j + 2] = o[2]; hreg[4 * j + 3] = o[3];
                 }
                 wait(&sm->a_empty[as], aph ^ 1u);
                 tc_fence_after();
-                tmem_st_32x32b_x32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(A_COL0 + as * (KB / 2)), h);
+                tmem_st_32x32b_x32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(A_COL0 + as * A_STAGE_COLS + h * (KB / 2)), hreg);
                 tmem_st_wait();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sm->a_full[as]);
-                if (++s == STAGES) { s = 0; ph ^= 1u; }
                 if (++as == ASTAGES) { as = 0; aph ^= 1u; }
             }
         }
     } else {
         // ================= epilogue: TMEM -> scale -> FP16 -> shared (transpose) -> global =================
         const int q = warp & 3;
-        const int et = (warp - 6) * 32 + lane;         // 0..127 among the epilogue threads
+        const int h = (warp - EPI_WARP0) >> 2;         // accumulator handled by this warp set
+        const int et = ((warp - EPI_WARP0) & 3) * 32 + lane;   // 0..127 inside the set
+        __half *ys = reinterpret_cast<__half *>(ys_base + h * YS_BYTES);
         const bool vec_ok = (p.N % 8) == 0;
         int it = 0;
         for (int t = blockIdx.x; t < ntiles; t += gridDim.x, it++) {
             const int nt = t % p.tiles_n, mt = t / p.tiles_n;
-            const int b = it & 1;
-            const int n = nt * TN + q * 32 + lane;
+            const int nbase = nt * TN + h * TH;
+            const int n = nbase + q * 32 + lane;
             const float sc = (n < p.N) ? __half2float(p.scales[n]) : 0.f;
-            wait(&sm->d_full[b], (uint32_t)((it >> 1) & 1));
+            const float *orow = nullptr;               // this row's sparse term, if it has any entries
+            if (p.has_ortho && n < p.N && p.row_ptr[n + 1] > p.row_ptr[n]) orow = p.o + (size_t)n * p.Mp + mt * TM;
+            // the sparse term of a chunk is fetched one chunk ahead (the first one before the
+            // accumulator is even complete), so its latency never sits in the exposed epilogue
+            float4 ov[8];
+            auto load_o = [&](int c) {
+                const float4 *o4 = reinterpret_cast<const float4 *>(orow + c * 32);
+#pragma unroll
+                for (int j4 = 0; j4 < 8; j4++) ov[j4] = o4[j4];
+            };
+            if (orow) load_o(0);
+            wait(&sm->d_full, (uint32_t)(it & 1));
             tc_fence_after();
             for (int c = 0; c < TM / 32; c++) {
                 uint32_t r[32];
-                tmem_ld_32x32b_x32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * TM + c * 32), r);
+                tmem_ld_32x32b_x32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(h * TM + c * 32), r);
                 tmem_ld_wait();
+                if (orow) {                            // y = scale * D + alpha * O, one FP16 rounding
 #pragma unroll
-                for (int j = 0; j < 32; j++) ys[j * YS_PITCH + q * 32 + lane] = __float2half_rn(__uint_as_float(r[j]) * sc);
-                named_bar_sync(1, 128);
+                    for (int j4 = 0; j4 < 8; j4++) {
+                        ys[(4 * j4 + 0) * YS_PITCH + q * 32 + lane] = __float2half_rn(fmaf(p.alpha, ov[j4].x, __uint_as_float(r[4 * j4 + 0]) * sc));
+                        ys[(4 * j4 + 1) * YS_PITCH + q * 32 + lane] = __float2half_rn(fmaf(p.alpha, ov[j4].y, __uint_as_float(r[4 * j4 + 1]) * sc));
+                        ys[(4 * j4 + 2) * YS_PITCH + q * 32 + lane] = __float2half_rn(fmaf(p.alpha, ov[j4].z, __uint_as_float(r[4 * j4 + 2]) * sc));
+                        ys[(4 * j4 + 3) * YS_PITCH + q * 32 + lane] = __float2half_rn(fmaf(p.alpha, ov[j4].w, __uint_as_float(r[4 * j4 + 3]) * sc));
+                    }
+                    if (c + 1 < TM / 32) load_o(c + 1);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) ys[j * YS_PITCH + q * 32 + lane] = __float2half_rn(__uint_as_float(r[j]) * sc);
+                }
+                named_bar_sync(1 + h, 128);
 #pragma unroll
                 for (int i2 = 0; i2 < 4; i2++) {
                     const int id = i2 * 128 + et, tok = id >> 4, part = id & 15;
-                    const int m = mt * TM + c * 32 + tok, n0 = nt * TN + part * 8;
+                    const int m = mt * TM + c * 32 + tok, n0 = nbase + part * 8;
                     if (m < p.M && n0 < p.N) {
                         const __half *src = ys + tok * YS_PITCH + part * 8;
                         __half *dst = p.y + (size_t)m * p.N + n0;
@@ -200,11 +256,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                         }
                     }
                 }
-                named_bar_sync(1, 128);
+                named_bar_sync(1 + h, 128);
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&sm->d_empty[b]);
+            if (lane == 0) mbar_arrive(&sm->d_empty);
         }
     }
 
@@ -213,19 +269,31 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
 }
 
-int64_t prefill_workspace_bytes(int64_t, int64_t, int64_t) { return 0; }
+int64_t spmm_workspace_bytes(int64_t M, int64_t K, int64_t N);            // spmm.cu
+int launch_spmm(const FwdArgs &a, const float **o_out, int *mp_out);
 
-static int launch_prefill_base(const FwdArgs &a)
+int64_t prefill_workspace_bytes(int64_t M, int64_t K, int64_t N) { return spmm_workspace_bytes(M, K, N); }
+
+int launch_prefill(const FwdArgs &a)
 {
     using namespace pf;
+    Params p;
+    p.row_ptr = nullptr; p.o = nullptr; p.Mp = 0; p.alpha = a.alpha; p.has_ortho = 0;
+    if (a.has_ortho) {
+        // sparse term first (transpose + SpMM into the workspace), added in the tensor-core epilogue
+        if (ceil_div(a.M, 64) > 65535) return ORTHO_B200_ERR_SHAPE;
+        int st = launch_spmm(a, &p.o, &p.Mp);
+        if (st != ORTHO_B200_OK) return st;
+        p.row_ptr = a.ortho.row_ptr;
+        p.has_ortho = 1;
+    }
     CUtensorMap xmap, wmap;
     if (!make_tensor_map_2d(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.x, (uint64_t)a.M, (uint64_t)a.K,
                             (uint64_t)a.K * 2, TM, KB, CU_TENSOR_MAP_SWIZZLE_128B))
         return ORTHO_B200_ERR_CUDA;
     if (!make_tensor_map_2d(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.w, (uint64_t)a.N, (uint64_t)(a.K / 2),
-                            (uint64_t)(a.K / 2), TN, KB / 2, CU_TENSOR_MAP_SWIZZLE_NONE))
+                            (uint64_t)(a.K / 2), TN, 128, CU_TENSOR_MAP_SWIZZLE_128B))
         return ORTHO_B200_ERR_CUDA;
-    Params p;
     p.scales = a.scales; p.y = a.y; p.M = (int)a.M; p.K = (int)a.K; p.N = (int)a.N;
     p.tiles_n = (int)ceil_div(a.N, TN); p.tiles_m = (int)ceil_div(a.M, TM); p.kblocks = (int)ceil_div(a.K, KB);
     p.status = kernel_status_word();
@@ -244,21 +312,6 @@ static int launch_prefill_base(const FwdArgs &a)
     prefill_kernel<<<grid, NWARPS * 32, kSmemBytes, a.stream>>>(xmap, wmap, p);
     count_launch();
     OB_CUDA(cudaGetLastError());
-    return ORTHO_B200_OK;
-}
-
-int launch_prefill(const FwdArgs &a)
-{
-    if (!a.has_ortho) return launch_prefill_base(a);
-    // sparse term not yet fused on the tensor-core path: token chunks through the streaming kernel
-    for (int64_t m0 = 0; m0 < a.M; m0 += ORTHO_B200_DECODE_MAX_M) {
-        FwdArgs b = a;
-        b.M = (a.M - m0 < ORTHO_B200_DECODE_MAX_M) ? (a.M - m0) : ORTHO_B200_DECODE_MAX_M;
-        b.x = a.x + m0 * a.K;
-        b.y = a.y + m0 * a.N;
-        int st = launch_decode(b);
-        if (st != ORTHO_B200_OK) return st;
-    }
     return ORTHO_B200_OK;
 }
 

@@ -119,7 +119,7 @@ class OrthoLinear(nn.Module):
     def _get_workspace(self, M: int) -> Optional[torch.Tensor]:
         if self.alpha <= 0 or self.ortho_values.numel() == 0:
             return None
-        need = _C.workspace_bytes(M, self.in_features, self.out_features)
+        need = _C.workspace_bytes(M, self.in_features, self.out_features, self._get_plan())
         if need == 0:
             return None
         if (self._workspace is None or self._workspace.numel() < need

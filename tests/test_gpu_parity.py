@@ -230,3 +230,32 @@ def test_tensor_core_path_base_only_against_oracle(oracle_mod, K, N, M):
     # the same rows through the streaming kernel (64-token calls) agree to FP16 rounding
     y64 = run_layer(layer.to(DEV), x[:64].contiguous().to(DEV), 0.0).float().cpu().numpy()
     assert np.abs(y[:64] - y64).max() <= 2e-2
+
+
+@pytest.mark.parametrize("kind,K,N,M,d,alpha,plan", [
+    ("zipf", 2048, 384, 300, 0.02, 0.5, True),      # rows longer than the SpMM's cooperative threshold
+    ("zipf", 2048, 384, 300, 0.02, 0.5, False),     # same through raw CSR (no plan)
+    ("gauss", 1024, 520, 129, 0.01, 1.0, True),
+    ("gauss", 4096, 256, 513, 0.003, 0.25, True),
+])
+def test_tensor_core_path_with_sparse_term_against_oracle(oracle_mod, kind, K, N, M, d, alpha, plan):
+    layer = wl.make_layer(K, N, d, seed=93, ortho=kind)
+    x = wl.make_input(M, K, seed=93)
+    if kind == "zipf":
+        assert int((layer.row_ptr[1:] - layer.row_ptr[:-1]).max()) > 512
+    y = run_layer(layer.to(DEV), x.to(DEV), alpha, plan=plan).float().cpu().numpy()
+    assert _lib.lib().ortho_b200_query_kernel_status() == 0
+    assert_close(y, layer_oracle(oracle_mod, layer, x, alpha), f"prefill fused {kind} {K}x{N} M={M}")
+    # alpha = 0 on the same layer is bit-identical to the layer without any entries
+    y0 = run_layer(layer.to(DEV), x.to(DEV), 0.0, plan=plan)
+    empty = wl.Layer(K, N, layer.base_weight.to(DEV), layer.base_scales.to(DEV),
+                     torch.zeros(N + 1, dtype=torch.int32, device=DEV), layer.col[:0].to(DEV), layer.vals[:0].to(DEV), 1.0)
+    assert torch.equal(y0, run_layer(empty, x.to(DEV), 1.0))
+    # a missing workspace is an error status, not a silent fallback
+    with pytest.raises(_lib.OrthoB200Error, match="workspace"):
+        ld = layer.to(DEV)
+        yy = torch.empty(M, N, dtype=torch.float16, device=DEV)
+        st = _lib.lib().ortho_b200_forward(ld.base_weight.data_ptr(), ld.base_scales.data_ptr(), ld.vals.data_ptr(),
+                                           ld.col.data_ptr(), ld.row_ptr.data_ptr(), ld.nnz, x.to(DEV).data_ptr(),
+                                           yy.data_ptr(), M, K, N, alpha, None, None, 0, None)
+        _lib.check(st, "ortho_b200_forward")
