@@ -157,13 +157,10 @@ def run_ours(args):
     items = sweep_items()
     # ---- build N_COPIES sets of (sharded) layers, plans and output buffers ------------------
     sets = []
-    full_bytes = 0
     for c in range(N_COPIES):
         layers = {}
         for (K, N) in wl.CFG1_SHAPES:
             L = wl.make_layer(K, N, wl.CFG1_DENSITY, seed=c, device=dev)
-            if c == 0:
-                pass
             if world > 1:
                 n0, n1 = N * rank // world, N * (rank + 1) // world
                 full = L
@@ -179,7 +176,7 @@ def run_ours(args):
     step_bytes = sum(sets[0][(K, N)][0]._full_bytes[M] for (K, N, M) in items)
     xs = {(K, M): wl.make_input(M, K, seed=M, device=dev) for (K, N, M) in items}
     ys = {(K, N, M): torch.empty(M, sets[0][(K, N)][0].N, dtype=torch.float16, device=dev) for (K, N, M) in items}
-    yg = {(K, N, M): torch.empty(world, M, sets[0][(K, N)][0].N, dtype=torch.float16, device=dev)
+    yg = {(K, N, M): torch.empty(world * M, sets[0][(K, N)][0].N, dtype=torch.float16, device=dev)
           for (K, N, M) in items} if world > 1 else None
 
     def run_step(c):
@@ -241,7 +238,7 @@ def run_ours(args):
             y = mods[c][(K, N)](xd)
             if world > 1:
                 dist.all_gather_into_tensor(yg[(K, N, M)], y)
-                hy[(K, N, M)].copy_(yg[(K, N, M)].permute(1, 0, 2).reshape(M, -1), non_blocking=True)
+                hy[(K, N, M)].copy_(yg[(K, N, M)].view(world, M, -1).permute(1, 0, 2).reshape(M, -1), non_blocking=True)
             else:
                 hy[(K, N, M)].copy_(y, non_blocking=True)
         torch.cuda.current_stream().synchronize()

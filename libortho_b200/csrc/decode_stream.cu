@@ -26,16 +26,15 @@
 
 namespace ob {
 
-constexpr int kKbx = 2;                       // 128-byte column blocks per TMA box
-constexpr int kBoxBytes = 16 * kKbx * 128;    // one TMA box: 16 rows x kKbx x 128 packed bytes
-constexpr int kBoxK = 256 * kKbx;             // weights per row in one box
+// One TMA box is 16 rows x KBX column blocks of 128 packed bytes (KBX is a kernel template
+// parameter: 2 for M <= 8, 1 for M = 9..16 where the activation slab limits the K range per CTA).
 constexpr int kWarps = 8;
 
 struct StreamParams {
     const __half *scales; const __half *x; __half *y;
     OrthoView ov; int has_ortho; float alpha;
     int M, K, N;
-    int nboxes;    // ceil(K / kBoxK)
+    int nboxes;    // ceil(K / weights per box row)
     int ntiles;    // ceil(N / 16)
     int pitch;     // bytes between token rows of the staged activation slab
     int stages;    // ring depth per warp
@@ -79,10 +78,13 @@ __device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.
 
 // MV = token slots kept per output row (M <= MV, power of two).  One CTA = 8 warps that split the
 // CTA's K range of a 16-row tile; a cluster of S CTAs splits K further.
-template <int MV>
+template <int MV, int KBX>
 __global__ void __launch_bounds__(kWarps * 32, (MV <= 8) ? 3 : 2)
 decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParams p)
 {
+    constexpr int kKbx = KBX;
+    constexpr int kBoxBytes = 16 * KBX * 128;
+    constexpr int kBoxK = 256 * KBX;
     constexpr int MT = (MV + 7) / 8;              // mma n=8 token blocks
     constexpr int NCH = 2;                        // independent accumulator chains
     constexpr int LPG = 32 / MV;                  // lanes per token index after the butterfly
@@ -198,8 +200,10 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
     // A box is laid out [row][column block][128 B]; the 128-byte swizzle XORs the 16-byte chunk index
     // with bits 7..9 of the shared-memory address, i.e. with (row * kKbx + block) & 7.  mma row g is
     // mapped to box row rho(g) = g with bits 0 and 1 swapped, so that the two rows met in one
-    // shared-memory phase (g = 2q, 2q+1) differ in bit 2 of that XOR term: every phase is conflict free.
-    const int brow0 = (g & 4) | ((g & 1) << 1) | ((g >> 1) & 1), brow1 = brow0 + 8;
+    // shared-memory phase (g = 2q, 2q+1) differ in bit 2 of that XOR term: every phase is conflict free
+    // (for one column block per box the XOR term is row & 7 and rho rotates the low three bits instead).
+    const int brow0 = (KBX == 2) ? ((g & 4) | ((g & 1) << 1) | ((g >> 1) & 1)) : ((g >> 1) | ((g & 1) << 2));
+    const int brow1 = brow0 + 8;
     // token row read by this lane for the mma column g of block mt.  Columns >= M are never stored,
     // and mma columns are independent, so those lanes may read any valid row: clamp, no predicate.
     const unsigned char *xrow[MT];
@@ -390,15 +394,16 @@ int *kernel_status_word();   // api.cu
 static int g_stream_cfg[2] = {0, 0};   // {k_split, stages}; 0 = built-in choice
 void set_stream_config(int s, int stages) { g_stream_cfg[0] = s; g_stream_cfg[1] = stages; }
 
-static size_t stream_smem_bytes(int MV, int64_t M, int boxes_per_cta, int stages)
+static size_t stream_smem_bytes(int MV, int kbx, int64_t M, int boxes_per_cta, int stages)
 {
-    return 1024 + (size_t)kWarps * stages * kBoxBytes + (((kWarps * stages + 1) * 8 + 127) & ~127) +
-           (size_t)2 * kWarps * 16 * MV * 4 + (size_t)2 * 16 * MV * 4 + (size_t)M * (boxes_per_cta * kBoxK * 2 + 64);
+    return 1024 + (size_t)kWarps * stages * (16 * kbx * 128) + (((kWarps * stages + 1) * 8 + 127) & ~127) +
+           (size_t)2 * kWarps * 16 * MV * 4 + (size_t)2 * 16 * MV * 4 + (size_t)M * (boxes_per_cta * 512 * kbx + 64);
 }
 
-template <int MV>
+template <int MV, int KBX>
 static int launch_stream_mv(const FwdArgs &a, const CUtensorMap &map, int S, int stages)
 {
+    constexpr int kBoxK = 256 * KBX;
     StreamParams p;
     p.scales = a.scales; p.x = a.x; p.y = a.y; p.ov = a.ortho; p.has_ortho = a.has_ortho; p.alpha = a.alpha;
     p.M = (int)a.M; p.K = (int)a.K; p.N = (int)a.N;
@@ -409,9 +414,9 @@ static int launch_stream_mv(const FwdArgs &a, const CUtensorMap &map, int S, int
     p.stages = stages;
     p.status = kernel_status_word();
     if (!p.status) return ORTHO_B200_ERR_CUDA;
-    const size_t smem = stream_smem_bytes(MV, a.M, boxes_per_cta, stages);
+    const size_t smem = stream_smem_bytes(MV, KBX, a.M, boxes_per_cta, stages);
     if (smem > 227 * 1024) return ORTHO_B200_ERR_SHAPE;
-    auto kern = decode_stream_kernel<MV>;
+    auto kern = decode_stream_kernel<MV, KBX>;
     static bool attr_set = false;
     if (!attr_set) {
         OB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
@@ -460,28 +465,30 @@ static int launch_stream_mv(const FwdArgs &a, const CUtensorMap &map, int S, int
 int launch_decode_stream(const FwdArgs &a)
 {
     if (a.M > 16) return ORTHO_B200_ERR_SHAPE;
-    const int nboxes = (int)ceil_div(a.K, kBoxK);
     const int MV = a.M <= 1 ? 1 : a.M <= 2 ? 2 : a.M <= 4 ? 4 : a.M <= 8 ? 8 : 16;
+    const int kbx = (MV <= 8) ? 2 : 1;
+    const int nboxes = (int)ceil_div(a.K, 256 * kbx);
     int S = g_stream_cfg[0], stages = g_stream_cfg[1];
     if (S <= 0) {
-        // split K over the cluster until the activation slab of a CTA is at most 64 KB
+        // one CTA per tile covers all of K when its activation slab fits; otherwise split K over the
+        // smallest cluster that does
         S = 1;
-        while (S < 8 && (size_t)a.M * (ceil_div(nboxes, S) * kBoxK * 2 + 64) > 64 * 1024) S *= 2;
+        while (S < 8 && stream_smem_bytes(MV, kbx, a.M, (int)ceil_div(nboxes, S), 2) > 200 * 1024) S *= 2;
     }
     if (S > 8) S = 8;
     if (stages <= 0) stages = 2;
-    while (stages > 2 && stream_smem_bytes(MV, a.M, (int)ceil_div(nboxes, S), stages) > 227 * 1024) stages--;
+    while (stages > 2 && stream_smem_bytes(MV, kbx, a.M, (int)ceil_div(nboxes, S), stages) > 227 * 1024) stages--;
 
+    // [N][K/2 / 128][128 B] view of the packed base; blocks past the end of a row read as zero
     CUtensorMap map;
-    // [N][ceil(K/2 / 128)][128 B] view of the packed base; bytes past the end of a row read as zero
-    if (!make_tensor_map_rows_of_128B(&map, a.w, (uint64_t)a.N, (uint64_t)(a.K / 2), 16, kKbx))
+    if (!make_tensor_map_rows_of_128B(&map, a.w, (uint64_t)a.N, (uint64_t)(a.K / 2), 16, (uint32_t)kbx))
         return ORTHO_B200_ERR_CUDA;
     switch (MV) {
-        case 1: return launch_stream_mv<1>(a, map, S, stages);
-        case 2: return launch_stream_mv<2>(a, map, S, stages);
-        case 4: return launch_stream_mv<4>(a, map, S, stages);
-        case 8: return launch_stream_mv<8>(a, map, S, stages);
-        default: return launch_stream_mv<16>(a, map, S, stages);
+        case 1: return launch_stream_mv<1, 2>(a, map, S, stages);
+        case 2: return launch_stream_mv<2, 2>(a, map, S, stages);
+        case 4: return launch_stream_mv<4, 2>(a, map, S, stages);
+        case 8: return launch_stream_mv<8, 2>(a, map, S, stages);
+        default: return launch_stream_mv<16, 1>(a, map, S, stages);
     }
 }
 
