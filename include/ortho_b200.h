@@ -51,7 +51,8 @@ enum {
     ORTHO_B200_ERR_CUDA = 6,        /* a CUDA call failed; see ortho_b200_last_cuda_error()        */
     ORTHO_B200_ERR_DEVICE = 7,      /* the current device is not compute capability 10.x           */
     ORTHO_B200_ERR_KERNEL = 8,      /* a kernel reported a bounded wait that ran out               */
-    ORTHO_B200_ERR_ALLOC = 9        /* host or device allocation failed                            */
+    ORTHO_B200_ERR_ALLOC = 9,       /* host or device allocation failed                            */
+    ORTHO_B200_ERR_SCRATCH_LIMIT = 10 /* needs more scratch than ORTHO_B200_STATIC_SCRATCH_BYTES   */
 };
 
 /* Replaces: the 0 / -1 convention of the reference C API (include/ortho.h:76-79,132-135). */
@@ -127,6 +128,38 @@ ORTHO_B200_API int ortho_b200_forward(const void *q_weight, const void *q_scales
                        int64_t M, int64_t K, int64_t N, float alpha,
                        const ortho_b200_plan *plan,
                        void *workspace, int64_t workspace_bytes, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Forward for callers that cannot allocate device memory.  It has no counterpart in the reference.
+ *
+ * Who needs it: code that runs where cudaMalloc must not be called -- a host application that owns
+ * the allocator and hands a plugin only tensors, a serving loop whose memory was fixed at start-up,
+ * or a section that is about to be recorded into a CUDA graph.  ortho_b200_forward asks such a
+ * caller for a workspace when M > ORTHO_B200_DECODE_MAX_M and the sparse term is active, and a
+ * plan has to be allocated too.  This entry point takes neither: it reads the CSR arrays directly
+ * and keeps the scratch (transposed activations + FP32 sparse term) in a fixed array of
+ * ORTHO_B200_STATIC_SCRATCH_BYTES that is part of the library image.  Every GPU that loads the
+ * library holds that array until the process exits.
+ *
+ * Limits and rules:
+ *  - if ortho_b200_workspace_bytes(M, K, N) exceeds ORTHO_B200_STATIC_SCRATCH_BYTES the call returns
+ *    ORTHO_B200_ERR_SCRATCH_LIMIT and launches nothing (M <= ORTHO_B200_DECODE_MAX_M, alpha <= 0 or
+ *    nnz == 0 need no scratch and are never rejected for size);
+ *  - the first call on a device looks up the array's device address (cudaGetSymbolAddress, no
+ *    allocation); make that first call before any stream capture begins;
+ *  - all calls share the one array and it keeps the previous call's contents.  Nothing in it needs
+ *    clearing (each call writes every byte it later reads), but calls that overlap on the GPU --
+ *    other streams, other host threads -- race on it: issue them one after another on one stream;
+ *  - no cudaMalloc / cudaFree or any other allocating call is made.
+ * Arguments as for ortho_b200_forward, without plan and workspace.
+ * ------------------------------------------------------------------------------------------- */
+#define ORTHO_B200_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)
+
+ORTHO_B200_API int ortho_b200_forward_static_scratch(const void *q_weight, const void *q_scales_f16,
+                       const void *ortho_values_f16, const int32_t *ortho_col_indices,
+                       const int32_t *ortho_row_ptr, int64_t nnz,
+                       const void *x_f16, void *y_f16,
+                       int64_t M, int64_t K, int64_t N, float alpha, void *stream);
 
 /* Synchronises the device and reports whether any kernel of this library gave up on a bounded
  * wait since the last query (ERR_KERNEL, and the flag is cleared) or not (OK).  Replaces the

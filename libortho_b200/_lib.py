@@ -55,6 +55,8 @@ def _declare(l):
     l.ortho_b200_forward.restype = c.c_int
     l.ortho_b200_forward.argtypes = [vp, vp, vp, i32p, i32p, i64, vp, vp, i64, i64, i64, c.c_float,
                                      vp, vp, i64, vp]
+    l.ortho_b200_forward_static_scratch.restype = c.c_int
+    l.ortho_b200_forward_static_scratch.argtypes = [vp, vp, vp, i32p, i32p, i64, vp, vp, i64, i64, i64, c.c_float, vp]
     l.ortho_b200_set_decode_config.restype = c.c_int
     l.ortho_b200_set_decode_config.argtypes = [c.c_int, c.c_int, c.c_int, c.c_int]
     l.ortho_b200_query_kernel_status.restype = c.c_int
@@ -69,7 +71,7 @@ EXPORTS = [
     "ortho_b200_plan_create", "ortho_b200_plan_destroy", "ortho_b200_plan_nnz",
     "ortho_b200_plan_max_row_nnz", "ortho_b200_plan_decode_dump", "ortho_b200_dequant_dump",
     "ortho_b200_workspace_bytes", "ortho_b200_plan_workspace_bytes", "ortho_b200_forward", "ortho_b200_set_decode_config",
-    "ortho_b200_launch_count", "ortho_b200_query_kernel_status",
+    "ortho_b200_launch_count", "ortho_b200_query_kernel_status", "ortho_b200_forward_static_scratch",
 ]
 
 

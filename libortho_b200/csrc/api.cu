@@ -66,6 +66,7 @@ extern "C" const char *ortho_b200_strerror(int status)
         case ORTHO_B200_ERR_DEVICE: return "current device is not a compute capability 10.x GPU";
         case ORTHO_B200_ERR_KERNEL: return "a kernel gave up on a bounded wait";
         case ORTHO_B200_ERR_ALLOC: return "allocation failed";
+        case ORTHO_B200_ERR_SCRATCH_LIMIT: return "this shape needs more scratch than the built-in ORTHO_B200_STATIC_SCRATCH_BYTES array holds";
         default: return "unknown status";
     }
 }
