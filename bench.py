@@ -243,7 +243,7 @@ def run_ours(args):
                 hy[(K, N, M)].copy_(y, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
-    for i in range(3):
+    for i in range(max(3, N_COPIES)):       # touches every weight set once: plans are built on first use
         e2e_step(i % N_COPIES)
     barrier()
     e2e_steps = max(3, min(args.steps, 20))
@@ -299,7 +299,15 @@ def run_ours(args):
             line["cpu_baseline"] = cpu_baseline()
         print(json.dumps(line))
     if world > 1:
-        dist.destroy_process_group()
+        # NCCL kernels live inside the captured graphs; tearing the communicator down while those
+        # graphs exist has hung at exit, so: drop the graphs, meet once more, and leave without the
+        # collective teardown
+        del graphs
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def time_forward_us(get_layer, x, y, stream, reps=2, replays=5):
