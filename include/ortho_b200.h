@@ -104,10 +104,10 @@ ORTHO_B200_API int ortho_b200_dequant_dump(const void *q_weight, const void *q_s
  * torch_bind/ortho_linear.py:142-151); same argument order and meaning, plus explicit sizes,
  * the optional plan, a caller-owned workspace and the stream.
  *
- *   M <= ORTHO_B200_DECODE_MAX_M : memory-bound streaming kernel (no workspace needed).
- *   larger M                     : tcgen05 / TMEM tensor-core kernel; needs
- *                                  ortho_b200_workspace_bytes(M, K, N) bytes of workspace when
- *                                  the ortho term is active, none otherwise.
+ *   M <= ORTHO_B200_DECODE_MAX_M : memory-bound streaming kernels.
+ *   larger M                     : tcgen05 / TMEM tensor-core kernel.
+ * Either regime needs ortho_b200_workspace_bytes(M, K, N) bytes of caller-owned workspace when the
+ * ortho term is active (alpha > 0 and nnz > 0), none otherwise.
  * plan may be NULL: the kernels then read the CSR arrays directly.  With a plan the CSR
  * pointers may be NULL.  alpha <= 0 or nnz == 0 skips the sparse stream entirely, so the output
  * is bit-identical to the base-only result (src/ortho.c:343 and the reference null test,
@@ -143,8 +143,8 @@ ORTHO_B200_API int ortho_b200_forward(const void *q_weight, const void *q_scales
  *
  * Limits and rules:
  *  - if ortho_b200_workspace_bytes(M, K, N) exceeds ORTHO_B200_STATIC_SCRATCH_BYTES the call returns
- *    ORTHO_B200_ERR_SCRATCH_LIMIT and launches nothing (M <= ORTHO_B200_DECODE_MAX_M, alpha <= 0 or
- *    nnz == 0 need no scratch and are never rejected for size);
+ *    ORTHO_B200_ERR_SCRATCH_LIMIT and launches nothing (alpha <= 0 or nnz == 0 need no scratch and are
+ *    never rejected for size);
  *  - the first call on a device looks up the array's device address (cudaGetSymbolAddress, no
  *    allocation); make that first call before any stream capture begins;
  *  - all calls share the one array and it keeps the previous call's contents.  Nothing in it needs
@@ -172,6 +172,7 @@ ORTHO_B200_API int ortho_b200_query_kernel_status(void);
  *                    k split over the cluster);
  *   row_groups == -1: streaming TMA kernel (M <= 16) with k_split CTAs per cluster and `unroll`
  *                    ring slots per warp (either may be 0 for the built-in choice);
+ *   row_groups == -2: tcgen05 decode kernel with k_split CTAs per cluster and `unroll` weight stages;
  *   row_groups == 0 : restore the built-in choice.
  * Returns ERR_SHAPE for an unsupported tuple. */
 ORTHO_B200_API int ortho_b200_set_decode_config(int row_groups, int k_groups, int unroll, int k_split);

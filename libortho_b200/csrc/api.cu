@@ -36,6 +36,8 @@ int *kernel_status_word()
     return cached;
 }
 
+int64_t decode_tc_workspace_bytes(int64_t M, int64_t N);   // decode_tc.cu
+
 static int check_device()
 {
     static thread_local int checked_device = -1;
@@ -96,7 +98,7 @@ extern "C" int ortho_b200_query_kernel_status(void)
 
 extern "C" int64_t ortho_b200_workspace_bytes(int64_t M, int64_t K, int64_t N)
 {
-    if (M <= ORTHO_B200_DECODE_MAX_M) return 0;
+    if (M <= ORTHO_B200_DECODE_MAX_M) return decode_tc_workspace_bytes(M, N);
     return prefill_workspace_bytes(M, K, N);
 }
 

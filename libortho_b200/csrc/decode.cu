@@ -258,11 +258,25 @@ decode_kernel(const DecodeParams p)
 struct DecodeCfg { int wr, wk, u, s; };
 static DecodeCfg g_override = {0, 0, 0, 0};
 static bool g_force_stream = false;
+static bool g_use_tc = false;                        // tcgen05 decode kernel: opt-in through the tuning hook (slower than the
+                                                     // streaming kernel on the benchmark shapes so far)
 int launch_decode_stream(const FwdArgs &a);          // decode_stream.cu
 void set_stream_config(int s, int stages);
+int launch_decode_tc(const FwdArgs &a);              // decode_tc.cu
+void set_tc_config(int s, int stages);
 
 int set_decode_config(int wr, int wk, int u, int s)
 {
+    if (wr == -2) {       // tcgen05 decode kernel with k_split = s CTAs per cluster and u weight stages (0 = built-in)
+        if (s < 0 || s > 8 || u < 0 || u > 8) return ORTHO_B200_ERR_SHAPE;
+        g_override = {0, 0, 0, 0};
+        g_force_stream = false;
+        g_use_tc = true;
+        set_tc_config(s, u);
+        return ORTHO_B200_OK;
+    }
+    g_use_tc = false;
+    set_tc_config(0, 0);
     if (wr == -1) {
         if ((s != 0 && s != 1 && s != 2 && s != 4 && s != 8) || u < 0 || u > 12 || u == 1) return ORTHO_B200_ERR_SHAPE;
         g_override = {0, 0, 0, 0};
@@ -357,6 +371,10 @@ static int launch_mt(const FwdArgs &a, const DecodeCfg &c)
 int launch_decode(const FwdArgs &a)
 {
     if (a.M > ORTHO_B200_DECODE_MAX_M) return ORTHO_B200_ERR_SHAPE;
+    if (g_use_tc) {
+        const int st = launch_decode_tc(a);
+        if (st != ORTHO_B200_ERR_SHAPE) return st;      // ERR_SHAPE: does not fit that kernel, use the others
+    }
     // M <= 16: persistent TMA streaming kernel, unless the generic tiling was asked for explicitly
     // (its TMA view needs whole 128-byte column blocks per row: K a multiple of 256)
     if (a.M <= 16 && (a.K % 256) == 0 && (g_force_stream || g_override.wr == 0)) return launch_decode_stream(a);

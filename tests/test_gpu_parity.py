@@ -259,3 +259,20 @@ def test_tensor_core_path_with_sparse_term_against_oracle(oracle_mod, kind, K, N
                                            ld.col.data_ptr(), ld.row_ptr.data_ptr(), ld.nnz, x.to(DEV).data_ptr(),
                                            yy.data_ptr(), M, K, N, alpha, None, None, 0, None)
         _lib.check(st, "ortho_b200_forward")
+
+
+@pytest.mark.parametrize("K,N,M,d,alpha,split", [(256, 128, 1, 0.0, 1.0, 1), (1024, 300, 16, 0.02, 1.0, 2),
+                                                  (4096, 1100, 5, 0.005, 0.5, 0), (11008, 512, 32, 0.005, 0.5, 0),
+                                                  (2048, 260, 20, 0.01, 1.0, 3)])
+def test_tcgen05_decode_kernel_against_oracle(oracle_mod, K, N, M, d, alpha, split):
+    """The opt-in tcgen05 decode kernel (weights converted into tensor memory, cluster split-K with a
+    distributed-shared-memory reduction) through the tuning hook."""
+    layer = wl.make_layer(K, N, d, seed=95)
+    x = wl.make_input(M, K, seed=95)
+    try:
+        assert _lib.lib().ortho_b200_set_decode_config(-2, 0, 0, split) == 0
+        y = run_layer(layer.to(DEV), x.to(DEV), alpha)
+    finally:
+        _lib.lib().ortho_b200_set_decode_config(0, 0, 0, 0)
+    assert _lib.lib().ortho_b200_query_kernel_status() == 0
+    assert_close(y.float().cpu().numpy(), layer_oracle(oracle_mod, layer, x, alpha), f"tc decode {K}x{N} M={M}")
