@@ -37,6 +37,9 @@ WORKLOAD = "decode sweep: (4096->12288, 4096->4096, 4096->22016, 11008->4096) x 
 N_COPIES = 6          # distinct weight sets rotated through (6 x ~100 MB >> 126 MB of L2)
 
 
+NCU_TRAFFIC_RATIO = 47.15 / 47.98    # measured DRAM traffic / algorithmic bytes of the captured decode launch
+
+
 def peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -143,6 +146,7 @@ def run_ours(args):
     import torch
     import torch.distributed as dist
     from libortho_b200 import _C_ops, _lib, workloads as wl
+    from libortho_b200.sharded import ShardedOrthoLinear, shard_bounds
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -162,7 +166,7 @@ def run_ours(args):
         for (K, N) in wl.CFG1_SHAPES:
             L = wl.make_layer(K, N, wl.CFG1_DENSITY, seed=c, device=dev)
             if world > 1:
-                n0, n1 = N * rank // world, N * (rank + 1) // world
+                n0, n1 = shard_bounds(N, world)[rank]
                 full = L
                 L = full.rows(n0, n1)
                 L._full_bytes = {M: full.algorithmic_bytes(M) for M in wl.CFG1_M}
@@ -179,9 +183,33 @@ def run_ours(args):
     yg = {(K, N, M): torch.empty(world * M, sets[0][(K, N)][0].N, dtype=torch.float16, device=dev)
           for (K, N, M) in items} if world > 1 else None
 
+    # multi-GPU exchange: peer stores issued by the decode kernel itself (default), or NCCL
+    exchange, comm, comm_off = "none", None, {}
+    if world > 1:
+        exchange = args.exchange
+        if exchange == "peer":
+            try:
+                off = 0
+                for (K, N, M) in items:
+                    comm_off[(K, N, M)] = off
+                    off += (2 * M * N + 255) // 256 * 256
+                comm = _C_ops.Comm(rank, world, off, device=dev)
+                comm.connect_group()
+            except Exception as e:       # no inter-process mapping on this box: the NCCL exchange still measures the path
+                print(f"[bench] peer-mapped buffers unavailable ({e}); using the NCCL all-gather", file=sys.stderr)
+                exchange, comm = "nccl", None
+            flags = torch.tensor([1 if exchange == "peer" else 0], device=dev)
+            dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+            if int(flags.item()) == 0:
+                exchange, comm = "nccl", None
+
     def run_step(c):
         for (K, N, M) in items:
             L, plan = sets[c][(K, N)]
+            if exchange == "peer":
+                _C_ops.forward_gather(L.base_weight, L.base_scales, L.vals, L.col, L.row_ptr, xs[(K, M)], 1.0,
+                                      comm, comm_off[(K, N, M)], N, shard_bounds(N, world)[rank][0], plan=plan)
+                continue
             _C_ops.forward(L.base_weight, L.base_scales, L.vals, L.col, L.row_ptr, xs[(K, M)], ys[(K, N, M)], 1.0, plan=plan)
             if world > 1:
                 dist.all_gather_into_tensor(yg[(K, N, M)], ys[(K, N, M)])
@@ -227,6 +255,13 @@ def run_ours(args):
 
     # ---- end to end through OrthoLinear.forward with host buffers -------------------------------
     mods = [{kn: sets[c][kn][0].to_module() for kn in sets[c]} for c in range(N_COPIES)]
+    if exchange == "peer":
+        for c in range(N_COPIES):
+            for (K, N) in list(mods[c]):
+                sh = ShardedOrthoLinear(K, N, device=dev)
+                sh.local = mods[c][(K, N)]
+                sh.enable_peer_gather(max(wl.CFG1_M))
+                mods[c][(K, N)] = sh
     hx = {(K, M): xs[(K, M)].cpu().pin_memory() for (K, N, M) in items}
     hy = {(K, N, M): torch.empty(M, N, dtype=torch.float16).pin_memory() for (K, N, M) in items}
     h2d = sum(hx[(K, M)].numel() * 2 for (K, N, M) in items)
@@ -236,7 +271,9 @@ def run_ours(args):
         for (K, N, M) in items:
             xd = hx[(K, M)].to(dev, non_blocking=True)
             y = mods[c][(K, N)](xd)
-            if world > 1:
+            if exchange == "peer":
+                hy[(K, N, M)].copy_(y, non_blocking=True)
+            elif world > 1:
                 dist.all_gather_into_tensor(yg[(K, N, M)], y)
                 hy[(K, N, M)].copy_(yg[(K, N, M)].view(world, M, -1).permute(1, 0, 2).reshape(M, -1), non_blocking=True)
             else:
@@ -278,6 +315,8 @@ def run_ours(args):
             "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "parallelism": f"N-sharded x{world} + all-gather" if world > 1 else "single GPU",
+                       "exchange": {"peer": "peer stores issued by the decode kernel (ortho_b200_forward_gather)",
+                                    "nccl": "NCCL all_gather_into_tensor after the kernel", "none": None}[exchange],
                        "l2": f"rotation over {N_COPIES} distinct weight sets (~100 MB each) > 126 MB L2",
                        "timing": "CUDA graph replay per step, CUDA events on the launch stream, max over ranks"},
             "clocks": clocks,
@@ -285,8 +324,11 @@ def run_ours(args):
                     "steps": e2e_steps, "api": "OrthoLinear.forward, pinned host X in, Y out, per forward"},
             "gpu_launches": int(launches_per_step * args.steps + e2e_launches),
             "roofline": {"bound": "hbm", "achieved": value if world == 1 else value / world, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                         "frac": (value if world == 1 else value / world) / pk["hbm_gbs"], "traffic": None,
-                         "peak_source": pk["source"], "kernel": "ob::decode_kernel",
+                         "frac": (value if world == 1 else value / world) / pk["hbm_gbs"],
+                         # DRAM bytes per launch: ncu read + write of one captured launch (47.15 MB for the
+                         # 47.98 MB 4096->22016 M=1 launch, profiles/), scaled by algorithmic bytes
+                         "traffic": NCU_TRAFFIC_RATIO * step_bytes / max(1, len(items)) / world,
+                         "peak_source": pk["source"], "kernel": "ob::decode_stream_kernel",
                          "launches_per_step": launches_per_step,
                          "algorithmic_bytes_per_launch": step_bytes / max(1, len(items)) / world},
             "percent_of_nominal_8TBs": value / world / 8000.0 * 100.0,
@@ -397,6 +439,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="multi-GPU output exchange: peer stores from the decode kernel, or an NCCL all-gather")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -161,6 +161,49 @@ ORTHO_B200_API int ortho_b200_forward_static_scratch(const void *q_weight, const
                        const void *x_f16, void *y_f16,
                        int64_t M, int64_t K, int64_t N, float alpha, void *stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * N-sharded layer: output all-gather through peer-mapped buffers (one process per GPU).
+ * The reference has no multi-device path; this is the exchange step a tensor-parallel caller needs
+ * after sharding the layer over output rows (rows are independent: src/ortho.c:354-366,389-396).
+ *
+ * comm_create   allocates `bytes` of device memory on the current device for rank `rank` of `world`
+ *               (world <= 8) plus a small control block.
+ * comm_export   writes this rank's inter-process handle (ORTHO_B200_COMM_HANDLE_BYTES bytes); the
+ *               caller exchanges the handles of all ranks by any means (e.g. an all-gather on the host).
+ * comm_connect  opens the other ranks' buffers; `handles` = world handles in rank order.
+ * comm_local    device pointer of the local buffer: the gathered outputs appear there.
+ * forward_gather computes this rank's N_local output columns (arguments as ortho_b200_forward, the
+ *               weights being the rank's row shard) and stores them at columns
+ *               [n_offset, n_offset + N_local) of the [M, N_total] FP16 matrix that starts
+ *               y_offset_bytes into EVERY rank's buffer.  When the stream reaches the end of the call
+ *               all ranks' slices of this forward are present in the local buffer.  Every rank must
+ *               issue the same sequence of forward_gather calls on a comm; a buffer region may be
+ *               reused by the second next call at the earliest (alternate two regions).  For M <= 16
+ *               the peer stores and the flag exchange are part of the decode kernel itself; other
+ *               shapes add one copy kernel.  A rank whose peers do not arrive within the timeout
+ *               (default 2 s) records a kernel status (ortho_b200_query_kernel_status) and returns.
+ *               n_offset must be a multiple of 8; y_offset_bytes a multiple of 16.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct ortho_b200_comm ortho_b200_comm;
+#define ORTHO_B200_COMM_HANDLE_BYTES 64
+#define ORTHO_B200_COMM_MAX_RANKS 8
+
+ORTHO_B200_API int ortho_b200_comm_create(int rank, int world, int64_t bytes, ortho_b200_comm **out);
+ORTHO_B200_API int ortho_b200_comm_export(const ortho_b200_comm *comm, void *handle);
+ORTHO_B200_API int ortho_b200_comm_connect(ortho_b200_comm *comm, const void *handles);
+ORTHO_B200_API void *ortho_b200_comm_local(const ortho_b200_comm *comm);
+ORTHO_B200_API int ortho_b200_comm_set_timeout_ms(ortho_b200_comm *comm, int64_t ms);
+ORTHO_B200_API int ortho_b200_comm_destroy(ortho_b200_comm *comm);
+ORTHO_B200_API int ortho_b200_forward_gather(const void *q_weight, const void *q_scales_f16,
+                       const void *ortho_values_f16, const int32_t *ortho_col_indices,
+                       const int32_t *ortho_row_ptr, int64_t nnz,
+                       const void *x_f16,
+                       int64_t M, int64_t K, int64_t N_local, float alpha,
+                       const ortho_b200_plan *plan,
+                       void *workspace, int64_t workspace_bytes,
+                       ortho_b200_comm *comm, int64_t y_offset_bytes,
+                       int64_t N_total, int64_t n_offset, void *stream);
+
 /* Synchronises the device and reports whether any kernel of this library gave up on a bounded
  * wait since the last query (ERR_KERNEL, and the flag is cleared) or not (OK).  Replaces the
  * cudaDeviceSynchronize + error check at the end of the reference dispatcher

@@ -9,6 +9,7 @@ stream, and any failure raises instead of being dropped.
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Optional
 
 import torch
@@ -139,3 +140,117 @@ def forward(q_weight: torch.Tensor, q_scales: torch.Tensor, ortho_values: torch.
             plan.handle if plan is not None else None, ws_ptr, ws_bytes,
             torch.cuda.current_stream(dev).cuda_stream)
     _lib.check(st, "ortho_b200_forward")
+
+
+COMM_HANDLE_BYTES = 64
+
+
+class _DevicePtr:
+    """Exposes a raw device allocation to torch through ``__cuda_array_interface__``."""
+
+    def __init__(self, ptr: int, nbytes: int, owner):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+        self._owner = owner
+
+
+class Comm:
+    """Peer-mapped output buffer of one rank (``ortho_b200_comm_*``).
+
+    ``exchange`` is a callable that takes this rank's handle (``bytes``) and returns the list of all
+    ranks' handles in rank order; ``Comm.connect_group`` does it with ``torch.distributed``."""
+
+    def __init__(self, rank: int, world: int, nbytes: int, device=None):
+        self.rank, self.world, self.nbytes = rank, world, int(nbytes)
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        h = ctypes.c_void_p()
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib().ortho_b200_comm_create(rank, world, self.nbytes, ctypes.byref(h)), "ortho_b200_comm_create")
+        self.handle = h
+        self._buffer = None
+
+    def export(self) -> bytes:
+        buf = ctypes.create_string_buffer(COMM_HANDLE_BYTES)
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib().ortho_b200_comm_export(self.handle, buf), "ortho_b200_comm_export")
+        return bytes(buf.raw)
+
+    def connect(self, handles) -> None:
+        if len(handles) != self.world or any(len(h) != COMM_HANDLE_BYTES for h in handles):
+            raise ValueError("need one 64-byte handle per rank, in rank order")
+        blob = ctypes.create_string_buffer(b"".join(handles), COMM_HANDLE_BYTES * self.world)
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib().ortho_b200_comm_connect(self.handle, blob), "ortho_b200_comm_connect")
+
+    def connect_group(self, group=None) -> None:
+        import torch.distributed as dist
+        handles = [None] * self.world
+        dist.all_gather_object(handles, self.export(), group=group)
+        self.connect(handles)
+        dist.barrier(group=group)
+
+    def set_timeout_ms(self, ms: int) -> None:
+        _lib.check(_lib.lib().ortho_b200_comm_set_timeout_ms(self.handle, int(ms)), "ortho_b200_comm_set_timeout_ms")
+
+    def buffer(self) -> torch.Tensor:
+        """The local buffer as a uint8 tensor (outputs of ``forward_gather`` appear in it)."""
+        if self._buffer is None:
+            ptr = _lib.lib().ortho_b200_comm_local(self.handle)
+            self._buffer = torch.as_tensor(_DevicePtr(int(ptr), self.nbytes, self), device=self.device)
+        return self._buffer
+
+    def output(self, offset_bytes: int, M: int, N_total: int) -> torch.Tensor:
+        """View of the FP16 ``[M, N_total]`` matrix that starts ``offset_bytes`` into the local buffer."""
+        return self.buffer()[offset_bytes: offset_bytes + 2 * M * N_total].view(torch.float16).view(M, N_total)
+
+    def close(self) -> None:
+        if self.handle is not None and self.handle.value:
+            self._buffer = None
+            with torch.cuda.device(self.device):
+                _lib.lib().ortho_b200_comm_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def forward_gather(q_weight: torch.Tensor, q_scales: torch.Tensor, ortho_values: torch.Tensor,
+                   ortho_col_indices: torch.Tensor, ortho_row_ptr: torch.Tensor,
+                   input: torch.Tensor, alpha: float, comm: Comm, y_offset_bytes: int,
+                   N_total: int, n_offset: int,
+                   plan: Optional[Plan] = None, workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """This rank's shard (``q_weight`` ``[N_local, K/2]`` ...) of an N-sharded layer: computes columns
+    ``[n_offset, n_offset + N_local)`` and leaves the complete ``[M, N_total]`` output in every rank's
+    ``comm`` buffer at ``y_offset_bytes``.  Returns the local view of that output."""
+    if not input.is_cuda:
+        raise RuntimeError("libortho_b200 has no CPU path: `input` must be a CUDA tensor")
+    if input.dtype != torch.float16 or q_weight.dtype != torch.uint8 or q_scales.dtype != torch.float16:
+        raise TypeError("input / q_scales must be float16 and q_weight uint8 (packed INT4)")
+    if input.dim() != 2 or not input.is_contiguous():
+        raise ValueError("input must be a contiguous [M, K] tensor")
+    M, K = input.shape
+    N = q_weight.shape[0]
+    if N and (tuple(q_weight.shape) != (N, K // 2) or q_scales.numel() != N):
+        raise ValueError("shape mismatch between q_weight/q_scales/input")
+    dev = input.device
+    nnz = int(ortho_values.numel()) if ortho_values is not None else 0
+    need = workspace_bytes(M, K, N, plan) if (nnz and alpha > 0 and N) else 0
+    ws_ptr, ws_bytes = None, 0
+    if need:
+        if workspace is None or workspace.numel() * workspace.element_size() < need:
+            workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+        ws_ptr, ws_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
+    with torch.cuda.device(dev):
+        st = _lib.lib().ortho_b200_forward_gather(
+            q_weight.data_ptr() if N else None, q_scales.data_ptr() if N else None,
+            ortho_values.data_ptr() if nnz else None,
+            ortho_col_indices.data_ptr() if nnz else None,
+            ortho_row_ptr.data_ptr() if nnz else None, nnz,
+            input.data_ptr(), M, K, N, float(alpha),
+            plan.handle if plan is not None else None, ws_ptr, ws_bytes,
+            comm.handle, int(y_offset_bytes), int(N_total), int(n_offset),
+            torch.cuda.current_stream(dev).cuda_stream)
+    _lib.check(st, "ortho_b200_forward_gather")
+    return comm.output(y_offset_bytes, M, N_total)

@@ -63,6 +63,21 @@ def _declare(l):
     l.ortho_b200_query_kernel_status.argtypes = []
     l.ortho_b200_launch_count.restype = i64
     l.ortho_b200_launch_count.argtypes = []
+    l.ortho_b200_comm_create.restype = c.c_int
+    l.ortho_b200_comm_create.argtypes = [c.c_int, c.c_int, i64, c.POINTER(vp)]
+    l.ortho_b200_comm_export.restype = c.c_int
+    l.ortho_b200_comm_export.argtypes = [vp, vp]
+    l.ortho_b200_comm_connect.restype = c.c_int
+    l.ortho_b200_comm_connect.argtypes = [vp, vp]
+    l.ortho_b200_comm_local.restype = vp
+    l.ortho_b200_comm_local.argtypes = [vp]
+    l.ortho_b200_comm_set_timeout_ms.restype = c.c_int
+    l.ortho_b200_comm_set_timeout_ms.argtypes = [vp, i64]
+    l.ortho_b200_comm_destroy.restype = c.c_int
+    l.ortho_b200_comm_destroy.argtypes = [vp]
+    l.ortho_b200_forward_gather.restype = c.c_int
+    l.ortho_b200_forward_gather.argtypes = [vp, vp, vp, i32p, i32p, i64, vp, i64, i64, i64, c.c_float,
+                                            vp, vp, i64, vp, i64, i64, i64, vp]
 
 
 # every symbol include/ortho_b200.h declares
@@ -72,6 +87,8 @@ EXPORTS = [
     "ortho_b200_plan_max_row_nnz", "ortho_b200_plan_decode_dump", "ortho_b200_dequant_dump",
     "ortho_b200_workspace_bytes", "ortho_b200_plan_workspace_bytes", "ortho_b200_forward", "ortho_b200_set_decode_config",
     "ortho_b200_launch_count", "ortho_b200_query_kernel_status", "ortho_b200_forward_static_scratch",
+    "ortho_b200_comm_create", "ortho_b200_comm_export", "ortho_b200_comm_connect", "ortho_b200_comm_local",
+    "ortho_b200_comm_set_timeout_ms", "ortho_b200_comm_destroy", "ortho_b200_forward_gather",
 ]
 
 

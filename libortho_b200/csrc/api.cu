@@ -102,13 +102,15 @@ extern "C" int64_t ortho_b200_workspace_bytes(int64_t M, int64_t K, int64_t N)
     return prefill_workspace_bytes(M, K, N);
 }
 
-extern "C" int ortho_b200_forward(const void *q_weight, const void *q_scales_f16,
-                                  const void *ortho_values_f16, const int32_t *ortho_col_indices,
-                                  const int32_t *ortho_row_ptr, int64_t nnz,
-                                  const void *x_f16, void *y_f16,
-                                  int64_t M, int64_t K, int64_t N, float alpha,
-                                  const ortho_b200_plan *plan,
-                                  void *workspace, int64_t workspace_bytes, void *stream)
+namespace ob {
+int forward_impl(const void *q_weight, const void *q_scales_f16,
+                 const void *ortho_values_f16, const int32_t *ortho_col_indices,
+                 const int32_t *ortho_row_ptr, int64_t nnz,
+                 const void *x_f16, void *y_f16,
+                 int64_t M, int64_t K, int64_t N, float alpha,
+                 const ortho_b200_plan *plan,
+                 void *workspace, int64_t workspace_bytes, void *stream,
+                 int64_t ldy, const GatherView *gv, bool *gather_fused)
 {
     if (M == 0) return ORTHO_B200_OK;
     if (!q_weight || !q_scales_f16 || !x_f16 || !y_f16) return ORTHO_B200_ERR_NULL;
@@ -151,7 +153,23 @@ extern "C" int ortho_b200_forward(const void *q_weight, const void *q_scales_f16
     }
     a.workspace = workspace; a.workspace_bytes = workspace_bytes;
     a.stream = (cudaStream_t)stream;
+    if (ldy != 0 && ldy < N) return ORTHO_B200_ERR_SHAPE;
+    a.ldy = ldy; a.gv = gv; a.gather_fused = gather_fused;
 
     if (M <= ORTHO_B200_DECODE_MAX_M) return launch_decode(a);
     return launch_prefill(a);
+}
+}  // namespace ob
+
+extern "C" int ortho_b200_forward(const void *q_weight, const void *q_scales_f16,
+                                  const void *ortho_values_f16, const int32_t *ortho_col_indices,
+                                  const int32_t *ortho_row_ptr, int64_t nnz,
+                                  const void *x_f16, void *y_f16,
+                                  int64_t M, int64_t K, int64_t N, float alpha,
+                                  const ortho_b200_plan *plan,
+                                  void *workspace, int64_t workspace_bytes, void *stream)
+{
+    return ob::forward_impl(q_weight, q_scales_f16, ortho_values_f16, ortho_col_indices, ortho_row_ptr, nnz,
+                            x_f16, y_f16, M, K, N, alpha, plan, workspace, workspace_bytes, stream,
+                            0, nullptr, nullptr);
 }

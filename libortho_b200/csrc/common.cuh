@@ -144,8 +144,21 @@ struct FwdArgs {
     const Plan *plan;
     void *workspace; int64_t workspace_bytes;
     cudaStream_t stream;
+    // output pitch in elements (0 = N) and, for the gathering entry point, the peer buffers: a
+    // launcher whose kernel publishes to the peers itself sets *gather_fused
+    int64_t ldy = 0;
+    const struct GatherView *gv = nullptr;
+    bool *gather_fused = nullptr;
+    int64_t pitch_y() const { return ldy ? ldy : N; }
 };
 int launch_decode(const FwdArgs &a);
+// the forward behind ortho_b200_forward(); ldy = output pitch in elements (0 = N), gv / gather_fused
+// as in FwdArgs
+int forward_impl(const void *q_weight, const void *q_scales_f16, const void *ortho_values_f16,
+                 const int32_t *ortho_col_indices, const int32_t *ortho_row_ptr, int64_t nnz,
+                 const void *x_f16, void *y_f16, int64_t M, int64_t K, int64_t N, float alpha,
+                 const ortho_b200_plan *plan, void *workspace, int64_t workspace_bytes, void *stream,
+                 int64_t ldy, const struct GatherView *gv, bool *gather_fused);
 int launch_prefill(const FwdArgs &a);
 int64_t prefill_workspace_bytes(int64_t M, int64_t K, int64_t N);
 int set_decode_config(int wr, int wk, int u, int s);

@@ -30,6 +30,7 @@ struct DecodeParams {
     const uint8_t *w; const __half *scales; const __half *x; __half *y;
     OrthoView ov; int has_ortho; float alpha;
     int M, K, N;
+    long long ldy;    // elements between token rows of y
     int T;            // ceil(K / 128): k steps of 128 elements (64 packed bytes per row)
     int pass_steps;   // k steps staged in shared memory per pass
     int pitch;        // bytes between token rows of the staged X slab (== pass_steps*256 + 64)
@@ -246,7 +247,7 @@ decode_kernel(const DecodeParams p)
                 }
                 float v = __half2float(p.scales[n]) * s;
                 if (p.has_ortho) v = fmaf(p.alpha, osm[i * TOK + m], v);
-                p.y[(size_t)m * N + n] = __float2half_rn(v);
+                p.y[(size_t)m * (size_t)p.ldy + n] = __float2half_rn(v);
             }
         }
     }
@@ -319,7 +320,7 @@ static int launch_cfg(const FwdArgs &a, int S)
     DecodeParams p;
     p.w = a.w; p.scales = a.scales; p.x = a.x; p.y = a.y;
     p.ov = a.ortho; p.has_ortho = a.has_ortho; p.alpha = a.alpha;
-    p.M = (int)a.M; p.K = (int)a.K; p.N = (int)a.N;
+    p.M = (int)a.M; p.K = (int)a.K; p.N = (int)a.N; p.ldy = a.pitch_y();
     p.T = (int)ceil_div(a.K, 128);
     constexpr int R = 16 * WR, TOK = 8 * MT;
     const int steps_per_cta = (int)ceil_div(p.T, S);

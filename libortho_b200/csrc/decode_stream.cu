@@ -22,6 +22,7 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include "gather.cuh"
 #include "tma.cuh"
 
 namespace ob {
@@ -38,8 +39,16 @@ struct StreamParams {
     int ntiles;    // ceil(N / 16)
     int pitch;     // bytes between token rows of the staged activation slab
     int stages;    // ring depth per warp
-    int *status;   // device word: set to 1 if a bounded wait gave up
+    int *status;   // device word: set to 1 if a bounded wait gave up (2: a peer's gather flag)
 };
+// extra kernel argument of the GATHER instantiation (the plain one takes an empty struct)
+struct StreamGather {
+    int ldy;       // elements between token rows of y
+    GatherView gv; // the finalized values are stored into every rank's output buffer
+};
+struct StreamNoGather {};
+template <bool G> struct StreamGatherArg { using type = StreamNoGather; };
+template <> struct StreamGatherArg<true> { using type = StreamGather; };
 
 __device__ __forceinline__ uint32_t prmt_b32(uint32_t a, uint32_t b, uint32_t sel) {
     uint32_t d;
@@ -78,9 +87,12 @@ __device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.
 
 // MV = token slots kept per output row (M <= MV, power of two).  One CTA = 8 warps that split the
 // CTA's K range of a 16-row tile; a cluster of S CTAs splits K further.
-template <int MV, int KBX>
+// GATHER: instantiation with a pitched output, peer stores and the flag exchange; the plain one
+// (output pitch N, one GPU) carries none of it
+template <int MV, int KBX, bool GATHER>
 __global__ void __launch_bounds__(kWarps * 32, (MV <= 8) ? 3 : 2)
-decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParams p)
+decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParams p,
+                     const typename StreamGatherArg<GATHER>::type gp)
 {
     constexpr int kKbx = KBX;
     constexpr int kBoxBytes = 16 * KBX * 128;
@@ -256,7 +268,13 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
                 }
                 float v = sc_prev * s;
                 if (p.has_ortho) v = fmaf(p.alpha, o, v);
-                p.y[(size_t)m * N + n] = __float2half_rn(v);
+                if constexpr (!GATHER) {
+                    p.y[(size_t)m * N + n] = __float2half_rn(v);
+                } else {
+                    const __half hv = __float2half_rn(v);
+                    const size_t at = (size_t)m * gp.ldy + n;
+                    for (int r = 0; r < gp.gv.world; r++) gp.gv.y[r][at] = hv;
+                }
             }
         }
     };
@@ -386,6 +404,10 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
     finalize(nt - 1);
     // nobody may leave while a peer can still read its shared memory
     if (S > 1) { cluster_arrive(); cluster_wait(); }
+    // multi-GPU: the last CTA raises this rank's flag on every peer and waits for theirs
+    if constexpr (GATHER) {
+        if (!gather_signal_and_wait(gp.gv, gridDim.x * gridDim.y)) atomicExch(p.status, 2);
+    }
 }
 
 // ---- host ------------------------------------------------------------------------------------
@@ -400,7 +422,7 @@ static size_t stream_smem_bytes(int MV, int kbx, int64_t M, int boxes_per_cta, i
            (size_t)2 * kWarps * 16 * MV * 4 + (size_t)2 * 16 * MV * 4 + (size_t)M * (boxes_per_cta * 512 * kbx + 64);
 }
 
-template <int MV, int KBX>
+template <int MV, int KBX, bool GATHER>
 static int launch_stream_mv(const FwdArgs &a, const CUtensorMap &map, int S, int stages)
 {
     constexpr int kBoxK = 256 * KBX;
@@ -414,9 +436,21 @@ static int launch_stream_mv(const FwdArgs &a, const CUtensorMap &map, int S, int
     p.stages = stages;
     p.status = kernel_status_word();
     if (!p.status) return ORTHO_B200_ERR_CUDA;
+    typename StreamGatherArg<GATHER>::type gp;
+    if constexpr (GATHER) {
+        gp.ldy = (int)a.pitch_y();
+        if (a.gv) {
+            gp.gv = *a.gv;
+            if (a.gather_fused) *a.gather_fused = true;
+        } else {               // pitched output without peers: a world of one whose buffer is y
+            gp.gv = GatherView{};
+            gp.gv.world = 1;
+            gp.gv.y[0] = a.y;
+        }
+    }
     const size_t smem = stream_smem_bytes(MV, KBX, a.M, boxes_per_cta, stages);
     if (smem > 227 * 1024) return ORTHO_B200_ERR_SHAPE;
-    auto kern = decode_stream_kernel<MV, KBX>;
+    auto kern = decode_stream_kernel<MV, KBX, GATHER>;
     static bool attr_set = false;
     if (!attr_set) {
         OB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
@@ -457,7 +491,7 @@ static int launch_stream_mv(const FwdArgs &a, const CUtensorMap &map, int S, int
     }
     int Gc = mc < p.ntiles ? mc : p.ntiles;
     cfg.gridDim = dim3((unsigned)S, (unsigned)Gc, 1);
-    OB_CUDA(cudaLaunchKernelEx(&cfg, kern, map, p));
+    OB_CUDA(cudaLaunchKernelEx(&cfg, kern, map, p, gp));
     count_launch();
     return ORTHO_B200_OK;
 }
@@ -483,12 +517,22 @@ int launch_decode_stream(const FwdArgs &a)
     CUtensorMap map;
     if (!make_tensor_map_rows_of_128B(&map, a.w, (uint64_t)a.N, (uint64_t)(a.K / 2), 16, (uint32_t)kbx))
         return ORTHO_B200_ERR_CUDA;
+    // the GATHER instantiation also serves any output whose pitch is not N
+    if (a.gv || a.pitch_y() != a.N) {
+        switch (MV) {
+            case 1: return launch_stream_mv<1, 2, true>(a, map, S, stages);
+            case 2: return launch_stream_mv<2, 2, true>(a, map, S, stages);
+            case 4: return launch_stream_mv<4, 2, true>(a, map, S, stages);
+            case 8: return launch_stream_mv<8, 2, true>(a, map, S, stages);
+            default: return launch_stream_mv<16, 1, true>(a, map, S, stages);
+        }
+    }
     switch (MV) {
-        case 1: return launch_stream_mv<1, 2>(a, map, S, stages);
-        case 2: return launch_stream_mv<2, 2>(a, map, S, stages);
-        case 4: return launch_stream_mv<4, 2>(a, map, S, stages);
-        case 8: return launch_stream_mv<8, 2>(a, map, S, stages);
-        default: return launch_stream_mv<16, 1>(a, map, S, stages);
+        case 1: return launch_stream_mv<1, 2, false>(a, map, S, stages);
+        case 2: return launch_stream_mv<2, 2, false>(a, map, S, stages);
+        case 4: return launch_stream_mv<4, 2, false>(a, map, S, stages);
+        case 8: return launch_stream_mv<8, 2, false>(a, map, S, stages);
+        default: return launch_stream_mv<16, 1, false>(a, map, S, stages);
     }
 }
 

@@ -42,6 +42,7 @@ struct Params {
     const float *o;          // sparse term O[n][TM] (FP32) or nullptr
     float alpha;
     int M, K, N;
+    long long ldy;           // elements between token rows of y
     int ntiles, nboxes;      // ceil(N/128), ceil(K/256)
     int wstages;
     int rb;                  // rows of a tile owned (finalized) by one CTA of the cluster: ceil(128 / S)
@@ -325,7 +326,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant
                             for (int r2 = 0; r2 < S; r2++) s += ib[(size_t)r2 * p.rb * TM + m];
                             float v = sc * s;
                             if (p.o) v = fmaf(p.alpha, p.o[(size_t)n * TM + m], v);
-                            p.y[(size_t)m * p.N + n] = __float2half_rn(v);
+                            p.y[(size_t)m * (size_t)p.ldy + n] = __float2half_rn(v);
                         }
                     }
                 }
@@ -385,7 +386,7 @@ static int launch_tc(const FwdArgs &a, int S, int wstages)
     using namespace dt;
     Params p;
     p.scales = a.scales; p.y = a.y; p.alpha = a.alpha; p.o = nullptr;
-    p.M = (int)a.M; p.K = (int)a.K; p.N = (int)a.N;
+    p.M = (int)a.M; p.K = (int)a.K; p.N = (int)a.N; p.ldy = a.pitch_y();
     p.ntiles = (int)ceil_div(a.N, TH); p.nboxes = (int)ceil_div(a.K, 256);
     p.wstages = wstages; p.rb = (TH + S - 1) / S;
     p.status = kernel_status_word();

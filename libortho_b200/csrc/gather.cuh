@@ -1,0 +1,92 @@
+// Output all-gather by peer stores: every rank keeps an [M, N_total] output buffer at the same offset
+// of a peer-mapped allocation; a rank's kernel stores its column slice into every rank's buffer and
+// the last CTA of the grid then raises a flag on every peer and waits (bounded) for the peers' flags.
+// Only plain stores / loads on peer memory are used: no TMA and no multicast object ever sees it.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+namespace ob {
+
+constexpr int kMaxRanks = 8;
+
+// control block at the end of every rank's allocation
+struct GatherCtrl {
+    int flag[kMaxRanks];     // flag[r] is written by rank r: the epoch of the last forward it finished
+    int epoch;               // this rank's own count of finished gathers (device-side: survives graph replay)
+    unsigned counter;        // CTAs of the running grid that have stored everything
+};
+
+// what a kernel needs to publish its slice.  world == 1 and ctrl[*] == nullptr: plain local store.
+struct GatherView {
+    int world, rank;
+    __half *y[kMaxRanks];          // rank r's output buffer as mapped into this process ([M][ld])
+    GatherCtrl *ctrl[kMaxRanks];   // rank r's control block as mapped into this process
+    long long timeout_ns;          // bound of the wait for the peers' flags
+};
+
+__device__ __forceinline__ void st_relaxed_sys(int *p, int v) {
+    asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_relaxed_sys(const int *p) {
+    int v;
+    asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ int ld_acquire_sys(const int *p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void fence_acq_rel_gpu() { asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
+__device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
+
+// Called by every thread of every CTA once the CTA's stores to all ranks have been issued.
+// `total_ctas` = CTAs of the grid.  Returns (in thread 0 of the last CTA) false when a peer's flag
+// did not arrive in time; the caller records that in the device status word.  Every other thread
+// returns true right after the CTA-wide barrier.
+//
+// Ordering: a CTA's stores -> bar.sync -> device-scope fence + counter increment by thread 0; the
+// thread that takes the last count has thereby observed every CTA's stores, issues ONE
+// system-scope fence (cumulative: it covers the observed stores) and then writes the flags with
+// relaxed system-scope stores.  A system-scope fence waits for the NVLink round trip of the
+// outstanding peer stores, so there is exactly one on the way out; on the way in the flags are
+// polled with relaxed loads and read once more with an acquire load when they have arrived.
+__device__ __forceinline__ bool gather_signal_and_wait(const GatherView &gv, unsigned total_ctas)
+{
+    if (gv.world <= 1) return true;
+    __syncthreads();
+    if (threadIdx.x != 0) return true;
+    fence_acq_rel_gpu();
+    GatherCtrl *mine = gv.ctrl[gv.rank];
+    if (atomicAdd(&mine->counter, 1u) != total_ctas - 1) return true;
+    fence_acq_rel_sys();
+    atomicExch(&mine->counter, 0u);
+    const int ep = mine->epoch + 1;
+    mine->epoch = ep;
+    for (int r = 0; r < gv.world; r++)
+        if (r != gv.rank) st_relaxed_sys(&gv.ctrl[r]->flag[gv.rank], ep);
+    bool ok = true;
+    const unsigned long long t0 = global_timer_ns();
+    for (int r = 0; r < gv.world; r++) {
+        if (r == gv.rank) continue;
+        const int *f = &mine->flag[r];
+        unsigned spins = 0;
+        while (ld_relaxed_sys(f) - ep < 0) {
+            if ((++spins & 63u) == 0 && (long long)(global_timer_ns() - t0) > gv.timeout_ns) { ok = false; break; }
+        }
+    }
+    // acquire side: the peers' slices are ordered before whatever follows
+    for (int r = 0; r < gv.world; r++)
+        if (r != gv.rank && ld_acquire_sys(&mine->flag[r]) - ep < 0) ok = false;
+    return ok;
+}
+
+}  // namespace ob

@@ -56,6 +56,7 @@ constexpr int A_STAGE_COLS = NH * (KB / 2);
 struct Params {
     const __half *scales; __half *y;
     int M, K, N;
+    long long ldy;          // elements between token rows of y
     int tiles_n, tiles_m, kblocks;
     int *status;
     // sparse term computed ahead by spmm_ortho_kernel: O[n][m] FP32 with row pitch Mp (rows without
@@ -204,7 +205,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         const int h = (warp - EPI_WARP0) >> 2;         // accumulator handled by this warp set
         const int et = ((warp - EPI_WARP0) & 3) * 32 + lane;   // 0..127 inside the set
         __half *ys = reinterpret_cast<__half *>(ys_base + h * YS_BYTES);
-        const bool vec_ok = (p.N % 8) == 0;
+        const bool vec_ok = (p.N % 8) == 0 && (p.ldy % 8) == 0 && (reinterpret_cast<uintptr_t>(p.y) & 15u) == 0;
         int it = 0;
         for (int t = blockIdx.x; t < ntiles; t += gridDim.x, it++) {
             const int nt = t % p.tiles_n, mt = t / p.tiles_n;
@@ -248,7 +249,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                     const int m = mt * TM + c * 32 + tok, n0 = nbase + part * 8;
                     if (m < p.M && n0 < p.N) {
                         const __half *src = ys + tok * YS_PITCH + part * 8;
-                        __half *dst = p.y + (size_t)m * p.N + n0;
+                        __half *dst = p.y + (size_t)m * (size_t)p.ldy + n0;
                         if (vec_ok) {
                             *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(src);
                         } else {
@@ -294,7 +295,7 @@ int launch_prefill(const FwdArgs &a)
     if (!make_tensor_map_2d(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.w, (uint64_t)a.N, (uint64_t)(a.K / 2),
                             (uint64_t)(a.K / 2), TN, 128, CU_TENSOR_MAP_SWIZZLE_128B))
         return ORTHO_B200_ERR_CUDA;
-    p.scales = a.scales; p.y = a.y; p.M = (int)a.M; p.K = (int)a.K; p.N = (int)a.N;
+    p.scales = a.scales; p.y = a.y; p.M = (int)a.M; p.K = (int)a.K; p.N = (int)a.N; p.ldy = a.pitch_y();
     p.tiles_n = (int)ceil_div(a.N, TN); p.tiles_m = (int)ceil_div(a.M, TM); p.kblocks = (int)ceil_div(a.K, KB);
     p.status = kernel_status_word();
     if (!p.status) return ORTHO_B200_ERR_CUDA;

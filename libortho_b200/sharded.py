@@ -4,7 +4,9 @@ Output rows are independent (every ``y[m, n]`` depends on weight row ``n`` alone
 ``src/ortho.c:354-366,389-396`` in the reference), so rank ``g`` of ``G`` keeps rows
 ``[n0, n1)``: a contiguous byte slice of ``base_weight``, the matching slice of ``base_scales`` and
 the CSR rows with ``row_ptr`` rebased to 0.  ``X`` is replicated.  The only collective is the
-all-gather of the ``[M, N/G]`` output shards into ``[M, N]`` (NCCL on GPUs; any backend works).
+all-gather of the ``[M, N/G]`` output shards into ``[M, N]``: either one NCCL
+``all_gather_into_tensor`` (any backend works), or -- ``enable_peer_gather`` -- the kernels store
+their slice straight into every rank's peer-mapped output buffer (``ortho_b200_forward_gather``).
 The reference has no multi-device path; this module is what a tensor-parallel caller would use
 in its place.
 """
@@ -59,6 +61,9 @@ class ShardedOrthoLinear(nn.Module):
         self.max_rows = max(b - a for a, b in self.bounds)
         self.local = OrthoLinear(in_features, max(self.n1 - self.n0, 0), device=device)
         self._local_forward = local_forward
+        self._comm = None
+        self._comm_max_m = 0
+        self._slot = 0
 
     @classmethod
     def from_full(cls, full: OrthoLinear, group=None, align: int = 16, local_forward=None) -> "ShardedOrthoLinear":
@@ -73,11 +78,47 @@ class ShardedOrthoLinear(nn.Module):
     def set_alpha(self, alpha: float):
         self.local.set_alpha(alpha)
 
+    def enable_peer_gather(self, max_tokens: int, comm=None, offset_bytes: int = 0) -> None:
+        """Switch the exchange to peer stores.  Allocates (or adopts: ``comm`` at ``offset_bytes``) a
+        peer-mapped buffer with two ``[max_tokens, out_features]`` FP16 regions that alternate
+        between forwards: a returned output stays valid until the second next forward."""
+        from . import _C_ops as _C
+        self._region = (2 * max_tokens * self.out_features + 255) // 256 * 256
+        if comm is None:
+            comm = _C.Comm(self.rank, self.world, 2 * self._region, device=self.local.base_weight.device)
+            if self.world > 1:
+                comm.connect_group(self.group)
+            offset_bytes = 0
+        self._comm, self._comm_off, self._comm_max_m = comm, offset_bytes, max_tokens
+
+    @staticmethod
+    def peer_gather_bytes(max_tokens: int, out_features: int) -> int:
+        return 2 * ((2 * max_tokens * out_features + 255) // 256 * 256)
+
+    def _forward_peer(self, x2: torch.Tensor) -> torch.Tensor:
+        from . import _C_ops as _C
+        M = x2.shape[0]
+        if M > self._comm_max_m:
+            raise ValueError(f"peer gather was sized for {self._comm_max_m} tokens, got {M}")
+        if x2.dtype != torch.float16:
+            x2 = x2.to(torch.float16)
+        off = self._comm_off + self._slot * self._region
+        self._slot ^= 1
+        loc = self.local
+        has = loc.alpha > 0 and loc.ortho_values.numel() > 0
+        return _C.forward_gather(loc.base_weight, loc.base_scales, loc.ortho_values, loc.ortho_col_indices,
+                                 loc.ortho_row_ptr, x2.contiguous(), loc.alpha, self._comm, off,
+                                 self.out_features, self.n0,
+                                 plan=loc._get_plan() if has else None,
+                                 workspace=loc._get_workspace(M) if self.n1 > self.n0 else None)
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         lead = x.shape[:-1]
         x2 = x.reshape(-1, self.in_features)
         M = x2.shape[0]
         rows = self.n1 - self.n0
+        if self._comm is not None and M > 0:
+            return self._forward_peer(x2).reshape(*lead, self.out_features)
         if self._local_forward is not None:
             y_local = self._local_forward(self.local, x2)
         elif rows > 0:

@@ -1,0 +1,48 @@
+"""Worker of the two-GPU peer-gather test (launched by torch.distributed.run, one rank per GPU)."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from libortho_b200 import OrthoLinear, _lib, workloads as wl        # noqa: E402
+from libortho_b200.sharded import ShardedOrthoLinear               # noqa: E402
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    dist.init_process_group("nccl", device_id=dev)
+    cases = [(4096, 2048, 1), (1024, 1056, 16), (512, 528, 40), (256, 1024, 200), (2048, 96, 4)]
+    for K, N, M in cases:
+        layer = wl.make_layer(K, N, 0.01, seed=K + N + M).to(dev)
+        full = OrthoLinear(K, N, device=dev)
+        full.base_weight, full.base_scales = layer.base_weight, layer.base_scales
+        full.ortho_row_ptr, full.ortho_col_indices, full.ortho_values = layer.row_ptr, layer.col, layer.vals
+        full.set_alpha(1.0)
+        sh = ShardedOrthoLinear.from_full(full)
+        sh.enable_peer_gather(M)
+        for it in range(6):                       # both regions, several epochs
+            x = wl.make_input(M, K, seed=100 + it).to(dev)
+            y = sh(x)
+            ref = full(x)
+            torch.cuda.synchronize()
+            assert _lib.lib().ortho_b200_query_kernel_status() == 0, "a gather wait timed out"
+            # the shard and the full layer may split K differently (another FP32 summation order):
+            # equal up to FP16 rounding of the same exact sums
+            d = (y.float() - ref.float()).abs().max().item()
+            rel = ((y.float() - ref.float()).norm() / ref.float().norm()).item()
+            assert d <= 2e-2 and rel <= 1e-3, f"rank {rank}: K={K} N={N} M={M} it={it}: max_abs={d} rel={rel}"
+        dist.barrier()
+    torch.cuda.synchronize()
+    open(os.path.join(sys.argv[1], f"ok{rank}"), "w").write("ok")
+    dist.barrier()
+    os._exit(0)
+
+
+if __name__ == "__main__":
+    main()
