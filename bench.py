@@ -431,6 +431,96 @@ def cpu_baseline():
             "ms_per_step": t_total * 1e3}
 
 
+def run_report(args):
+    """All BASELINE.json configurations on one GPU, as a markdown table (``--report PATH``).  Decode-sized
+    forwards rotate over enough weight copies to exceed L2; per-forward device time from CUDA graphs."""
+    import torch
+    from libortho_b200 import _C_ops, workloads as wl
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    pk = peaks()
+    stream = torch.cuda.Stream(dev)
+    rows = []
+
+    def measure(tag, make, Ms, alphas):
+        L0 = make(0)
+        nbytes = L0.K * L0.N // 2 + 6 * L0.nnz
+        ncopies = max(1, min(N_COPIES, -(-(300 << 20) // nbytes)))
+        layers = [L0] + [make(c) for c in range(1, ncopies)]
+        plans = [_C_ops.Plan(L.row_ptr, L.col, L.vals, L.K, L.N) for L in layers]
+        for M in Ms:
+            x = wl.make_input(M, L0.K, seed=M, device=dev)
+            y = torch.empty(M, L0.N, dtype=torch.float16, device=dev)
+            need = _C_ops.workspace_bytes(M, L0.K, L0.N, plans[0])
+            ws = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
+            for alpha in alphas:
+                reps = 2 if M <= 64 else 1
+                n = reps * ncopies
+                with torch.cuda.stream(stream):
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=stream):
+                        for r in range(n):
+                            L = layers[r % ncopies]
+                            _C_ops.forward(L.base_weight, L.base_scales, L.vals, L.col, L.row_ptr, x, y, alpha,
+                                           plan=plans[r % ncopies], workspace=ws)
+                    for _ in range(3):
+                        g.replay()
+                    stream.synchronize()
+                    ts = []
+                    for _ in range(5 if M <= 2048 else 3):
+                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        e0.record(stream)
+                        g.replay()
+                        e1.record(stream)
+                        e1.synchronize()
+                        ts.append(e0.elapsed_time(e1) * 1e3 / n)
+                us = statistics.median(ts)
+                gbs = L0.algorithmic_bytes(M, alpha) / us / 1e3
+                tf = L0.algorithmic_flops(M, alpha) / us / 1e6
+                rows.append(f"| {tag} | {L0.K}->{L0.N} | {M} | {alpha} | {L0.nnz} | {us:.1f} | {M / us * 1e6:.3g} | {gbs:.0f} | "
+                            f"{100 * gbs / pk['hbm_gbs']:.1f} | {tf:.1f} | {100 * tf / pk['tf_sustained']:.1f} |")
+            del x, y, ws
+        del layers, plans
+        torch.cuda.empty_cache()
+
+    measure("0", lambda c: wl.make_layer(4096, 4096, 0.01, seed=c, device=dev, ortho="residual10"), [8], [0.0, 1.0])
+    for (K, N) in wl.CFG1_SHAPES:
+        measure("1", lambda c: wl.make_layer(K, N, wl.CFG1_DENSITY, seed=c, device=dev), wl.CFG1_M, [1.0])
+    K, N = wl.CFG2_SHAPE
+    measure("2", lambda c: wl.make_zipf_layer(K, N, wl.CFG2_DENSITY, seed=c, device=dev, alpha=wl.CFG2_ALPHA), wl.CFG2_M,
+            [wl.CFG2_ALPHA, 0.0])
+    for (K, N) in wl.CFG3_SHAPES:
+        measure("3", lambda c: wl.make_layer(K, N, wl.CFG3_DENSITY, seed=c, device=dev), wl.CFG3_M, [1.0])
+    sieve = wl.make_sieve_layer(device=dev)
+    measure("4 (threshold 10: nnz=0)", lambda c: sieve, [1, 2048], [0.0, 1.0])
+    sieve1 = wl.make_sieve_layer(device=dev, sparsity_target=0.01)
+    measure("4 (supplementary: keep top 1 %)", lambda c: sieve1, [1, 2048], [0.25, 1.0])
+
+    # the reference's CPU forward on configuration 0 (1 thread and all threads)
+    import oracle
+    impl = "reference_fast" if oracle.available("reference_fast") else "port"
+    if impl == "port":
+        oracle.build()
+    L = wl.make_layer(4096, 4096, 0.01, seed=0, ortho="residual10")
+    a = (L.base_weight.numpy(), L.base_scales.float().numpy(), L.row_ptr.numpy(), L.col.numpy(), L.vals.float().numpy())
+    x = wl.make_input(8, 4096, seed=8).float().numpy()
+    cpu = []
+    for th in (1, oracle.host_threads()):
+        t0 = time.perf_counter()
+        oracle.forward_csr(*a, x, 1.0, impl=impl, threads=th)
+        dt = time.perf_counter() - t0
+        cpu.append(f"| 0 | 4096->4096 | 8 | 1.0 | {L.nnz} | {dt * 1e6:.0f} | {8 / dt:.3g} | {L.algorithmic_bytes(8) / dt / 1e9:.2f} | - | "
+                   f"{L.algorithmic_flops(8) / dt / 1e12:.4f} | - | CPU `{impl}`, {th} thread(s) |")
+    head = ("| config | shape K->N | M | alpha | nnz | us / forward | tokens/s | GB/s (algorithmic) | % of measured HBM "
+            f"({pk['hbm_gbs']:.0f} GB/s) | TFLOP/s | % of measured sustained tensor ({pk['tf_sustained']:.0f} TF) |")
+    sep = "|" + "---|" * 11
+    out = ["# All configurations, one B200 (`python bench.py --report <path>`)", "", head, sep, *rows, "",
+           "CPU rows (host of the same box):", "", head + " note |", sep + "---|", *cpu, ""]
+    with open(args.report, "w") as f:
+        f.write("\n".join(out))
+    print("\n".join(out))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -441,8 +531,12 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="multi-GPU output exchange: peer stores from the decode kernel, or an NCCL all-gather")
+    ap.add_argument("--report", default=None, metavar="PATH",
+                    help="instead of the benchmark line: time every configuration on one GPU and write a markdown table")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.report:
+        run_report(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
