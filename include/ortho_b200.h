@@ -104,8 +104,8 @@ ORTHO_B200_API int ortho_b200_dequant_dump(const void *q_weight, const void *q_s
  * torch_bind/ortho_linear.py:142-151); same argument order and meaning, plus explicit sizes,
  * the optional plan, a caller-owned workspace and the stream.
  *
- *   M <= ORTHO_B200_DECODE_MAX_M : memory-bound streaming kernels.
- *   larger M                     : tcgen05 / TMEM tensor-core kernel.
+ *   M <= 24  : memory-bound streaming kernels (ORTHO_B200_DECODE_MAX_M is the most they accept).
+ *   larger M : tcgen05 / TMEM tensor-core kernel.
  * Either regime needs ortho_b200_workspace_bytes(M, K, N) bytes of caller-owned workspace when the
  * ortho term is active (alpha > 0 and nnz > 0), none otherwise.
  * plan may be NULL: the kernels then read the CSR arrays directly.  With a plan the CSR
@@ -216,7 +216,9 @@ ORTHO_B200_API int ortho_b200_query_kernel_status(void);
  *   row_groups == -1: streaming TMA kernel (M <= 16) with k_split CTAs per cluster and `unroll`
  *                    ring slots per warp (either may be 0 for the built-in choice);
  *   row_groups == -2: tcgen05 decode kernel with k_split CTAs per cluster and `unroll` weight stages;
- *   row_groups == 0 : restore the built-in choice.
+ *   row_groups == -3: forwards with more than k_split tokens (0..ORTHO_B200_DECODE_MAX_M) use the
+ *                    tensor-core kernel (built-in: 24);
+ *   row_groups == 0 : restore the built-in choice of kernel and tiling (not the -3 threshold).
  * Returns ERR_SHAPE for an unsupported tuple. */
 ORTHO_B200_API int ortho_b200_set_decode_config(int row_groups, int k_groups, int unroll, int k_split);
 

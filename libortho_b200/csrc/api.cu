@@ -98,7 +98,7 @@ extern "C" int ortho_b200_query_kernel_status(void)
 
 extern "C" int64_t ortho_b200_workspace_bytes(int64_t M, int64_t K, int64_t N)
 {
-    if (M <= ORTHO_B200_DECODE_MAX_M) return decode_tc_workspace_bytes(M, N);
+    if (M <= g_prefill_above) return decode_tc_workspace_bytes(M, N);
     return prefill_workspace_bytes(M, K, N);
 }
 
@@ -156,7 +156,7 @@ int forward_impl(const void *q_weight, const void *q_scales_f16,
     if (ldy != 0 && ldy < N) return ORTHO_B200_ERR_SHAPE;
     a.ldy = ldy; a.gv = gv; a.gather_fused = gather_fused;
 
-    if (M <= ORTHO_B200_DECODE_MAX_M) return launch_decode(a);
+    if (M <= g_prefill_above) return launch_decode(a);
     return launch_prefill(a);
 }
 }  // namespace ob

@@ -259,6 +259,10 @@ decode_kernel(const DecodeParams p)
 struct DecodeCfg { int wr, wk, u, s; };
 static DecodeCfg g_override = {0, 0, 0, 0};
 static bool g_force_stream = false;
+// Forwards with more tokens than this go to the tcgen05 prefill kernel.  Measured on 8192->8192 / 8192->57344 /
+// 28672->8192: at 32 tokens the 128 x 256 tensor-core tile (mostly padding) takes 97 / 370 / 300 us where the
+// mma.sync kernel below takes 146 / 972 / 479 us; at 17 tokens the two are within a few per cent.
+int g_prefill_above = 24;
 static bool g_use_tc = false;                        // tcgen05 decode kernel: opt-in through the tuning hook (slower than the
                                                      // streaming kernel on the benchmark shapes so far)
 int launch_decode_stream(const FwdArgs &a);          // decode_stream.cu
@@ -268,6 +272,11 @@ void set_tc_config(int s, int stages);
 
 int set_decode_config(int wr, int wk, int u, int s)
 {
+    if (wr == -3) {       // forwards with more than s tokens (0 <= s <= 64) go to the tensor-core prefill kernel
+        if (s < 0 || s > ORTHO_B200_DECODE_MAX_M) return ORTHO_B200_ERR_SHAPE;
+        g_prefill_above = s;
+        return ORTHO_B200_OK;
+    }
     if (wr == -2) {       // tcgen05 decode kernel with k_split = s CTAs per cluster and u weight stages (0 = built-in)
         if (s < 0 || s > 8 || u < 0 || u > 8) return ORTHO_B200_ERR_SHAPE;
         g_override = {0, 0, 0, 0};

@@ -39,6 +39,7 @@ struct StreamParams {
     int ntiles;    // ceil(N / 16)
     int pitch;     // bytes between token rows of the staged activation slab
     int stages;    // ring depth per warp
+    int red_bufs;  // 2: partial sums double-buffered; 1 (S == 1 only): one buffer and a group barrier per tile
     int *status;   // device word: set to 1 if a bounded wait gave up (2: a peer's gather flag)
 };
 // extra kernel argument of the GATHER instantiation (the plain one takes an empty struct)
@@ -89,8 +90,11 @@ __device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.
 // CTA's K range of a 16-row tile; a cluster of S CTAs splits K further.
 // GATHER: instantiation with a pitched output, peer stores and the flag exchange; the plain one
 // (output pitch N, one GPU) carries none of it
-template <int MV, int KBX, bool GATHER>
-__global__ void __launch_bounds__(kWarps * 32, (MV <= 8) ? 3 : 2)
+// NG = warp groups per CTA.  A group is the 8-warp unit described above, with its own rings, tile barrier
+// and reduction buffers; the groups of a CTA work on different tiles and share one activation slab, which
+// is what limits residency for 8 and 16 tokens (NG = 2: one CTA of 16 warps per SM instead of one of 8).
+template <int MV, int KBX, bool GATHER, int NG>
+__global__ void __launch_bounds__(NG * kWarps * 32, NG == 2 ? 1 : 2)
 decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParams p,
                      const typename StreamGatherArg<GATHER>::type gp)
 {
@@ -102,27 +106,35 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
     constexpr int LPG = 32 / MV;                  // lanes per token index after the butterfly
     extern __shared__ __align__(1024) unsigned char smem[];
 
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // tid / warp are relative to the warp group; cid / G index warp groups, not CTAs
+    const int grp = (NG == 1) ? 0 : (int)(threadIdx.x >> 8);
+    const int tid = threadIdx.x & 255, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const int S = (int)cluster_nctarank();
     const int rank = (int)cluster_ctarank();
-    const int cid = blockIdx.y, G = gridDim.y;
+    const int cid = blockIdx.y * NG + grp, G = gridDim.y * NG;
     const int K = p.K, N = p.N, M = p.M;
 
     // ---- shared memory carve-up ----------------------------------------------------------------
     // the 128-byte TMA swizzle is a function of the shared-memory address: ring slots sit on 1 KB
-    unsigned char *ring = smem + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);    // kWarps * stages * 2 KB
+    // one region per warp group (rounded to 1 KB), then the activation slab shared by the groups
+    const size_t region = ((size_t)kWarps * p.stages * kBoxBytes + (((kWarps * p.stages + 1) * 8 + 127) & ~127) +
+                           (size_t)p.red_bufs * kWarps * 16 * MV * 4 + (size_t)2 * 16 * MV * 4 + 1023) & ~(size_t)1023;
+    unsigned char *base = smem + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);
+    unsigned char *ring = base + (size_t)grp * region;                            // kWarps * stages boxes
     uint64_t *bars = reinterpret_cast<uint64_t *>(ring + (size_t)kWarps * p.stages * kBoxBytes);
     uint64_t *tbar = bars + kWarps * p.stages;                                    // tile barrier (S == 1)
     float *red = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(bars) + (((kWarps * p.stages + 1) * 8 + 127) & ~127));
-    float *osm = red + 2 * kWarps * 16 * MV;                                      // [2][16*MV]
-    unsigned char *xs = reinterpret_cast<unsigned char *>(osm + 2 * 16 * MV);     // M * pitch
+    float *osm = red + p.red_bufs * kWarps * 16 * MV;                             // [2][16*MV]
+    unsigned char *xs = base + (size_t)NG * region;                               // M * pitch
 
     // ---- this warp's share of the K range, in boxes of 256 weights -----------------------------
     const int cb0 = (p.nboxes * rank) / S, cb1 = (p.nboxes * (rank + 1)) / S;
     const int wb0 = cb0 + ((cb1 - cb0) * warp) / kWarps, wb1 = cb0 + ((cb1 - cb0) * (warp + 1)) / kWarps;
     const int nbw = wb1 - wb0;
-    const int nt = (p.ntiles - cid + G - 1) / G;          // tiles walked by this cluster
+    const int nt = cid < p.ntiles ? (p.ntiles - cid + G - 1) / G : 0;   // tiles walked by this warp group
+    // every group of every CTA of the cluster goes through the same number of tile barriers
+    const int nt_loop = ((int)blockIdx.y * NG < p.ntiles) ? (p.ntiles - (int)blockIdx.y * NG + G - 1) / G : 0;
     const int total = nt * nbw;                           // boxes this warp consumes
     const int k_lo = cb0 * kBoxK, k_hi = min(cb1 * kBoxK, K); // activation slab of this CTA
 
@@ -192,7 +204,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
     {
         const int chunks_per_row = (cb1 - cb0) * (kBoxK / 8);
         const int totalc = M * chunks_per_row;
-        for (int idx = tid; idx < totalc; idx += kWarps * 32) {
+        for (int idx = (int)threadIdx.x; idx < totalc; idx += NG * kWarps * 32) {
             const int r = idx / chunks_per_row, q = idx - r * chunks_per_row;
             const int k = k_lo + q * 8;
             uint4 v = make_uint4(0, 0, 0, 0);
@@ -244,17 +256,18 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
     // the row scale a finalizing thread needs is fetched one tile early, so that the finalize of
     // tile i (executed while tile i+1 is in flight) never waits on global memory
     float sc_prev = 0.f;
+    const int rmask = p.red_bufs - 1;          // 1: alternate the partial-sum buffers, 0: single buffer
     auto finalize = [&](int ti) {
-        const int buf = ti & 1;
+        const int buf = ti & 1, rbuf = ti & rmask;
         if (fin_on) {
             const int m = fin_m, i = fin_i;
             const int n = (cid + ti * G) * 16 + i;
             if (n < N) {
-                const uint32_t red_base = smem_u32(red + (size_t)buf * kWarps * 16 * MV);
+                const uint32_t red_base = smem_u32(red + (size_t)rbuf * kWarps * 16 * MV);
                 const uint32_t osm_base = smem_u32(osm + (size_t)buf * 16 * MV);
                 float s = 0.f, o = 0.f;
                 if (S == 1) {
-                    const float *rb = red + (size_t)buf * kWarps * 16 * MV + i * MV + m;
+                    const float *rb = red + (size_t)rbuf * kWarps * 16 * MV + i * MV + m;
 #pragma unroll
                     for (int w = 0; w < kWarps; w++) s += rb[w * 16 * MV];
                     if (p.has_ortho) o = osm[(size_t)buf * 16 * MV + i * MV + m];
@@ -279,7 +292,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
         }
     };
 
-    for (int ti = 0; ti < nt; ti++) {
+    for (int ti = 0; ti < nt_loop; ti++) {
         float sc_new = 0.f;
         if (fin_on) {
             const int n = (cid + ti * G) * 16 + fin_i;
@@ -299,7 +312,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
         }
 
         // ---- base: consume this warp's boxes of the tile ---------------------------------------
-        for (int bi = 0; bi < nbw; bi++) {
+        for (int bi = 0; bi < (ti < nt ? nbw : 0); bi++) {
             if (!mbar_try_wait(&my_bars[c_st], c_ph)) {
                 if (!dead && !mbar_wait(&my_bars[c_st], c_ph)) { dead = true; if (lane == 0) atomicExch(p.status, 1); }
             }
@@ -369,8 +382,10 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
             if (!tile_wait(ti - 1) && !dead) { dead = true; if (lane == 0) atomicExch(p.status, 1); }
             finalize(ti - 1);
         }
+        // single partial-sum buffer: every read of the previous tile's sums precedes the new writes
+        if (rmask == 0) asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "r"(kWarps * 32) : "memory");
         {
-            float *mine = red + ((size_t)(ti & 1) * kWarps + warp) * 16 * MV;
+            float *mine = red + ((size_t)(ti & rmask) * kWarps + warp) * 16 * MV;
 #pragma unroll
             for (int mt = 0; mt < MT; mt++) {
 #pragma unroll
@@ -400,8 +415,10 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
             }
         }
     }
-    if (!tile_wait(nt - 1) && !dead) { if (lane == 0) atomicExch(p.status, 1); }
-    finalize(nt - 1);
+    if (nt_loop > 0) {
+        if (!tile_wait(nt_loop - 1) && !dead) { if (lane == 0) atomicExch(p.status, 1); }
+        finalize(nt_loop - 1);
+    }
     // nobody may leave while a peer can still read its shared memory
     if (S > 1) { cluster_arrive(); cluster_wait(); }
     // multi-GPU: the last CTA raises this rank's flag on every peer and waits for theirs
@@ -416,14 +433,15 @@ int *kernel_status_word();   // api.cu
 static int g_stream_cfg[2] = {0, 0};   // {k_split, stages}; 0 = built-in choice
 void set_stream_config(int s, int stages) { g_stream_cfg[0] = s; g_stream_cfg[1] = stages; }
 
-static size_t stream_smem_bytes(int MV, int kbx, int64_t M, int boxes_per_cta, int stages)
+static size_t stream_smem_bytes(int MV, int kbx, int64_t M, int boxes_per_cta, int stages, int ng = 1, int red_bufs = 2)
 {
-    return 1024 + (size_t)kWarps * stages * (16 * kbx * 128) + (((kWarps * stages + 1) * 8 + 127) & ~127) +
-           (size_t)2 * kWarps * 16 * MV * 4 + (size_t)2 * 16 * MV * 4 + (size_t)M * (boxes_per_cta * 512 * kbx + 64);
+    const size_t region = ((size_t)kWarps * stages * (16 * kbx * 128) + (((kWarps * stages + 1) * 8 + 127) & ~127) +
+                           (size_t)red_bufs * kWarps * 16 * MV * 4 + (size_t)2 * 16 * MV * 4 + 1023) & ~(size_t)1023;
+    return 1024 + (size_t)ng * region + (size_t)M * (boxes_per_cta * 512 * kbx + 64);
 }
 
-template <int MV, int KBX, bool GATHER>
-static int launch_stream_mv(const FwdArgs &a, const CUtensorMap &map, int S, int stages)
+template <int MV, int KBX, bool GATHER, int NG = 1>
+static int launch_stream_mv(const FwdArgs &a, const CUtensorMap &map, int S, int stages, int red_bufs)
 {
     constexpr int kBoxK = 256 * KBX;
     StreamParams p;
@@ -434,6 +452,7 @@ static int launch_stream_mv(const FwdArgs &a, const CUtensorMap &map, int S, int
     const int boxes_per_cta = (int)ceil_div(p.nboxes, S);
     p.pitch = boxes_per_cta * kBoxK * 2 + 64;
     p.stages = stages;
+    p.red_bufs = red_bufs;
     p.status = kernel_status_word();
     if (!p.status) return ORTHO_B200_ERR_CUDA;
     typename StreamGatherArg<GATHER>::type gp;
@@ -448,16 +467,16 @@ static int launch_stream_mv(const FwdArgs &a, const CUtensorMap &map, int S, int
             gp.gv.y[0] = a.y;
         }
     }
-    const size_t smem = stream_smem_bytes(MV, KBX, a.M, boxes_per_cta, stages);
+    const size_t smem = stream_smem_bytes(MV, KBX, a.M, boxes_per_cta, stages, NG, red_bufs);
     if (smem > 227 * 1024) return ORTHO_B200_ERR_SHAPE;
-    auto kern = decode_stream_kernel<MV, KBX, GATHER>;
+    auto kern = decode_stream_kernel<MV, KBX, GATHER, NG>;
     static bool attr_set = false;
     if (!attr_set) {
         OB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         attr_set = true;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.blockDim = dim3(kWarps * 32, 1, 1);
+    cfg.blockDim = dim3(NG * kWarps * 32, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = a.stream;
     cudaLaunchAttribute attr[2];
@@ -489,7 +508,8 @@ static int launch_stream_mv(const FwdArgs &a, const CUtensorMap &map, int S, int
         cache[cache_n % 16] = {S, smem, n};
         if (cache_n < 16) cache_n++;
     }
-    int Gc = mc < p.ntiles ? mc : p.ntiles;
+    const int units = (int)ceil_div(p.ntiles, NG);       // a CTA takes NG tiles per round
+    int Gc = mc < units ? mc : units;
     cfg.gridDim = dim3((unsigned)S, (unsigned)Gc, 1);
     OB_CUDA(cudaLaunchKernelEx(&cfg, kern, map, p, gp));
     count_launch();
@@ -502,38 +522,47 @@ int launch_decode_stream(const FwdArgs &a)
     const int MV = a.M <= 1 ? 1 : a.M <= 2 ? 2 : a.M <= 4 ? 4 : a.M <= 8 ? 8 : 16;
     const int kbx = (MV <= 8) ? 2 : 1;
     const int nboxes = (int)ceil_div(a.K, 256 * kbx);
-    int S = g_stream_cfg[0], stages = g_stream_cfg[1];
+    int S = g_stream_cfg[0], stages = g_stream_cfg[1], ng = 1, red_bufs = 2;
     if (S <= 0) {
         // one CTA per tile covers all of K when its activation slab fits; otherwise split K over the
         // smallest cluster that does
         S = 1;
         while (S < 8 && stream_smem_bytes(MV, kbx, a.M, (int)ceil_div(nboxes, S), 2) > 200 * 1024) S *= 2;
+        // 8 or more tokens: the activation slab decides how many warps an SM can hold, so two warp
+        // groups share one slab when that needs no further split of K (a cluster costs a DSMEM
+        // exchange per tile and makes every CTA walk the tile's sparse entries) and leaves each
+        // warp at least one box per tile; without a cluster a single partial-sum buffer may make it fit
+        if (MV >= 8 && nboxes / S >= kWarps) {
+            const int bpc2 = (int)ceil_div(nboxes, S);
+            if (stream_smem_bytes(MV, kbx, a.M, bpc2, 2, 2, 2) <= 227 * 1024) ng = 2;
+            else if (S == 1 && stream_smem_bytes(MV, kbx, a.M, bpc2, 2, 2, 1) <= 227 * 1024) { ng = 2; red_bufs = 1; }
+        }
     }
     if (S > 8) S = 8;
-    if (stages <= 0) stages = 2;
-    while (stages > 2 && stream_smem_bytes(MV, kbx, a.M, (int)ceil_div(nboxes, S), stages) > 227 * 1024) stages--;
+    const int bpc = (int)ceil_div(nboxes, S);
+    if (stages <= 0) {
+        // one token: 2 CTAs of 128 registers per SM, and a third ring slot when two such CTAs still fit
+        stages = (MV == 1 && stream_smem_bytes(MV, kbx, a.M, bpc, 3) <= 113 * 1024) ? 3 : 2;
+    }
+    while (stages > 2 && stream_smem_bytes(MV, kbx, a.M, bpc, stages, ng, red_bufs) > 227 * 1024) stages--;
 
     // [N][K/2 / 128][128 B] view of the packed base; blocks past the end of a row read as zero
     CUtensorMap map;
     if (!make_tensor_map_rows_of_128B(&map, a.w, (uint64_t)a.N, (uint64_t)(a.K / 2), 16, (uint32_t)kbx))
         return ORTHO_B200_ERR_CUDA;
     // the GATHER instantiation also serves any output whose pitch is not N
-    if (a.gv || a.pitch_y() != a.N) {
-        switch (MV) {
-            case 1: return launch_stream_mv<1, 2, true>(a, map, S, stages);
-            case 2: return launch_stream_mv<2, 2, true>(a, map, S, stages);
-            case 4: return launch_stream_mv<4, 2, true>(a, map, S, stages);
-            case 8: return launch_stream_mv<8, 2, true>(a, map, S, stages);
-            default: return launch_stream_mv<16, 1, true>(a, map, S, stages);
-        }
-    }
+    const bool gather = a.gv || a.pitch_y() != a.N;
+#define OB_STREAM(MV_, KBX_, NG_) \
+    (gather ? launch_stream_mv<MV_, KBX_, true, NG_>(a, map, S, stages, red_bufs) \
+            : launch_stream_mv<MV_, KBX_, false, NG_>(a, map, S, stages, red_bufs))
     switch (MV) {
-        case 1: return launch_stream_mv<1, 2, false>(a, map, S, stages);
-        case 2: return launch_stream_mv<2, 2, false>(a, map, S, stages);
-        case 4: return launch_stream_mv<4, 2, false>(a, map, S, stages);
-        case 8: return launch_stream_mv<8, 2, false>(a, map, S, stages);
-        default: return launch_stream_mv<16, 1, false>(a, map, S, stages);
+        case 1: return OB_STREAM(1, 2, 1);
+        case 2: return OB_STREAM(2, 2, 1);
+        case 4: return OB_STREAM(4, 2, 1);
+        case 8: return ng == 2 ? OB_STREAM(8, 2, 2) : OB_STREAM(8, 2, 1);
+        default: return ng == 2 ? OB_STREAM(16, 1, 2) : OB_STREAM(16, 1, 1);
     }
+#undef OB_STREAM
 }
 
 }  // namespace ob

@@ -143,10 +143,12 @@ def test_every_decode_tiling_agrees_with_the_oracle(oracle_mod, cfg, M):
     x = wl.make_input(M, K, seed=41)
     ref = layer_oracle(oracle_mod, layer, x, 0.75)
     try:
+        assert _lib.lib().ortho_b200_set_decode_config(-3, 0, 0, 64) == 0      # keep 33 and 64 tokens on this kernel
         assert _lib.lib().ortho_b200_set_decode_config(*cfg) == 0
         y = run_layer(layer.to(DEV), x.to(DEV), 0.75)
     finally:
         _lib.lib().ortho_b200_set_decode_config(0, 0, 0, 0)
+        _lib.lib().ortho_b200_set_decode_config(-3, 0, 0, 24)
     assert_close(y.float().cpu().numpy(), ref, f"cfg={cfg} M={M}")
 
 
@@ -164,6 +166,29 @@ def test_decode_sweep_shapes_against_oracle(oracle_mod, K, N):
         ref = np.concatenate([layer_oracle(oracle_mod, s, x.cpu(), 1.0, threads=1) for s in sub], axis=1)
         assert_close(y[:, rows], ref, f"{K}->{N} M={M}")
         assert np.isfinite(y).all()
+
+
+@pytest.mark.parametrize("K,N", [(8192, 10240), (28672, 8192)])
+def test_sharded_config_shapes_against_oracle(oracle_mod, K, N):
+    """Llama-70B-style shapes (0.3 % ortho) at M in {1, 32, 4096}: a row sample of the output against
+    the oracle, for all tokens at M <= 32 and for a seeded token sample at M = 4096 (tokens and rows
+    are independent in the reference: src/ortho.c:346-349, 354-366)."""
+    layer = wl.make_layer(K, N, wl.CFG3_DENSITY, seed=71, device=DEV)
+    rows = sorted({0, 17, 127, 128, N // 2 + 3, N - 129, N - 1} | set(range(N // 5, N // 5 + 24)))
+    cpu = layer.to("cpu")
+    sub = [cpu.rows(r, r + 1) for r in rows]
+    g = torch.Generator().manual_seed(7)
+    for M in (1, 32, 4096):
+        x = wl.make_input(M, K, seed=M, device=DEV)
+        y = run_layer(layer, x, 1.0)
+        toks = list(range(M)) if M <= 32 else sorted(torch.randperm(M, generator=g)[:64].tolist())
+        xs = x[toks].cpu()
+        ref = np.concatenate([layer_oracle(oracle_mod, s_, xs, 1.0, threads=1) for s_ in sub], axis=1)
+        got = y[toks][:, rows].float().cpu().numpy()
+        assert_close(got, ref, f"{K}->{N} M={M}")
+        assert bool(torch.isfinite(y).all())
+        del x, y
+    torch.cuda.empty_cache()
 
 
 def test_linearity_and_alpha_properties_at_full_size():
