@@ -528,12 +528,12 @@ int launch_decode_stream(const FwdArgs &a)
         // smallest cluster that does
         S = 1;
         while (S < 8 && stream_smem_bytes(MV, kbx, a.M, (int)ceil_div(nboxes, S), 2) > 200 * 1024) S *= 2;
-        // 8 or more tokens: the activation slab decides how many warps an SM can hold, so two warp
-        // groups share one slab when that needs no further split of K (a cluster costs a DSMEM
+        // a large activation slab (8 or more tokens, or a long K) leaves room for one CTA per SM only;
+        // two warp groups then share one slab when that needs no further split of K (a cluster costs a DSMEM
         // exchange per tile and makes every CTA walk the tile's sparse entries) and leaves each
         // warp at least one box per tile; without a cluster a single partial-sum buffer may make it fit
-        if (MV >= 8 && nboxes / S >= kWarps) {
-            const int bpc2 = (int)ceil_div(nboxes, S);
+        const int bpc2 = (int)ceil_div(nboxes, S);
+        if (nboxes / S >= kWarps && 2 * stream_smem_bytes(MV, kbx, a.M, bpc2, 2) > 227 * 1024) {   // one CTA per SM otherwise
             if (stream_smem_bytes(MV, kbx, a.M, bpc2, 2, 2, 2) <= 227 * 1024) ng = 2;
             else if (S == 1 && stream_smem_bytes(MV, kbx, a.M, bpc2, 2, 2, 1) <= 227 * 1024) { ng = 2; red_bufs = 1; }
         }
@@ -556,9 +556,9 @@ int launch_decode_stream(const FwdArgs &a)
     (gather ? launch_stream_mv<MV_, KBX_, true, NG_>(a, map, S, stages, red_bufs) \
             : launch_stream_mv<MV_, KBX_, false, NG_>(a, map, S, stages, red_bufs))
     switch (MV) {
-        case 1: return OB_STREAM(1, 2, 1);
-        case 2: return OB_STREAM(2, 2, 1);
-        case 4: return OB_STREAM(4, 2, 1);
+        case 1: return ng == 2 ? OB_STREAM(1, 2, 2) : OB_STREAM(1, 2, 1);
+        case 2: return ng == 2 ? OB_STREAM(2, 2, 2) : OB_STREAM(2, 2, 1);
+        case 4: return ng == 2 ? OB_STREAM(4, 2, 2) : OB_STREAM(4, 2, 1);
         case 8: return ng == 2 ? OB_STREAM(8, 2, 2) : OB_STREAM(8, 2, 1);
         default: return ng == 2 ? OB_STREAM(16, 1, 2) : OB_STREAM(16, 1, 1);
     }
