@@ -195,6 +195,7 @@ def run_ours(args):
                     off += (2 * M * N + 255) // 256 * 256
                 comm = _C_ops.Comm(rank, world, off, device=dev)
                 comm.connect_group()
+                comm.set_deferred(not args.no_deferred)
             except Exception as e:       # no inter-process mapping on this box: the NCCL exchange still measures the path
                 print(f"[bench] peer-mapped buffers unavailable ({e}); using the NCCL all-gather", file=sys.stderr)
                 exchange, comm = "nccl", None
@@ -213,6 +214,8 @@ def run_ours(args):
             _C_ops.forward(L.base_weight, L.base_scales, L.vals, L.col, L.row_ptr, xs[(K, M)], ys[(K, N, M)], 1.0, plan=plan)
             if world > 1:
                 dist.all_gather_into_tensor(yg[(K, N, M)], ys[(K, N, M)])
+        if exchange == "peer":
+            comm.wait()          # deferred mode: every forward waited for its predecessor's exchange; this is the last one's
 
     # ---- capture one CUDA graph per weight set --------------------------------------------------
     stream = torch.cuda.Stream(dev)
@@ -315,7 +318,8 @@ def run_ours(args):
             "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "parallelism": f"N-sharded x{world} + all-gather" if world > 1 else "single GPU",
-                       "exchange": {"peer": "peer stores issued by the decode kernel (ortho_b200_forward_gather)",
+                       "exchange": {"peer": "peer stores issued by the decode kernel (ortho_b200_forward_gather)" +
+                                            ("" if args.no_deferred else "; each forward waits for its predecessor's flags, the step ends with a wait"),
                                     "nccl": "NCCL all_gather_into_tensor after the kernel", "none": None}[exchange],
                        "l2": f"rotation over {N_COPIES} distinct weight sets (~100 MB each) > 126 MB L2",
                        "timing": "CUDA graph replay per step, CUDA events on the launch stream, max over ranks"},
@@ -531,6 +535,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="multi-GPU output exchange: peer stores from the decode kernel, or an NCCL all-gather")
+    ap.add_argument("--no-deferred", action="store_true",
+                    help="peer exchange: every forward waits for its own exchange instead of the next one waiting for it")
     ap.add_argument("--report", default=None, metavar="PATH",
                     help="instead of the benchmark line: time every configuration on one GPU and write a markdown table")
     args = ap.parse_args()

@@ -193,6 +193,12 @@ ORTHO_B200_API int ortho_b200_comm_export(const ortho_b200_comm *comm, void *han
 ORTHO_B200_API int ortho_b200_comm_connect(ortho_b200_comm *comm, const void *handles);
 ORTHO_B200_API void *ortho_b200_comm_local(const ortho_b200_comm *comm);
 ORTHO_B200_API int ortho_b200_comm_set_timeout_ms(ortho_b200_comm *comm, int64_t ms);
+/* Deferred mode (off by default): a forward_gather only signals its own exchange; the NEXT
+ * forward_gather on the same comm waits for it after its own weight prefetch and before it reads
+ * its input, which hides the flag latency of a chain of layers.  Any other consumer of a gathered
+ * output must be preceded by ortho_b200_comm_wait(comm, stream).  Set identically on every rank. */
+ORTHO_B200_API int ortho_b200_comm_set_deferred(ortho_b200_comm *comm, int on);
+ORTHO_B200_API int ortho_b200_comm_wait(ortho_b200_comm *comm, void *stream);
 ORTHO_B200_API int ortho_b200_comm_destroy(ortho_b200_comm *comm);
 ORTHO_B200_API int ortho_b200_forward_gather(const void *q_weight, const void *q_scales_f16,
                        const void *ortho_values_f16, const int32_t *ortho_col_indices,

@@ -191,6 +191,16 @@ class Comm:
     def set_timeout_ms(self, ms: int) -> None:
         _lib.check(_lib.lib().ortho_b200_comm_set_timeout_ms(self.handle, int(ms)), "ortho_b200_comm_set_timeout_ms")
 
+    def set_deferred(self, on: bool) -> None:
+        """Deferred mode: a forward only signals; the next forward on this comm (or ``wait``) waits."""
+        _lib.check(_lib.lib().ortho_b200_comm_set_deferred(self.handle, 1 if on else 0), "ortho_b200_comm_set_deferred")
+
+    def wait(self) -> None:
+        """Enqueue the wait for the last exchange on the current stream (deferred mode; no-op otherwise)."""
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib().ortho_b200_comm_wait(self.handle, torch.cuda.current_stream(self.device).cuda_stream),
+                       "ortho_b200_comm_wait")
+
     def buffer(self) -> torch.Tensor:
         """The local buffer as a uint8 tensor (outputs of ``forward_gather`` appear in it)."""
         if self._buffer is None:

@@ -73,6 +73,10 @@ def _declare(l):
     l.ortho_b200_comm_local.argtypes = [vp]
     l.ortho_b200_comm_set_timeout_ms.restype = c.c_int
     l.ortho_b200_comm_set_timeout_ms.argtypes = [vp, i64]
+    l.ortho_b200_comm_set_deferred.restype = c.c_int
+    l.ortho_b200_comm_set_deferred.argtypes = [vp, c.c_int]
+    l.ortho_b200_comm_wait.restype = c.c_int
+    l.ortho_b200_comm_wait.argtypes = [vp, vp]
     l.ortho_b200_comm_destroy.restype = c.c_int
     l.ortho_b200_comm_destroy.argtypes = [vp]
     l.ortho_b200_forward_gather.restype = c.c_int
@@ -89,6 +93,7 @@ EXPORTS = [
     "ortho_b200_launch_count", "ortho_b200_query_kernel_status", "ortho_b200_forward_static_scratch",
     "ortho_b200_comm_create", "ortho_b200_comm_export", "ortho_b200_comm_connect", "ortho_b200_comm_local",
     "ortho_b200_comm_set_timeout_ms", "ortho_b200_comm_destroy", "ortho_b200_forward_gather",
+    "ortho_b200_comm_set_deferred", "ortho_b200_comm_wait",
 ]
 
 

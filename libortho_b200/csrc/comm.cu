@@ -30,6 +30,7 @@ struct Comm {
     unsigned char *base[kMaxRanks];   // base[rank] is the local allocation
     bool opened[kMaxRanks];
     bool connected;
+    bool deferred;
     long long timeout_ns;
 };
 
@@ -63,6 +64,12 @@ gather_push_kernel(const GatherView gv, int M, int nloc, long long ldy, int *sta
         }
     }
     if (!gather_signal_and_wait(gv, gridDim.x)) atomicExch(status, 2);
+}
+
+// deferred mode: waits for the peers' flags of this rank's last exchange (one thread)
+__global__ void gather_wait_kernel(const GatherView gv, int *status)
+{
+    if (!gather_wait_previous(gv)) atomicExch(status, 2);
 }
 
 }  // namespace ob
@@ -150,6 +157,32 @@ extern "C" int ortho_b200_comm_set_timeout_ms(ortho_b200_comm *comm, int64_t ms)
     return ORTHO_B200_OK;
 }
 
+extern "C" int ortho_b200_comm_set_deferred(ortho_b200_comm *comm, int on)
+{
+    Comm *cm = as_comm(comm);
+    if (!cm) return ORTHO_B200_ERR_NULL;
+    cm->deferred = on != 0;
+    return ORTHO_B200_OK;
+}
+
+extern "C" int ortho_b200_comm_wait(ortho_b200_comm *comm, void *stream)
+{
+    Comm *cm = as_comm(comm);
+    if (!cm) return ORTHO_B200_ERR_NULL;
+    if (!cm->connected) return ORTHO_B200_ERR_PLAN;
+    if (cm->world <= 1 || !cm->deferred) return ORTHO_B200_OK;
+    GatherView gv;
+    memset(&gv, 0, sizeof(gv));
+    gv.world = cm->world; gv.rank = cm->rank; gv.timeout_ns = cm->timeout_ns; gv.deferred = 1;
+    for (int r = 0; r < cm->world; r++) gv.ctrl[r] = reinterpret_cast<GatherCtrl *>(cm->base[r] + cm->ctrl_off);
+    int *status = kernel_status_word();
+    if (!status) return ORTHO_B200_ERR_CUDA;
+    gather_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(gv, status);
+    OB_CUDA(cudaGetLastError());
+    count_launch();
+    return ORTHO_B200_OK;
+}
+
 extern "C" int ortho_b200_comm_destroy(ortho_b200_comm *comm)
 {
     Comm *cm = as_comm(comm);
@@ -189,6 +222,7 @@ extern "C" int ortho_b200_forward_gather(const void *q_weight, const void *q_sca
     GatherView gv;
     memset(&gv, 0, sizeof(gv));
     gv.world = cm->world; gv.rank = cm->rank; gv.timeout_ns = cm->timeout_ns;
+    gv.deferred = cm->deferred ? 1 : 0;
     for (int r = 0; r < cm->world; r++) {
         gv.y[r] = reinterpret_cast<__half *>(cm->base[r] + y_offset_bytes) + n_offset;
         gv.ctrl[r] = reinterpret_cast<GatherCtrl *>(cm->base[r] + cm->ctrl_off);
@@ -197,6 +231,13 @@ extern "C" int ortho_b200_forward_gather(const void *q_weight, const void *q_sca
     if (!status) return ORTHO_B200_ERR_CUDA;
 
     bool fused = false;
+    // deferred mode: the streaming decode kernel waits for the previous exchange itself; any other
+    // kernel is preceded by the one-thread wait kernel
+    if (cm->deferred && cm->world > 1 && !(N_local > 0 && stream_kernel_selected(M, K))) {
+        gather_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(gv, status);
+        OB_CUDA(cudaGetLastError());
+        count_launch();
+    }
     if (N_local > 0) {
         // the slice is computed by the ordinary forward with the output pitch of the full matrix
         int st = ob::forward_impl(q_weight, q_scales_f16, ortho_values_f16, ortho_col_indices, ortho_row_ptr, nnz,

@@ -378,6 +378,13 @@ static int launch_mt(const FwdArgs &a, const DecodeCfg &c)
     return ORTHO_B200_ERR_SHAPE;
 }
 
+// M <= 16: persistent TMA streaming kernel, unless another kernel was asked for explicitly
+// (its TMA view needs whole 128-byte column blocks per row: K a multiple of 256)
+bool stream_kernel_selected(int64_t M, int64_t K)
+{
+    return M <= g_prefill_above && !g_use_tc && M <= 16 && (K % 256) == 0 && (g_force_stream || g_override.wr == 0);
+}
+
 int launch_decode(const FwdArgs &a)
 {
     if (a.M > ORTHO_B200_DECODE_MAX_M) return ORTHO_B200_ERR_SHAPE;
@@ -385,8 +392,6 @@ int launch_decode(const FwdArgs &a)
         const int st = launch_decode_tc(a);
         if (st != ORTHO_B200_ERR_SHAPE) return st;      // ERR_SHAPE: does not fit that kernel, use the others
     }
-    // M <= 16: persistent TMA streaming kernel, unless the generic tiling was asked for explicitly
-    // (its TMA view needs whole 128-byte column blocks per row: K a multiple of 256)
     if (a.M <= 16 && (a.K % 256) == 0 && (g_force_stream || g_override.wr == 0)) return launch_decode_stream(a);
     const DecodeCfg c = choose(a.M, a.K, a.N);
     if (a.M <= 8) return launch_mt<1>(a, c);

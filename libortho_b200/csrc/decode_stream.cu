@@ -197,6 +197,9 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
     }
 
     griddep_wait();
+    if constexpr (GATHER) {   // deferred exchange: the previous forward's slices must have arrived before X is read
+        if (!gather_wait_previous(gp.gv)) atomicExch(p.status, 2);
+    }
 
     // ---- stage X[:, k_lo:k_hi) once, in unpack pair order ---------------------------------------
     // 16-byte chunk (x0..x7) is stored as (x0,x4,x1,x5,x2,x6,x3,x7); inside a 128-element step the 16

@@ -24,6 +24,8 @@ struct GatherView {
     __half *y[kMaxRanks];          // rank r's output buffer as mapped into this process ([M][ld])
     GatherCtrl *ctrl[kMaxRanks];   // rank r's control block as mapped into this process
     long long timeout_ns;          // bound of the wait for the peers' flags
+    int deferred;                  // 1: a kernel waits for the PREVIOUS exchange before it reads its input and
+                                   // only signals its own; 0: it signals and waits for its own exchange
 };
 
 __device__ __forceinline__ void st_relaxed_sys(int *p, int v) {
@@ -48,6 +50,39 @@ __device__ __forceinline__ int ld_acquire_sys(const int *p) {
 __device__ __forceinline__ void fence_acq_rel_gpu() { asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
 __device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
 
+// One thread: wait (bounded) until every peer's flag has reached epoch `ep`, then read the flags
+// once more with acquire loads so that the peers' slices are ordered before whatever follows.
+__device__ __forceinline__ bool gather_wait_flags(const GatherView &gv, int ep)
+{
+    const GatherCtrl *mine = gv.ctrl[gv.rank];
+    bool ok = true;
+    const unsigned long long t0 = global_timer_ns();
+    for (int r = 0; r < gv.world; r++) {
+        if (r == gv.rank) continue;
+        const int *f = &mine->flag[r];
+        unsigned spins = 0;
+        while (ld_relaxed_sys(f) - ep < 0) {
+            if ((++spins & 63u) == 0 && (long long)(global_timer_ns() - t0) > gv.timeout_ns) { ok = false; break; }
+        }
+    }
+    for (int r = 0; r < gv.world; r++)
+        if (r != gv.rank && ld_acquire_sys(&mine->flag[r]) - ep < 0) ok = false;
+    return ok;
+}
+
+// Deferred mode, consumer side: called by every thread of a CTA after the grid dependency has been
+// resolved (the previous kernel of the stream, which raised this rank's epoch, is complete) and
+// before the CTA reads activations: thread 0 waits for the peers' flags of that epoch.
+__device__ __forceinline__ bool gather_wait_previous(const GatherView &gv)
+{
+    bool ok = true;
+    if (gv.world > 1 && gv.deferred) {
+        if (threadIdx.x == 0) ok = gather_wait_flags(gv, ld_relaxed_sys(&gv.ctrl[gv.rank]->epoch));
+        __syncthreads();
+    }
+    return ok;
+}
+
 // Called by every thread of every CTA once the CTA's stores to all ranks have been issued.
 // `total_ctas` = CTAs of the grid.  Returns (in thread 0 of the last CTA) false when a peer's flag
 // did not arrive in time; the caller records that in the device status word.  Every other thread
@@ -59,6 +94,8 @@ __device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_re
 // relaxed system-scope stores.  A system-scope fence waits for the NVLink round trip of the
 // outstanding peer stores, so there is exactly one on the way out; on the way in the flags are
 // polled with relaxed loads and read once more with an acquire load when they have arrived.
+// In deferred mode the kernel returns after the flag stores: the next kernel of the stream (or
+// ortho_b200_comm_wait) waits for them.
 __device__ __forceinline__ bool gather_signal_and_wait(const GatherView &gv, unsigned total_ctas)
 {
     if (gv.world <= 1) return true;
@@ -73,20 +110,8 @@ __device__ __forceinline__ bool gather_signal_and_wait(const GatherView &gv, uns
     mine->epoch = ep;
     for (int r = 0; r < gv.world; r++)
         if (r != gv.rank) st_relaxed_sys(&gv.ctrl[r]->flag[gv.rank], ep);
-    bool ok = true;
-    const unsigned long long t0 = global_timer_ns();
-    for (int r = 0; r < gv.world; r++) {
-        if (r == gv.rank) continue;
-        const int *f = &mine->flag[r];
-        unsigned spins = 0;
-        while (ld_relaxed_sys(f) - ep < 0) {
-            if ((++spins & 63u) == 0 && (long long)(global_timer_ns() - t0) > gv.timeout_ns) { ok = false; break; }
-        }
-    }
-    // acquire side: the peers' slices are ordered before whatever follows
-    for (int r = 0; r < gv.world; r++)
-        if (r != gv.rank && ld_acquire_sys(&mine->flag[r]) - ep < 0) ok = false;
-    return ok;
+    if (gv.deferred) return true;
+    return gather_wait_flags(gv, ep);
 }
 
 }  // namespace ob

@@ -37,6 +37,21 @@ def main():
             d = (y.float() - ref.float()).abs().max().item()
             rel = ((y.float() - ref.float()).norm() / ref.float().norm()).item()
             assert d <= 2e-2 and rel <= 1e-3, f"rank {rank}: K={K} N={N} M={M} it={it}: max_abs={d} rel={rel}"
+        # deferred mode: a forward only signals; the next forward on the comm, or comm.wait(), waits
+        sh._comm.set_deferred(True)
+        xa, xb = wl.make_input(M, K, seed=301).to(dev), wl.make_input(M, K, seed=302).to(dev)
+        for it in range(4):
+            ya = sh(xa)                           # region 0
+            yb = sh(xb)                           # region 1; its kernel waits for ya's exchange
+            sh._comm.wait()                       # yb's exchange
+            ra, rb = full(xa), full(xb)
+            torch.cuda.synchronize()
+            assert _lib.lib().ortho_b200_query_kernel_status() == 0, "a deferred gather wait timed out"
+            for y, ref in ((ya, ra), (yb, rb)):
+                d = (y.float() - ref.float()).abs().max().item()
+                rel = ((y.float() - ref.float()).norm() / ref.float().norm()).item()
+                assert d <= 2e-2 and rel <= 1e-3, f"rank {rank}: deferred K={K} N={N} M={M} it={it}: max_abs={d} rel={rel}"
+        sh._comm.set_deferred(False)
         dist.barrier()
     torch.cuda.synchronize()
     open(os.path.join(sys.argv[1], f"ok{rank}"), "w").write("ok")
