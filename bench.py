@@ -500,6 +500,26 @@ def run_report(args):
     sieve1 = wl.make_sieve_layer(device=dev, sparsity_target=0.01)
     measure("4 (supplementary: keep top 1 %)", lambda c: sieve1, [1, 2048], [0.25, 1.0])
 
+    # device-side packer (the producer of the layout): HBM-bound, W read once from DRAM (row re-read from L2)
+    pack_rows = []
+    for (K, N) in [(4096, 4096), (8192, 8192), (8192, 28672)]:
+        w = torch.randn(N, K, device=dev) * 0.02
+        wo = torch.where(torch.rand(N, K, device=dev) < 0.003, torch.randn(N, K, device=dev) * 0.05, torch.zeros((), device=dev))
+        for name, fn, nbytes in (("pack_base", lambda: _C_ops.pack_base(w), N * K * 4 + N * K // 2 + 2 * N),
+                                 ("pack_ortho_csr (count + scan + fill)", lambda: _C_ops.pack_ortho_csr(wo), 2 * N * K * 4)):
+            fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(5):
+                fn()
+            e1.record()
+            e1.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / 5
+            pack_rows.append(f"| {name} | {N}x{K} FP32 | {us:.0f} | {nbytes / us / 1e3:.0f} | {100 * nbytes / us / 1e3 / pk['hbm_gbs']:.1f} |")
+        del w, wo
+        torch.cuda.empty_cache()
+
     # the reference's CPU forward on configuration 0 (1 thread and all threads)
     import oracle
     impl = "reference_fast" if oracle.available("reference_fast") else "port"
@@ -519,7 +539,10 @@ def run_report(args):
             f"({pk['hbm_gbs']:.0f} GB/s) | TFLOP/s | % of measured sustained tensor ({pk['tf_sustained']:.0f} TF) |")
     sep = "|" + "---|" * 11
     out = ["# All configurations, one B200 (`python bench.py --report <path>`)", "", head, sep, *rows, "",
-           "CPU rows (host of the same box):", "", head + " note |", sep + "---|", *cpu, ""]
+           "CPU rows (host of the same box):", "", head + " note |", sep + "---|", *cpu, "",
+           "Device-side packer (algorithmic bytes: W read once + outputs; the CSR build reads W twice; includes the host "
+           "read-back of nnz and the output allocations):", "",
+           "| step | input | us | GB/s | % of measured HBM |", "|---|---|---|---|---|", *pack_rows, ""]
     with open(args.report, "w") as f:
         f.write("\n".join(out))
     print("\n".join(out))

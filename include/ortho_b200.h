@@ -210,6 +210,25 @@ ORTHO_B200_API int ortho_b200_forward_gather(const void *q_weight, const void *q
                        ortho_b200_comm *comm, int64_t y_offset_bytes,
                        int64_t N_total, int64_t n_offset, void *stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Device-side packer: produces the buffers the forward consumes from FP32 weights that are already
+ * on the GPU.  Replaces the torch chain of OrthoLinear.load_from_weights
+ * (torch_bind/ortho_linear.py:79-128) and pack_ortho_sparse(..., "csr") (tools/sieve.py:119-152),
+ * with bit-identical results:
+ *   pack_base : scales = max(rowmax|W| / 7, 1e-6) unless scales_in (FP32, [N]) is given;
+ *               w_int = clamp(round_half_even(W / scale), -8, 7); two per byte, even index low.
+ *               Writes q_weight_out [N, K/2] and q_scales_f16_out [N].  K a multiple of 8.
+ *   csr_count : row_ptr_out [N+1] of the positions with W_ortho != 0 (row_ptr_out[N] = nnz;
+ *               read it back to size the next call's outputs).
+ *   csr_fill  : col_out / val_f16_out [nnz] in row-major order, values rounded to FP16.
+ * W and W_ortho are [N, K] FP32, row-major, 16-byte aligned.
+ * ------------------------------------------------------------------------------------------- */
+ORTHO_B200_API int ortho_b200_pack_base(const float *w, int64_t N, int64_t K, const float *scales_in,
+                       void *q_weight_out, void *q_scales_f16_out, void *stream);
+ORTHO_B200_API int ortho_b200_csr_count(const float *w_ortho, int64_t N, int64_t K, int32_t *row_ptr_out, void *stream);
+ORTHO_B200_API int ortho_b200_csr_fill(const float *w_ortho, int64_t N, int64_t K, const int32_t *row_ptr,
+                       int32_t *col_out, void *val_f16_out, void *stream);
+
 /* Synchronises the device and reports whether any kernel of this library gave up on a bounded
  * wait since the last query (ERR_KERNEL, and the flag is cleared) or not (OK).  Replaces the
  * cudaDeviceSynchronize + error check at the end of the reference dispatcher

@@ -264,3 +264,46 @@ def forward_gather(q_weight: torch.Tensor, q_scales: torch.Tensor, ortho_values:
             torch.cuda.current_stream(dev).cuda_stream)
     _lib.check(st, "ortho_b200_forward_gather")
     return comm.output(y_offset_bytes, M, N_total)
+
+
+def pack_base(weight: torch.Tensor, scales: Optional[torch.Tensor] = None):
+    """Device-side INT4 quantise + pack of an FP32 ``[N, K]`` CUDA tensor: ``(q_weight u8 [N, K/2],
+    q_scales f16 [N])``, bit-identical to the torch chain of ``OrthoLinear.load_from_weights``."""
+    if not weight.is_cuda or weight.dtype != torch.float32 or weight.dim() != 2:
+        raise TypeError("weight must be a 2-D float32 CUDA tensor")
+    w = weight.contiguous()
+    N, K = w.shape
+    dev = w.device
+    s_in = None
+    if scales is not None:
+        s_in = scales.to(device=dev, dtype=torch.float32).contiguous()
+        if s_in.numel() != N:
+            raise ValueError("scales must have one entry per output row")
+    q = torch.empty(N, K // 2, dtype=torch.uint8, device=dev)
+    qs = torch.empty(N, dtype=torch.float16, device=dev)
+    with torch.cuda.device(dev):
+        st = _lib.lib().ortho_b200_pack_base(w.data_ptr(), N, K, s_in.data_ptr() if s_in is not None else None,
+                                             q.data_ptr(), qs.data_ptr(), torch.cuda.current_stream(dev).cuda_stream)
+    _lib.check(st, "ortho_b200_pack_base")
+    return q, qs
+
+
+def pack_ortho_csr(w_ortho: torch.Tensor):
+    """Device-side CSR build of an FP32 ``[N, K]`` CUDA tensor: ``(row_ptr i32 [N+1], col i32 [nnz],
+    values f16 [nnz])`` in row-major order (one host read of nnz between the two passes)."""
+    if not w_ortho.is_cuda or w_ortho.dtype != torch.float32 or w_ortho.dim() != 2:
+        raise TypeError("w_ortho must be a 2-D float32 CUDA tensor")
+    w = w_ortho.contiguous()
+    N, K = w.shape
+    dev = w.device
+    row_ptr = torch.empty(N + 1, dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        _lib.check(_lib.lib().ortho_b200_csr_count(w.data_ptr(), N, K, row_ptr.data_ptr(), stream), "ortho_b200_csr_count")
+        nnz = int(row_ptr[N].item())
+        col = torch.empty(nnz, dtype=torch.int32, device=dev)
+        val = torch.empty(nnz, dtype=torch.float16, device=dev)
+        if nnz:
+            _lib.check(_lib.lib().ortho_b200_csr_fill(w.data_ptr(), N, K, row_ptr.data_ptr(), col.data_ptr(), val.data_ptr(),
+                                                     stream), "ortho_b200_csr_fill")
+    return row_ptr, col, val

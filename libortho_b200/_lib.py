@@ -63,6 +63,12 @@ def _declare(l):
     l.ortho_b200_query_kernel_status.argtypes = []
     l.ortho_b200_launch_count.restype = i64
     l.ortho_b200_launch_count.argtypes = []
+    l.ortho_b200_pack_base.restype = c.c_int
+    l.ortho_b200_pack_base.argtypes = [vp, i64, i64, vp, vp, vp, vp]
+    l.ortho_b200_csr_count.restype = c.c_int
+    l.ortho_b200_csr_count.argtypes = [vp, i64, i64, vp, vp]
+    l.ortho_b200_csr_fill.restype = c.c_int
+    l.ortho_b200_csr_fill.argtypes = [vp, i64, i64, vp, vp, vp, vp]
     l.ortho_b200_comm_create.restype = c.c_int
     l.ortho_b200_comm_create.argtypes = [c.c_int, c.c_int, i64, c.POINTER(vp)]
     l.ortho_b200_comm_export.restype = c.c_int
@@ -94,6 +100,7 @@ EXPORTS = [
     "ortho_b200_comm_create", "ortho_b200_comm_export", "ortho_b200_comm_connect", "ortho_b200_comm_local",
     "ortho_b200_comm_set_timeout_ms", "ortho_b200_comm_destroy", "ortho_b200_forward_gather",
     "ortho_b200_comm_set_deferred", "ortho_b200_comm_wait",
+    "ortho_b200_pack_base", "ortho_b200_csr_count", "ortho_b200_csr_fill",
 ]
 
 

@@ -64,6 +64,13 @@ class OrthoLinear(nn.Module):
         clamped to [-8, 7], the division using the FP32 scale while the stored scale is FP16;
         two elements per byte, even flat index in the low nibble."""
         device = ortho_weight.device
+        if (base_weight.is_cuda and ortho_weight.is_cuda and base_weight.dtype == torch.float32
+                and ortho_weight.dtype == torch.float32 and self.in_features % 8 == 0):
+            # weights already on the GPU: the device-side packer produces the same bits as the chain below
+            self.base_weight.data, self.base_scales.data = _C.pack_base(base_weight, base_scales)
+            self.ortho_row_ptr, self.ortho_col_indices, self.ortho_values = _C.pack_ortho_csr(ortho_weight)
+            self._invalidate()
+            return
         if base_scales is None:
             scales = (base_weight.abs().max(dim=1)[0] / 7.0).clamp(min=1e-6)
         else:
