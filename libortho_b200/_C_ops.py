@@ -124,7 +124,9 @@ def forward(q_weight: torch.Tensor, q_scales: torch.Tensor, ortho_values: torch.
             raise TypeError("ortho buffers must be float16 / int32 / int32")
         if ortho_row_ptr.numel() != N + 1 or ortho_col_indices.numel() != nnz:
             raise ValueError("CSR arrays have inconsistent sizes")
-    need = workspace_bytes(M, K, N, plan) if (nnz and alpha > 0) else 0
+    # the sparse pre-pass needs its scratch; the tensor-core regime (more than 24 tokens) also uses scratch for
+    # the split-K of its last wave when it is given some
+    need = workspace_bytes(M, K, N, plan) if ((nnz and alpha > 0) or M > 24) else 0
     ws_ptr, ws_bytes = None, 0
     if need:
         if workspace is None or workspace.numel() * workspace.element_size() < need:

@@ -96,6 +96,16 @@ extern "C" int ortho_b200_query_kernel_status(void)
     return ORTHO_B200_OK;
 }
 
+namespace ob {
+int64_t prefill_min_workspace_bytes(int64_t M, int64_t K, int64_t N);
+// scratch a forward with an active ortho term cannot do without
+int64_t min_workspace_bytes(int64_t M, int64_t K, int64_t N)
+{
+    if (M <= g_prefill_above) return decode_tc_workspace_bytes(M, N);
+    return prefill_min_workspace_bytes(M, K, N);
+}
+}  // namespace ob
+
 extern "C" int64_t ortho_b200_workspace_bytes(int64_t M, int64_t K, int64_t N)
 {
     if (M <= g_prefill_above) return decode_tc_workspace_bytes(M, N);

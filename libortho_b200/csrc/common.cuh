@@ -161,6 +161,7 @@ int forward_impl(const void *q_weight, const void *q_scales_f16, const void *ort
                  int64_t ldy, const struct GatherView *gv, bool *gather_fused);
 int launch_prefill(const FwdArgs &a);
 int64_t prefill_workspace_bytes(int64_t M, int64_t K, int64_t N);
+int64_t min_workspace_bytes(int64_t M, int64_t K, int64_t N);
 int set_decode_config(int wr, int wk, int u, int s);
 bool stream_kernel_selected(int64_t M, int64_t K);   // the forward of (M, K) will run decode_stream_kernel
 extern int g_prefill_above;   // forwards with more tokens than this use the prefill kernel (decode.cu)

@@ -62,7 +62,25 @@ struct Params {
     // sparse term computed ahead by spmm_ortho_kernel: O[n][m] FP32 with row pitch Mp (rows without
     // entries are never written and never read)
     const int32_t *row_ptr; const float *o; int Mp; float alpha; int has_ortho;
+    // split-K of the last, partial wave: tiles [full_tiles, full_tiles + n_split) are each worked on by two
+    // CTAs (k-blocks [0, kh) and [kh, kblocks)); the second one leaves its raw FP32 accumulators in
+    // part[j][128][TM] and raises flags[j], the first one adds them in its epilogue
+    int full_tiles, n_split, kh;
+    float *part; int *flags;
 };
+
+struct Unit { int t, kb0, kb1, role, j; };      // role 0: whole tile, 1: first K half (final), 2: second K half (partial)
+__device__ __forceinline__ Unit unit_of(const Params &p, int u) {
+    Unit r;
+    if (u < p.full_tiles) { r.t = u; r.kb0 = 0; r.kb1 = p.kblocks; r.role = 0; r.j = 0; return r; }
+    const int v = u - p.full_tiles;
+    r.j = v >> 1; r.t = p.full_tiles + r.j;
+    if (v & 1) { r.kb0 = p.kh; r.kb1 = p.kblocks; r.role = 2; } else { r.kb0 = 0; r.kb1 = p.kh; r.role = 1; }
+    return r;
+}
+constexpr int kMaxSplit = 74;                               // at most half of the SMs' worth of split tiles
+constexpr size_t kSplitPartBytes = (size_t)kMaxSplit * TH * TM * 4;
+constexpr size_t kSplitBytes = kSplitPartBytes + 1024;      // partial tiles, then the flag words
 
 struct Smem {
     uint64_t x_full[STAGES], x_empty[STAGES];
@@ -87,7 +105,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     Smem *sm = reinterpret_cast<Smem *>(ys_base + NH * YS_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int ntiles = p.tiles_n * p.tiles_m;
+    const int nunits = p.full_tiles + 2 * p.n_split;       // work units of the grid (a split tile counts twice)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(&sm->x_full[s], 1); mbar_init(&sm->x_empty[s], 1); }
@@ -114,9 +132,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         // ================= TMA producer =================
         if (lane == 0) {
             int s = 0, wsi = 0; uint32_t ph = 0, wph = 0;
-            for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
-                const int nt = t % p.tiles_n, mt = t / p.tiles_n;
-                for (int kb = 0; kb < p.kblocks; kb++) {
+            for (int u = blockIdx.x; u < nunits; u += gridDim.x) {
+                const Unit un = unit_of(p, u);
+                const int nt = un.t % p.tiles_n, mt = un.t / p.tiles_n;
+                for (int kb = un.kb0; kb < un.kb1; kb++) {
                     if ((kb % WKB) == 0) {      // packed weights: one 128-byte-wide load per WKB k-blocks
                         wait(&sm->w_empty[wsi], wph ^ 1u);
                         mbar_arrive_expect_tx(&sm->w_full[wsi], W_BYTES);
@@ -137,16 +156,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
             const uint64_t desc0 = umma_desc_sw128(smem_u32(xs));     // stage s, k step kk: + s*X_BYTES/16 + 2*kk
             int s = 0, as = 0; uint32_t ph = 0, aph = 0;
             int it = 0;
-            for (int t = blockIdx.x; t < ntiles; t += gridDim.x, it++) {
+            for (int u = blockIdx.x; u < nunits; u += gridDim.x, it++) {
+                const Unit un = unit_of(p, u);
                 wait(&sm->d_empty, (uint32_t)((it & 1) ^ 1));     // the epilogue has drained the accumulators
                 tc_fence_after();
-                for (int kb = 0; kb < p.kblocks; kb++) {
+                for (int kb = un.kb0; kb < un.kb1; kb++) {
                     wait(&sm->x_full[s], ph);
                     wait(&sm->a_full[as], aph);
                     tc_fence_after();
                     const uint32_t a_tmem = tmem + (uint32_t)(A_COL0 + as * A_STAGE_COLS);
                     const uint64_t bdesc = desc0 + (uint64_t)(s * (X_BYTES >> 4));
-                    const uint32_t acc0 = (uint32_t)(kb != 0);
+                    const uint32_t acc0 = (uint32_t)(kb != un.kb0);
 #pragma unroll
                     for (int kk = 0; kk < KB / 16; kk++) {
 #pragma unroll
@@ -169,14 +189,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         const int row = h * TH + q * 32 + lane;        // output row inside the tile
         int wsi = 0, as = 0; uint32_t wph = 0, aph = 0;
         const uint32_t swz = (uint32_t)(row & 7);      // 128-byte swizzle: 16-byte chunk c sits at c ^ (row & 7)
-        for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
-            for (int kb = 0; kb < p.kblocks; kb++) {
+        for (int u = blockIdx.x; u < nunits; u += gridDim.x) {
+            const Unit un = unit_of(p, u);
+            for (int kb = un.kb0; kb < un.kb1; kb++) {
                 const int sub = kb % WKB;                   // which 32-byte slice of the 128-byte weight row
                 if (sub == 0) wait(&sm->w_full[wsi], wph);
                 const unsigned char *wrow = ws + (size_t)wsi * W_BYTES + row * 128;
                 const uint4 w0 = *reinterpret_cast<const uint4 *>(wrow + ((((uint32_t)(2 * sub)) ^ swz) << 4));
                 const uint4 w1 = *reinterpret_cast<const uint4 *>(wrow + ((((uint32_t)(2 * sub + 1)) ^ swz) << 4));
-                if (sub == WKB - 1 || kb == p.kblocks - 1) {   // last slice of this weight stage: hand it back
+                if (sub == WKB - 1 || kb == un.kb1 - 1) {   // last slice of this weight stage: hand it back
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&sm->w_empty[wsi]);
                     if (++wsi == WSTAGES) { wsi = 0; wph ^= 1u; }
@@ -207,9 +228,33 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         __half *ys = reinterpret_cast<__half *>(ys_base + h * YS_BYTES);
         const bool vec_ok = (p.N % 8) == 0 && (p.ldy % 8) == 0 && (reinterpret_cast<uintptr_t>(p.y) & 15u) == 0;
         int it = 0;
-        for (int t = blockIdx.x; t < ntiles; t += gridDim.x, it++) {
-            const int nt = t % p.tiles_n, mt = t / p.tiles_n;
+        for (int u = blockIdx.x; u < nunits; u += gridDim.x, it++) {
+            const Unit un = unit_of(p, u);
+            const int nt = un.t % p.tiles_n, mt = un.t / p.tiles_n;
             const int nbase = nt * TN + h * TH;
+            if (un.role == 2) {
+                // second K half of a split tile: raw accumulators to the partial buffer, then the flag
+                float *prow = p.part + ((size_t)un.j * TH + (size_t)(q * 32 + lane)) * TM;
+                wait(&sm->d_full, (uint32_t)(it & 1));
+                tc_fence_after();
+                for (int c = 0; c < TM / 32; c++) {
+                    uint32_t r[32];
+                    tmem_ld_32x32b_x32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(h * TM + c * 32), r);
+                    tmem_ld_wait();
+                    float4 *dst = reinterpret_cast<float4 *>(prow + c * 32);
+#pragma unroll
+                    for (int j4 = 0; j4 < 8; j4++)
+                        dst[j4] = make_float4(__uint_as_float(r[4 * j4]), __uint_as_float(r[4 * j4 + 1]),
+                                              __uint_as_float(r[4 * j4 + 2]), __uint_as_float(r[4 * j4 + 3]));
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sm->d_empty);
+                __threadfence();
+                named_bar_sync(1 + h, 128);
+                if (et == 0) asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p.flags + un.j), "r"(1) : "memory");
+                continue;
+            }
             const int n = nbase + q * 32 + lane;
             const float sc = (n < p.N) ? __half2float(p.scales[n]) : 0.f;
             const float *orow = nullptr;               // this row's sparse term, if it has any entries
@@ -225,10 +270,35 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
             if (orow) load_o(0);
             wait(&sm->d_full, (uint32_t)(it & 1));
             tc_fence_after();
+            const float *prow = nullptr;               // first K half of a split tile: the partner's partial sums
+            if (un.role == 1) {
+                if (et == 0 && !dead) {                // bounded wait for the partner's flag
+                    int seen = 0;
+                    for (unsigned spin = 0; spin < (1u << 22); spin++) {
+                        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(p.flags + un.j) : "memory");
+                        if (seen) break;
+                        __nanosleep(64);
+                    }
+                    if (!seen) atomicExch(p.status, 1);
+                }
+                named_bar_sync(1 + h, 128);
+                prow = p.part + ((size_t)un.j * TH + (size_t)(q * 32 + lane)) * TM;
+            }
             for (int c = 0; c < TM / 32; c++) {
                 uint32_t r[32];
                 tmem_ld_32x32b_x32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(h * TM + c * 32), r);
                 tmem_ld_wait();
+                if (prow) {
+                    const float4 *p4 = reinterpret_cast<const float4 *>(prow + c * 32);
+#pragma unroll
+                    for (int j4 = 0; j4 < 8; j4++) {
+                        const float4 pv = __ldcg(p4 + j4);
+                        r[4 * j4 + 0] = __float_as_uint(__uint_as_float(r[4 * j4 + 0]) + pv.x);
+                        r[4 * j4 + 1] = __float_as_uint(__uint_as_float(r[4 * j4 + 1]) + pv.y);
+                        r[4 * j4 + 2] = __float_as_uint(__uint_as_float(r[4 * j4 + 2]) + pv.z);
+                        r[4 * j4 + 3] = __float_as_uint(__uint_as_float(r[4 * j4 + 3]) + pv.w);
+                    }
+                }
                 if (orow) {                            // y = scale * D + alpha * O, one FP16 rounding
 #pragma unroll
                     for (int j4 = 0; j4 < 8; j4++) {
@@ -273,7 +343,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
 int64_t spmm_workspace_bytes(int64_t M, int64_t K, int64_t N);            // spmm.cu
 int launch_spmm(const FwdArgs &a, const float **o_out, int *mp_out);
 
-int64_t prefill_workspace_bytes(int64_t M, int64_t K, int64_t N) { return spmm_workspace_bytes(M, K, N); }
+// what the sparse pre-pass needs (the forward refuses less when the ortho term is active) ...
+int64_t prefill_min_workspace_bytes(int64_t M, int64_t K, int64_t N) { return spmm_workspace_bytes(M, K, N); }
+// ... and what ortho_b200_workspace_bytes() reports: room behind it for the split-K partial tiles, which the
+// forward uses when it is there (also for base-only calls) and does without otherwise
+int64_t prefill_workspace_bytes(int64_t M, int64_t K, int64_t N)
+{
+    return ((spmm_workspace_bytes(M, K, N) + 255) / 256) * 256 + (int64_t)pf::kSplitBytes;
+}
 
 int launch_prefill(const FwdArgs &a)
 {
@@ -308,8 +385,27 @@ int launch_prefill(const FwdArgs &a)
         OB_CUDA(cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev));
         attr_set = true;
     }
-    const int ntiles = p.tiles_n * p.tiles_m;
-    const int grid = ntiles < num_sms ? ntiles : num_sms;
+    // split-K of the last partial wave: worth it when the leftover tiles occupy at most half of the SMs
+    // and the caller's workspace has room for their partial sums behind the sparse pre-pass's part
+    {
+        const int T = p.tiles_n * p.tiles_m;
+        const int G = T < num_sms ? T : num_sms;
+        const int L = T % G == 0 ? (T < num_sms ? T : 0) : T % G;       // tiles of the last wave
+        const int64_t nv = (a.has_ortho && a.plan && a.ortho.entries) ? a.plan->n_virtual : 0;
+        const int64_t off = a.has_ortho ? ((spmm_workspace_bytes(a.M, a.K, a.N + nv) + 255) / 256) * 256 : 0;
+        p.full_tiles = T; p.n_split = 0; p.kh = 0; p.part = nullptr; p.flags = nullptr;
+        const int kh = (p.kblocks / 2 / WKB) * WKB;
+        if (L > 0 && 2 * L <= num_sms && L <= kMaxSplit && kh >= WKB && a.workspace &&
+            ((uintptr_t)a.workspace & 255u) == 0 && a.workspace_bytes >= off + (int64_t)kSplitBytes) {
+            unsigned char *base = reinterpret_cast<unsigned char *>(a.workspace) + off;
+            p.full_tiles = T - L; p.n_split = L; p.kh = kh;
+            p.part = reinterpret_cast<float *>(base);
+            p.flags = reinterpret_cast<int *>(base + kSplitPartBytes);
+            OB_CUDA(cudaMemsetAsync(p.flags, 0, (size_t)L * sizeof(int), a.stream));
+        }
+    }
+    const int nunits = p.full_tiles + 2 * p.n_split;
+    const int grid = nunits < num_sms ? nunits : num_sms;
     prefill_kernel<<<grid, NWARPS * 32, kSmemBytes, a.stream>>>(xmap, wmap, p);
     count_launch();
     OB_CUDA(cudaGetLastError());

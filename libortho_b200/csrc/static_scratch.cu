@@ -60,7 +60,7 @@ extern "C" int ortho_b200_forward_static_scratch(const void *q_weight, const voi
     const bool has_ortho = (alpha > 0.0f) && (nnz > 0);
     if (has_ortho && (!ortho_values_f16 || !ortho_col_indices || !ortho_row_ptr)) return ORTHO_B200_ERR_NULL;
 
-    const int64_t need = has_ortho ? ortho_b200_workspace_bytes(M, K, N) : 0;
+    const int64_t need = has_ortho ? min_workspace_bytes(M, K, N) : 0;
     if (need > (int64_t)ORTHO_B200_STATIC_SCRATCH_BYTES) return ORTHO_B200_ERR_SCRATCH_LIMIT;
 
     int major = 0, dev = 0;

@@ -124,9 +124,10 @@ class OrthoLinear(nn.Module):
         return self._plan
 
     def _get_workspace(self, M: int) -> Optional[torch.Tensor]:
-        if self.alpha <= 0 or self.ortho_values.numel() == 0:
+        sparse = self.alpha > 0 and self.ortho_values.numel() > 0
+        if not sparse and M <= 24:
             return None
-        need = _C.workspace_bytes(M, self.in_features, self.out_features, self._get_plan())
+        need = _C.workspace_bytes(M, self.in_features, self.out_features, self._get_plan() if sparse else None)
         if need == 0:
             return None
         if (self._workspace is None or self._workspace.numel() < need
