@@ -47,7 +47,8 @@ constexpr int YS_PITCH = TH + 8;         // halves per staged token row (pad aga
 constexpr int YS_BYTES = 32 * YS_PITCH * 2;
 constexpr int CONV_WARPS = 4 * NH;       // one converter thread per output row of the tile
 constexpr int EPI_WARP0 = 2 + CONV_WARPS;
-constexpr int EPI_WARPS = 4 * NH;        // one epilogue warp set per accumulator
+constexpr int ESETS = 2;                 // epilogue warp sets per accumulator: set e drains the 32-token chunks c = e, e + 2, ...
+constexpr int EPI_WARPS = 4 * NH * ESETS;
 constexpr int NWARPS = EPI_WARP0 + EPI_WARPS;
 constexpr int TMEM_COLS = 512;
 constexpr int A_COL0 = NH * TM;          // accumulators occupy [0, NH*TM); converted weights follow
@@ -90,7 +91,7 @@ struct Smem {
     uint32_t tmem_base;
 };
 
-constexpr size_t kSmemBytes = 1024 + (size_t)STAGES * X_BYTES + (size_t)WSTAGES * W_BYTES + NH * YS_BYTES + sizeof(Smem) + 256;
+constexpr size_t kSmemBytes = 1024 + (size_t)STAGES * X_BYTES + (size_t)WSTAGES * W_BYTES + NH * ESETS * YS_BYTES + sizeof(Smem) + 256;
 }  // namespace pf
 
 __global__ void __launch_bounds__(pf::NWARPS * 32, 1)
@@ -102,7 +103,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     unsigned char *xs = base;                                       // STAGES x 16 KB, 1 KB aligned
     unsigned char *ws = xs + (size_t)STAGES * X_BYTES;              // WSTAGES x 32 KB, 1 KB aligned
     unsigned char *ys_base = ws + (size_t)WSTAGES * W_BYTES;        // NH staging tiles for the transposed store
-    Smem *sm = reinterpret_cast<Smem *>(ys_base + NH * YS_BYTES);
+    Smem *sm = reinterpret_cast<Smem *>(ys_base + NH * ESETS * YS_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nunits = p.full_tiles + 2 * p.n_split;       // work units of the grid (a split tile counts twice)
@@ -223,9 +224,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     } else {
         // ================= epilogue: TMEM -> scale -> FP16 -> shared (transpose) -> global =================
         const int q = warp & 3;
-        const int h = (warp - EPI_WARP0) >> 2;         // accumulator handled by this warp set
+        const int h = 0;                               // accumulator handled by this warp set (NH == 1)
+        const int eset = (warp - EPI_WARP0) >> 2;      // which set of four warps: it drains chunks eset, eset + ESETS, ...
         const int et = ((warp - EPI_WARP0) & 3) * 32 + lane;   // 0..127 inside the set
-        __half *ys = reinterpret_cast<__half *>(ys_base + h * YS_BYTES);
+        __half *ys = reinterpret_cast<__half *>(ys_base + eset * YS_BYTES);
+        static_assert(NH == 1, "the epilogue warp sets are laid out for one accumulator");
         const bool vec_ok = (p.N % 8) == 0 && (p.ldy % 8) == 0 && (reinterpret_cast<uintptr_t>(p.y) & 15u) == 0;
         int it = 0;
         for (int u = blockIdx.x; u < nunits; u += gridDim.x, it++) {
@@ -237,7 +240,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                 float *prow = p.part + ((size_t)un.j * TH + (size_t)(q * 32 + lane)) * TM;
                 wait(&sm->d_full, (uint32_t)(it & 1));
                 tc_fence_after();
-                for (int c = 0; c < TM / 32; c++) {
+                for (int c = eset; c < TM / 32; c += ESETS) {
                     uint32_t r[32];
                     tmem_ld_32x32b_x32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(h * TM + c * 32), r);
                     tmem_ld_wait();
@@ -251,8 +254,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sm->d_empty);
                 __threadfence();
-                named_bar_sync(1 + h, 128);
-                if (et == 0) asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p.flags + un.j), "r"(1) : "memory");
+                named_bar_sync(1 + eset, 128);
+                // every set counts itself in; the partner waits for all ESETS of them
+                if (et == 0) asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p.flags + un.j), "r"(1) : "memory");
                 continue;
             }
             const int n = nbase + q * 32 + lane;
@@ -267,7 +271,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
 #pragma unroll
                 for (int j4 = 0; j4 < 8; j4++) ov[j4] = o4[j4];
             };
-            if (orow) load_o(0);
+            if (orow) load_o(eset);
             wait(&sm->d_full, (uint32_t)(it & 1));
             tc_fence_after();
             const float *prow = nullptr;               // first K half of a split tile: the partner's partial sums
@@ -276,28 +280,35 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                     int seen = 0;
                     for (unsigned spin = 0; spin < (1u << 22); spin++) {
                         asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(p.flags + un.j) : "memory");
-                        if (seen) break;
+                        if (seen >= ESETS) break;
                         __nanosleep(64);
                     }
-                    if (!seen) atomicExch(p.status, 1);
+                    if (seen < ESETS) atomicExch(p.status, 1);
                 }
-                named_bar_sync(1 + h, 128);
+                named_bar_sync(1 + eset, 128);
                 prow = p.part + ((size_t)un.j * TH + (size_t)(q * 32 + lane)) * TM;
             }
-            for (int c = 0; c < TM / 32; c++) {
+            // the partner's partial sums are fetched one chunk ahead, like the sparse term
+            float4 pv[8];
+            auto load_p = [&](int c) {
+                const float4 *p4 = reinterpret_cast<const float4 *>(prow + c * 32);
+#pragma unroll
+                for (int j4 = 0; j4 < 8; j4++) pv[j4] = __ldcg(p4 + j4);
+            };
+            if (prow) load_p(eset);
+            for (int c = eset; c < TM / 32; c += ESETS) {
                 uint32_t r[32];
                 tmem_ld_32x32b_x32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(h * TM + c * 32), r);
                 tmem_ld_wait();
                 if (prow) {
-                    const float4 *p4 = reinterpret_cast<const float4 *>(prow + c * 32);
 #pragma unroll
                     for (int j4 = 0; j4 < 8; j4++) {
-                        const float4 pv = __ldcg(p4 + j4);
-                        r[4 * j4 + 0] = __float_as_uint(__uint_as_float(r[4 * j4 + 0]) + pv.x);
-                        r[4 * j4 + 1] = __float_as_uint(__uint_as_float(r[4 * j4 + 1]) + pv.y);
-                        r[4 * j4 + 2] = __float_as_uint(__uint_as_float(r[4 * j4 + 2]) + pv.z);
-                        r[4 * j4 + 3] = __float_as_uint(__uint_as_float(r[4 * j4 + 3]) + pv.w);
+                        r[4 * j4 + 0] = __float_as_uint(__uint_as_float(r[4 * j4 + 0]) + pv[j4].x);
+                        r[4 * j4 + 1] = __float_as_uint(__uint_as_float(r[4 * j4 + 1]) + pv[j4].y);
+                        r[4 * j4 + 2] = __float_as_uint(__uint_as_float(r[4 * j4 + 2]) + pv[j4].z);
+                        r[4 * j4 + 3] = __float_as_uint(__uint_as_float(r[4 * j4 + 3]) + pv[j4].w);
                     }
+                    if (c + ESETS < TM / 32) load_p(c + ESETS);
                 }
                 if (orow) {                            // y = scale * D + alpha * O, one FP16 rounding
 #pragma unroll
@@ -307,12 +318,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                         ys[(4 * j4 + 2) * YS_PITCH + q * 32 + lane] = __float2half_rn(fmaf(p.alpha, ov[j4].z, __uint_as_float(r[4 * j4 + 2]) * sc));
                         ys[(4 * j4 + 3) * YS_PITCH + q * 32 + lane] = __float2half_rn(fmaf(p.alpha, ov[j4].w, __uint_as_float(r[4 * j4 + 3]) * sc));
                     }
-                    if (c + 1 < TM / 32) load_o(c + 1);
+                    if (c + ESETS < TM / 32) load_o(c + ESETS);
                 } else {
 #pragma unroll
                     for (int j = 0; j < 32; j++) ys[j * YS_PITCH + q * 32 + lane] = __float2half_rn(__uint_as_float(r[j]) * sc);
                 }
-                named_bar_sync(1 + h, 128);
+                named_bar_sync(1 + eset, 128);
 #pragma unroll
                 for (int i2 = 0; i2 < 4; i2++) {
                     const int id = i2 * 128 + et, tok = id >> 4, part = id & 15;
@@ -327,7 +338,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                         }
                     }
                 }
-                named_bar_sync(1 + h, 128);
+                named_bar_sync(1 + eset, 128);
             }
             tc_fence_before();
             __syncwarp();
