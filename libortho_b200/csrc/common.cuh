@@ -40,8 +40,8 @@ struct Plan {
     int64_t n_virtual, n_long;
     int32_t *vbeg, *vend, *hrow, *hptr;
 };
-constexpr int kPlanHeavy = 128;
-constexpr int kPlanSeg = 128;
+constexpr int kPlanHeavy = 32;
+constexpr int kPlanSeg = 32;
 constexpr uint32_t kPlanMagic = 0x0B200A17u;
 
 // view of the ortho component handed to kernels: either packed plan entries or raw CSR

@@ -271,7 +271,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
 #pragma unroll
                 for (int j4 = 0; j4 < 8; j4++) ov[j4] = o4[j4];
             };
-            if (orow) load_o(eset);
+            if (orow) {
+                load_o(eset);
+                // the other chunks of this row's sparse term: ask L2 for them while the MMAs still run
+                for (int c = eset + ESETS; c < TM / 32; c += ESETS)
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(orow + c * 32));
+            }
             wait(&sm->d_full, (uint32_t)(it & 1));
             tc_fence_after();
             const float *prow = nullptr;               // first K half of a split tile: the partner's partial sums

@@ -192,7 +192,17 @@ __global__ void combine_segments_kernel(const int32_t *__restrict__ hrow, const 
     const int m = blockIdx.y * 256 + threadIdx.x;
     if (m >= Mp) return;
     float s = 0.f;
-    for (int v = hptr[h]; v < hptr[h + 1]; v++) s += o[(size_t)(nrows_real + v) * Mp + m];
+    const int v0 = hptr[h], v1 = hptr[h + 1];
+    const float *src = o + (size_t)nrows_real * Mp + m;
+    int v = v0;
+    for (; v + 8 <= v1; v += 8) {          // eight loads in flight, added in segment order
+        float t[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) t[i] = src[(size_t)(v + i) * Mp];
+#pragma unroll
+        for (int i = 0; i < 8; i++) s += t[i];
+    }
+    for (; v < v1; v++) s += src[(size_t)v * Mp];
     o[(size_t)hrow[h] * Mp + m] = s;
 }
 
