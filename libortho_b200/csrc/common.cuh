@@ -39,9 +39,14 @@ struct Plan {
     // output row hrow[h] and owns segments [hptr[h], hptr[h+1]).  Built on the host at plan creation.
     int64_t n_virtual, n_long;
     int32_t *vbeg, *vend, *hrow, *hptr;
+    // "long" for this layer: more than 32 entries (what the SpMM preloads per row) while the mean row fits in
+    // 32, else more than twice the mean.  What the split buys is a shorter longest chain of dependent gathers per
+    // warp, so rows are only cut when they stand out (a layer whose rows all hold ~90 entries is balanced as
+    // it is, and cutting it would triple the sparse-term traffic)
+    int heavy;
 };
-constexpr int kPlanHeavy = 32;
-constexpr int kPlanSeg = 32;
+constexpr int kPlanHeavy = 32;     // lower bound of the per-layer threshold; also the segment length floor
+constexpr int kNoPlanHeavy = 128;  // without a plan: rows above this are processed by a whole CTA
 constexpr uint32_t kPlanMagic = 0x0B200A17u;
 
 // view of the ortho component handed to kernels: either packed plan entries or raw CSR

@@ -113,6 +113,7 @@ extern "C" int ortho_b200_plan_create(ortho_b200_plan **plan_out, const int32_t 
     pl->magic = kPlanMagic; pl->K = K; pl->N = N; pl->nnz = nnz; pl->max_row_nnz = 0;
     pl->row_ptr = nullptr; pl->entries = nullptr; pl->erow = nullptr; pl->tile_ptr = nullptr;
     pl->n_virtual = 0; pl->n_long = 0; pl->vbeg = nullptr; pl->vend = nullptr; pl->hrow = nullptr; pl->hptr = nullptr;
+    pl->heavy = kPlanHeavy;
     cudaError_t e = cudaGetDevice(&pl->device);
     if (e != cudaSuccess) { note_cuda_error(e); delete pl; return ORTHO_B200_ERR_CUDA; }
     if (nnz > 0) {
@@ -145,18 +146,25 @@ extern "C" int ortho_b200_plan_create(ortho_b200_plan **plan_out, const int32_t 
             return ORTHO_B200_ERR_CUDA;
         }
         pl->max_row_nnz = h_max;
-        if (h_max > kPlanHeavy) {
+        {
+            // 32 entries are what the SpMM keeps preloaded per row (its fast path), so that is the cut while
+            // the mean row still fits it; denser layers are balanced as they are and only cut outliers
+            const int64_t mean = (nnz + N - 1) / N;
+            pl->heavy = (int)(mean <= kPlanHeavy ? kPlanHeavy : (2 * mean > 4096 ? 4096 : 2 * mean));
+        }
+        const int32_t kHeavyRow = pl->heavy, kSegLen = pl->heavy;
+        if (h_max > kHeavyRow) {
             // split the long rows into segments on the host (one pass over the row pointers)
             std::vector<int32_t> rp((size_t)N + 1), vb, ve, hr, hp;
             e = cudaMemcpy(rp.data(), row_ptr, sizeof(int32_t) * (N + 1), cudaMemcpyDeviceToHost);
             if (e == cudaSuccess) {
                 for (int64_t n = 0; n < N; n++) {
                     const int32_t b = rp[n], en = rp[n + 1];
-                    if (en - b <= kPlanHeavy) continue;
+                    if (en - b <= kHeavyRow) continue;
                     hr.push_back((int32_t)n);
                     hp.push_back((int32_t)vb.size());
-                    for (int32_t s0 = b; s0 < en; s0 += kPlanSeg) {
-                        vb.push_back(s0); ve.push_back(s0 + kPlanSeg < en ? s0 + kPlanSeg : en);
+                    for (int32_t s0 = b; s0 < en; s0 += kSegLen) {
+                        vb.push_back(s0); ve.push_back(s0 + kSegLen < en ? s0 + kSegLen : en);
                     }
                 }
                 hp.push_back((int32_t)vb.size());

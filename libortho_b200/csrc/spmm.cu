@@ -7,7 +7,7 @@
 // the activations are first transposed once per forward (Xt[k][m]) so that one sparse entry touches
 // a contiguous run of tokens; a warp then walks one output row's entries and keeps 8 tokens per
 // lane in FP32 registers, so every entry costs one 16-byte load and 8 FMAs per lane.  Rows longer
-// than kHeavy entries are split over the 8 warps of the CTA and their partial sums are combined in
+// than SpmmParams::heavy entries are split over the 8 warps of the CTA and their partial sums are combined in
 // shared memory in a fixed order, so the result does not depend on scheduling.  The tensor-core
 // kernel's epilogue adds alpha * O to scale * D before the single FP16 rounding.
 #include "common.cuh"
@@ -16,7 +16,6 @@ namespace ob {
 
 constexpr int kSpTok = 256;       // tokens per CTA (8 per lane)
 constexpr int kSpRows = 8;        // warps per CTA; each warp owns 8 consecutive rows
-constexpr int kHeavy = kPlanHeavy; // rows with more entries are processed by the whole CTA (or as plan segments)
 
 // X[M][K] (FP16) -> Xt[K][Mp] (FP16), zero padded for m >= M.  64 x 64 tiles; 16-byte global loads
 // along k, 16-byte global stores along m, transposition through a padded shared tile.
@@ -48,7 +47,8 @@ struct SpmmParams {
     const int32_t *rbeg, *rend;    // entry range of work row r: [rbeg[r], rend[r]) (row_ptr / row_ptr + 1, or segments)
     const __half *xt; float *o;    // o already points at the first output slot of this launch
     int nrows, K, Mp;
-    int skip_long;                 // rows longer than kHeavy are handled elsewhere (as segments)
+    int heavy;                     // rows with more entries are processed by the whole CTA, or ...
+    int skip_long;                 // ... skipped here because the plan carries them as segments
 };
 
 __device__ __forceinline__ void spmm_entry(const SpmmParams &p, int e, int &c, float &v)
@@ -126,7 +126,7 @@ spmm_ortho_kernel(const SpmmParams p)
     for (int r = 0; r < RPW; r++) {
         const int e0 = __shfl_sync(0xffffffffu, rb, r), e1 = __shfl_sync(0xffffffffu, re, r);
         const int cnt = e1 - e0;
-        if (cnt > kHeavy) {
+        if (cnt > p.heavy) {
             if (!p.skip_long && lane == 0) heavy_rows[atomicAdd(&n_heavy, 1)] = warp * RPW + r;
         } else if (cnt > 0) {
             float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -228,6 +228,7 @@ int launch_spmm(const FwdArgs &a, const float **o_out, int *mp_out)
     OB_CUDA(cudaGetLastError());
     SpmmParams p;
     p.ov = a.ortho; p.xt = xt; p.K = (int)a.K; p.Mp = (int)Mp;
+    p.heavy = (a.plan && a.ortho.entries) ? a.plan->heavy : kNoPlanHeavy;
     // real rows (long ones are skipped when the plan provides their segments)
     p.rbeg = a.ortho.row_ptr; p.rend = a.ortho.row_ptr + 1; p.nrows = (int)a.N; p.o = o; p.skip_long = nv > 0 ? 1 : 0;
     dim3 sg((unsigned)ceil_div(a.N, kSpRows * 8), (unsigned)(Mp / kSpTok));
