@@ -548,6 +548,92 @@ def run_report(args):
     print("\n".join(out))
 
 
+def run_sharded_report(args):
+    """The 70B-style configuration, N-sharded over the ranks of this job with the peer-store gather
+    (``--sharded-report PATH`` under torch.distributed.run).  Per (shape, M): device time of the sharded
+    forward with and without the exchange, max over ranks; every timed forward is preceded by an L2 flush
+    whose own cost is measured separately and subtracted."""
+    import torch
+    import torch.distributed as dist
+    from libortho_b200 import _C_ops, workloads as wl
+    from libortho_b200.sharded import shard_bounds
+    world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    pk = peaks()
+    stream = torch.cuda.Stream(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    max_m, max_n = max(wl.CFG3_M), max(n for _, n in wl.CFG3_SHAPES)
+    comm = _C_ops.Comm(rank, world, 2 * max_m * max_n, device=dev)
+    if world > 1:
+        comm.connect_group()
+    rows = []
+
+    def timed(fn, n):
+        with torch.cuda.stream(stream):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                for _ in range(n):
+                    flush.fill_(1)
+                    fn()
+            g.replay()
+            stream.synchronize()
+            if world > 1:
+                dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            g.replay()
+            e1.record(stream)
+            e1.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) * 1e3 / n], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    t_flush = timed(lambda: None, 4)
+    for (K, N) in wl.CFG3_SHAPES:
+        full = wl.make_layer(K, N, wl.CFG3_DENSITY, seed=0, device=dev)
+        n0, n1 = shard_bounds(N, world)[rank]
+        L = full.rows(n0, n1) if world > 1 else full
+        fb = {M: full.algorithmic_bytes(M) for M in wl.CFG3_M}
+        ff = {M: full.algorithmic_flops(M) for M in wl.CFG3_M}
+        del full
+        torch.cuda.empty_cache()
+        plan = _C_ops.Plan(L.row_ptr, L.col, L.vals, L.K, L.N)
+        for M in wl.CFG3_M:
+            x = wl.make_input(M, K, seed=M, device=dev)
+            y = torch.empty(M, L.N, dtype=torch.float16, device=dev)
+            ws = torch.empty(max(_C_ops.workspace_bytes(M, K, L.N, plan), 16), dtype=torch.uint8, device=dev)
+            n = 4 if M <= 32 else 2
+            t_local = timed(lambda: _C_ops.forward(L.base_weight, L.base_scales, L.vals, L.col, L.row_ptr, x, y, 1.0,
+                                                   plan=plan, workspace=ws), n) - t_flush
+            t_gather = timed(lambda: _C_ops.forward_gather(L.base_weight, L.base_scales, L.vals, L.col, L.row_ptr, x, 1.0,
+                                                           comm, 0, N, n0, plan=plan, workspace=ws), n) - t_flush
+            gbs, tf = fb[M] / t_gather / 1e3, ff[M] / t_gather / 1e6
+            rows.append(f"| {K}->{N} | {M} | {world} | {t_local:.1f} | {t_gather:.1f} | {t_gather - t_local:.1f} | {M / t_gather * 1e6:.3g} | "
+                        f"{gbs:.0f} | {100 * gbs / world / pk['hbm_gbs']:.1f} | {tf:.1f} | {100 * tf / world / pk['tf_sustained']:.1f} |")
+            del x, y, ws
+        del L, plan
+        torch.cuda.empty_cache()
+    if rank == 0:
+        head = ("| shape K->N | M | GPUs | us, shard forward only | us, forward + output gather | exchange us | tokens/s | aggregate GB/s | "
+                "% of measured HBM per GPU | aggregate TFLOP/s | % of measured sustained tensor per GPU |")
+        out = [f"# 70B-style layers, N-sharded over {world} B200 with the peer-store output gather "
+               "(`torch.distributed.run ... bench.py --sharded-report <path>`)", "",
+               f"L2 flushed before every forward (256 MB fill, {t_flush:.1f} us, subtracted); device time, max over ranks.", "",
+               head, "|" + "---|" * 11, *rows, ""]
+        with open(args.sharded_report, "w") as f:
+            f.write("\n".join(out))
+        print("\n".join(out))
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os._exit(0)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -562,8 +648,12 @@ def main():
                     help="peer exchange: every forward waits for its own exchange instead of the next one waiting for it")
     ap.add_argument("--report", default=None, metavar="PATH",
                     help="instead of the benchmark line: time every configuration on one GPU and write a markdown table")
+    ap.add_argument("--sharded-report", default=None, metavar="PATH",
+                    help="under torch.distributed.run: time the 70B-style layers sharded over the job's ranks, write a table")
     args = ap.parse_args()
-    if args.report:
+    if args.sharded_report:
+        run_sharded_report(args)
+    elif args.report:
         run_report(args)
     elif args.impl == "reference":
         run_reference(args)

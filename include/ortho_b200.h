@@ -179,8 +179,8 @@ ORTHO_B200_API int ortho_b200_forward_static_scratch(const void *q_weight, const
  *               all ranks' slices of this forward are present in the local buffer.  Every rank must
  *               issue the same sequence of forward_gather calls on a comm; a buffer region may be
  *               reused by the second next call at the earliest (alternate two regions).  For M <= 16
- *               the peer stores and the flag exchange are part of the decode kernel itself; other
- *               shapes add one copy kernel.  A rank whose peers do not arrive within the timeout
+ *               and for M > 24 the peer stores and the flag exchange are part of the compute kernel
+ *               itself; the shapes in between add one copy kernel.  A rank whose peers do not arrive within the timeout
  *               (default 2 s) records a kernel status (ortho_b200_query_kernel_status) and returns.
  *               n_offset must be a multiple of 8; y_offset_bytes a multiple of 16.
  * ------------------------------------------------------------------------------------------- */

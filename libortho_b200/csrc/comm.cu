@@ -6,8 +6,10 @@
 // and leaves the complete output in every rank's buffer when the stream reaches the end of the call:
 //   * M <= 16 (streaming decode kernel): the kernel's finalize step stores straight into all
 //     ranks' buffers and its last CTA exchanges the completion flags -- one launch;
-//   * other shapes: the compute kernel writes the local buffer, gather_push_kernel copies the slice
-//     to the peers and exchanges the flags.
+//   * M > 24 (tcgen05 kernel): its epilogue stores every finished output tile into all ranks'
+//     buffers while the MMAs of the next tiles run, and its last CTA exchanges the flags -- one launch;
+//   * what is left (17..24 tokens, K not a multiple of 256): the compute kernel writes the local
+//     buffer, gather_push_kernel copies the slice to the peers and exchanges the flags.
 // Peer memory is only ever touched by plain loads / stores of these kernels.
 // The reference has no multi-device path; the layer-level partition this serves is the row
 // independence of src/ortho.c:354-366,389-396.

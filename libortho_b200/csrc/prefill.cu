@@ -23,7 +23,10 @@
 //   warp 0       TMA producer           warp 1       MMA issuer, TMEM allocator
 //   warps 2-9    INT4 -> FP16 -> TMEM (one thread per output row of the tile)
 //   warps 10-17  epilogue (TMEM -> scale -> FP16 -> global), one set of 4 warps per accumulator
+#include <cstring>
+
 #include "common.cuh"
+#include "gather.cuh"
 #include "umma.cuh"
 
 namespace ob {
@@ -68,6 +71,10 @@ struct Params {
     // part[j][128][TM] and raises flags[j], the first one adds them in its epilogue
     int full_tiles, n_split, kh;
     float *part; int *flags;
+    // N-sharded layer: the epilogue stores every output tile into all ranks' buffers (peer stores over NVLink,
+    // overlapped tile by tile with the MMAs of the following tiles) and the last CTA exchanges the flags
+    int gather;
+    GatherView gv;
 };
 
 struct Unit { int t, kb0, kb1, role, j; };      // role 0: whole tile, 1: first K half (final), 2: second K half (partial)
@@ -336,10 +343,21 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                     if (m < p.M && n0 < p.N) {
                         const __half *src = ys + tok * YS_PITCH + part * 8;
                         __half *dst = p.y + (size_t)m * (size_t)p.ldy + n0;
-                        if (vec_ok) {
-                            *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(src);
+                        if (!p.gather) {
+                            if (vec_ok) {
+                                *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(src);
+                            } else {
+                                for (int e = 0; e < 8 && n0 + e < p.N; e++) dst[e] = src[e];
+                            }
                         } else {
-                            for (int e = 0; e < 8 && n0 + e < p.N; e++) dst[e] = src[e];
+                            const size_t at = (size_t)m * (size_t)p.ldy + n0;
+                            if (vec_ok) {
+                                const uint4 v = *reinterpret_cast<const uint4 *>(src);
+                                for (int r = 0; r < p.gv.world; r++) *reinterpret_cast<uint4 *>(p.gv.y[r] + at) = v;
+                            } else {
+                                for (int r = 0; r < p.gv.world; r++)
+                                    for (int e = 0; e < 8 && n0 + e < p.N; e++) p.gv.y[r][at + e] = src[e];
+                            }
                         }
                     }
                 }
@@ -351,6 +369,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         }
     }
 
+    if (p.gather) {
+        if (!gather_signal_and_wait(p.gv, gridDim.x)) atomicExch(p.status, 2);
+    }
     tc_fence_before();
     __syncthreads();
     if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
@@ -392,6 +413,13 @@ int launch_prefill(const FwdArgs &a)
     p.tiles_n = (int)ceil_div(a.N, TN); p.tiles_m = (int)ceil_div(a.M, TM); p.kblocks = (int)ceil_div(a.K, KB);
     p.status = kernel_status_word();
     if (!p.status) return ORTHO_B200_ERR_CUDA;
+    p.gather = 0;
+    memset(&p.gv, 0, sizeof(p.gv));
+    if (a.gv && a.gv->world > 1) {
+        p.gv = *a.gv;
+        p.gather = 1;
+        if (a.gather_fused) *a.gather_fused = true;
+    }
     static bool attr_set = false;
     static int num_sms = 148;
     if (!attr_set) {
