@@ -50,6 +50,7 @@ class OrthoLinear(nn.Module):
             self.register_parameter("bias", None)
         self._plan: Optional[_C.Plan] = None
         self._plan_key = None
+        self._ws_need = {}
         self._workspace: Optional[torch.Tensor] = None
 
     def set_alpha(self, alpha: float):
@@ -92,6 +93,7 @@ class OrthoLinear(nn.Module):
     def _invalidate(self):
         self._plan = None
         self._plan_key = None
+        self._ws_need = {}
 
     def _apply(self, fn, recurse=True):
         out = super()._apply(fn, recurse)
@@ -121,13 +123,21 @@ class OrthoLinear(nn.Module):
             self._plan = _C.Plan(self.ortho_row_ptr, self.ortho_col_indices, self.ortho_values,
                                  self.in_features, self.out_features)
             self._plan_key = key
+            self._ws_need = {}
         return self._plan
 
     def _get_workspace(self, M: int) -> Optional[torch.Tensor]:
         sparse = self.alpha > 0 and self.ortho_values.numel() > 0
         if not sparse and M <= 24:
             return None
-        need = _C.workspace_bytes(M, self.in_features, self.out_features, self._get_plan() if sparse else None)
+        plan = self._get_plan() if sparse else None
+        key = (M, id(plan))
+        need = self._ws_need.get(key)
+        if need is None:                       # one size query per (token count, plan), not per forward
+            need = _C.workspace_bytes(M, self.in_features, self.out_features, plan)
+            if len(self._ws_need) > 64:
+                self._ws_need.clear()
+            self._ws_need[key] = need
         if need == 0:
             return None
         if (self._workspace is None or self._workspace.numel() < need
