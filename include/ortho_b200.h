@@ -105,7 +105,8 @@ ORTHO_B200_API int ortho_b200_dequant_dump(const void *q_weight, const void *q_s
  * the optional plan, a caller-owned workspace and the stream.
  *
  *   M <= 24  : memory-bound streaming kernels (ORTHO_B200_DECODE_MAX_M is the most they accept);
- *              also M <= 32 with N <= 4096 and M <= 64 with N <= 1024 (too few 128-row tiles to fill the GPU).
+ *              also M <= 32 with N <= 4096 and M <= 64 with N <= 1024 while N * K <= 4096 * 8192 (too few
+ *              128-row tiles to fill the GPU).
  *   larger M : tcgen05 / TMEM tensor-core kernel.
  * Either regime needs ortho_b200_workspace_bytes(M, K, N) bytes of caller-owned workspace when the
  * ortho term is active (alpha > 0 and nnz > 0), none otherwise.

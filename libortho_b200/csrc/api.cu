@@ -101,14 +101,14 @@ int64_t prefill_min_workspace_bytes(int64_t M, int64_t K, int64_t N);
 // scratch a forward with an active ortho term cannot do without
 int64_t min_workspace_bytes(int64_t M, int64_t K, int64_t N)
 {
-    if (decode_regime(M, N)) return decode_tc_workspace_bytes(M, N);
+    if (decode_regime(M, N, K)) return decode_tc_workspace_bytes(M, N);
     return prefill_min_workspace_bytes(M, K, N);
 }
 }  // namespace ob
 
 extern "C" int64_t ortho_b200_workspace_bytes(int64_t M, int64_t K, int64_t N)
 {
-    if (decode_regime(M, N)) return decode_tc_workspace_bytes(M, N);
+    if (decode_regime(M, N, K)) return decode_tc_workspace_bytes(M, N);
     return prefill_workspace_bytes(M, K, N);
 }
 
@@ -166,7 +166,7 @@ int forward_impl(const void *q_weight, const void *q_scales_f16,
     if (ldy != 0 && ldy < N) return ORTHO_B200_ERR_SHAPE;
     a.ldy = ldy; a.gv = gv; a.gather_fused = gather_fused;
 
-    if (decode_regime(M, N)) return launch_decode(a);
+    if (decode_regime(M, N, K)) return launch_decode(a);
     return launch_prefill(a);
 }
 }  // namespace ob

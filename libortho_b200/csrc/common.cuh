@@ -170,5 +170,5 @@ int64_t min_workspace_bytes(int64_t M, int64_t K, int64_t N);
 int set_decode_config(int wr, int wk, int u, int s);
 bool stream_kernel_selected(int64_t M, int64_t K);   // the forward of (M, K) will run decode_stream_kernel
 extern int g_prefill_above;   // forwards with more tokens than this use the prefill kernel (decode.cu) ...
-bool decode_regime(int64_t M, int64_t N);   // ... except narrow layers of up to 64 tokens: true = decode kernels
+bool decode_regime(int64_t M, int64_t N, int64_t K);   // ... except narrow layers of up to 64 tokens: true = decode kernels
 }  // namespace ob

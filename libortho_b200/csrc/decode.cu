@@ -268,13 +268,15 @@ constexpr int kPrefillAboveBuiltin = 24;
 // Which regime a forward runs in.  Above the token threshold the tensor-core kernel wins unless the layer (or
 // the shard of it that this GPU holds) has so few 128-row tiles that most SMs would idle for a whole K sweep:
 // measured at K = 8192, M = 32: N = 1024 / 2048 / 4096 take 24 / 27 / 51 us here against 96 / 96 / 93 us there
-// (141 against 95 us at N = 7168); M = 64: 63 against 98 us at N = 1024, 117 against 96 us at N = 2048.
+// (141 against 95 us at N = 7168); M = 64: 63 against 98 us at N = 1024, 117 against 96 us at N = 2048.  With a
+// long K the balance tips back (K = 28672, N = 4096, M = 32: 272 against 216 us), hence the bound on N * K.
 // The narrow-layer exception only applies to the built-in threshold, so that the tuning hook can still force
 // either kernel.
-bool decode_regime(int64_t M, int64_t N)
+bool decode_regime(int64_t M, int64_t N, int64_t K)
 {
     if (M <= g_prefill_above) return true;
     if (g_prefill_above != kPrefillAboveBuiltin || M > ORTHO_B200_DECODE_MAX_M) return false;
+    if (N * K > (int64_t)4096 * 8192) return false;
     return (M <= 32 && N <= 4096) || N <= 1024;
 }
 static bool g_use_tc = false;                        // tcgen05 decode kernel: opt-in through the tuning hook (slower than the

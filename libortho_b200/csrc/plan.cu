@@ -226,7 +226,7 @@ extern "C" int64_t ortho_b200_plan_workspace_bytes(const ortho_b200_plan *plan, 
     const Plan *pl = reinterpret_cast<const Plan *>(plan);
     if (!pl || pl->magic != kPlanMagic) return -1;
     if (pl->nnz == 0) return 0;
-    if (decode_regime(M, pl->N)) return ortho_b200_workspace_bytes(M, pl->K, pl->N);
+    if (decode_regime(M, pl->N, pl->K)) return ortho_b200_workspace_bytes(M, pl->K, pl->N);
     return prefill_workspace_bytes(M, pl->K, pl->N + pl->n_virtual);
 }
 
