@@ -90,7 +90,7 @@ class ClockSampler:
 
 
 def sweep_items():
-    from libortho_b200 import workloads as wl
+    import workloads as wl
     return [(K, N, M) for M in wl.CFG1_M for (K, N) in wl.CFG1_SHAPES]
 
 
@@ -103,7 +103,7 @@ def run_reference(args):
         return
     import numpy as np
     import oracle
-    from libortho_b200 import workloads as wl
+    import workloads as wl
     impl, kind = ("reference_fast", "reference") if oracle.available("reference_fast") else ("port", "port")
     if impl == "port":
         oracle.build()
@@ -145,7 +145,8 @@ def run_reference(args):
 def run_ours(args):
     import torch
     import torch.distributed as dist
-    from libortho_b200 import _C_ops, _lib, workloads as wl
+    from libortho_b200 import _C_ops, _lib
+    import workloads as wl
     from libortho_b200.sharded import ShardedOrthoLinear, shard_bounds
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -382,7 +383,8 @@ def time_forward_us(get_layer, x, y, stream, reps=2, replays=5):
 
 def bench_prefill(dev, pk):
     import torch
-    from libortho_b200 import _C_ops, workloads as wl
+    from libortho_b200 import _C_ops
+    import workloads as wl
     K, N = wl.CFG2_SHAPE
     L = wl.make_zipf_layer(K, N, wl.CFG2_DENSITY, seed=0, device=dev, alpha=wl.CFG2_ALPHA)
     plan = _C_ops.Plan(L.row_ptr, L.col, L.vals, K, N)
@@ -415,7 +417,7 @@ def bench_prefill(dev, pk):
 def cpu_baseline():
     """Reference CPU forward (oracle/_ref, reference flags) on this host: one pass over the sweep."""
     import oracle
-    from libortho_b200 import workloads as wl
+    import workloads as wl
     impl, kind = ("reference_fast", "reference") if oracle.available("reference_fast") else ("port", "port")
     if impl == "port":
         oracle.build()
@@ -439,7 +441,8 @@ def run_report(args):
     """All BASELINE.json configurations on one GPU, as a markdown table (``--report PATH``).  Decode-sized
     forwards rotate over enough weight copies to exceed L2; per-forward device time from CUDA graphs."""
     import torch
-    from libortho_b200 import _C_ops, workloads as wl
+    from libortho_b200 import _C_ops
+    import workloads as wl
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     pk = peaks()
@@ -555,7 +558,8 @@ def run_sharded_report(args):
     whose own cost is measured separately and subtracted."""
     import torch
     import torch.distributed as dist
-    from libortho_b200 import _C_ops, workloads as wl
+    from libortho_b200 import _C_ops
+    import workloads as wl
     from libortho_b200.sharded import shard_bounds
     world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)

@@ -66,7 +66,7 @@ ORTHO_B200_API int ortho_b200_last_cuda_error(void);
  * Has no counterpart in the reference (its kernels read CSR directly,
  * src/dual_gemm.cu:106-130); it takes the place of the per-call orth_layer_t the binding builds
  * on its stack (torch_bind/bindings.cpp:19-36).  The plan owns only its own device copies
- * (packed {col16|f16 value} entries in row order, per-entry row ids, per-128-row-tile ranges);
+ * (packed {col16|f16 value} entries in row order, row pointers, segment tables of long rows);
  * it never retains the caller's pointers.  Creation allocates device memory, launches the
  * re-layout kernels on `stream` and synchronises that stream once.  A plan is immutable after
  * creation and may be shared by concurrent forwards.  nnz == 0 yields a valid empty plan.
@@ -237,12 +237,13 @@ ORTHO_B200_API int ortho_b200_csr_fill(const float *w_ortho, int64_t N, int64_t 
  * (src/dual_gemm.cu:361-371), as an explicit call instead of a cost on every forward. */
 ORTHO_B200_API int ortho_b200_query_kernel_status(void);
 
-/* Benchmark/tuning hook: overrides the decode kernels' tiling for later forwards from this process.
+/* Benchmark/tuning hook: overrides the decode kernels' tiling for forwards that START after the call
+ * returns, from any thread of this process (the state sits behind a lock; a forward uses the
+ * snapshot it took on entry).
  *   row_groups > 0 : generic kernel with (row groups per CTA, k groups per CTA, loads in flight,
  *                    k split over the cluster);
  *   row_groups == -1: streaming TMA kernel (M <= 16) with k_split CTAs per cluster and `unroll`
  *                    ring slots per warp (either may be 0 for the built-in choice);
- *   row_groups == -2: tcgen05 decode kernel with k_split CTAs per cluster and `unroll` weight stages;
  *   row_groups == -3: forwards with more than k_split tokens (0..ORTHO_B200_DECODE_MAX_M) use the
  *                    tensor-core kernel (built-in: 24);
  *   row_groups == 0 : restore the built-in choice of kernel and tiling (not the -3 threshold).

@@ -36,7 +36,17 @@ int *kernel_status_word()
     return cached;
 }
 
-int64_t decode_tc_workspace_bytes(int64_t M, int64_t N);   // decode_tc.cu
+int device_sm_count(int dev)
+{
+    static std::atomic<int> cached[kMaxDevices];
+    if (dev < 0 || dev >= kMaxDevices) return 148;
+    int n = cached[dev].load(std::memory_order_relaxed);
+    if (n <= 0) {
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) { (void)cudaGetLastError(); return 148; }
+        cached[dev].store(n, std::memory_order_relaxed);
+    }
+    return n;
+}
 
 static int check_device()
 {
@@ -101,14 +111,14 @@ int64_t prefill_min_workspace_bytes(int64_t M, int64_t K, int64_t N);
 // scratch a forward with an active ortho term cannot do without
 int64_t min_workspace_bytes(int64_t M, int64_t K, int64_t N)
 {
-    if (decode_regime(M, N, K)) return decode_tc_workspace_bytes(M, N);
+    if (decode_regime(M, N, K)) return 0;          // the decode kernels use no global scratch
     return prefill_min_workspace_bytes(M, K, N);
 }
 }  // namespace ob
 
 extern "C" int64_t ortho_b200_workspace_bytes(int64_t M, int64_t K, int64_t N)
 {
-    if (decode_regime(M, N, K)) return decode_tc_workspace_bytes(M, N);
+    if (decode_regime(M, N, K)) return 0;
     return prefill_workspace_bytes(M, K, N);
 }
 

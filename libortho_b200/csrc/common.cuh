@@ -21,10 +21,33 @@ void count_launch(int n = 1);          // feeds ortho_b200_launch_count()
 
 static inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
+// ---- per-device launch state ----------------------------------------------------------------------
+// cudaFuncSetAttribute, the SM count and cluster occupancy belong to ONE device: caches of them are
+// indexed by the current device (a process may run forwards on several GPUs) and only ever move from
+// "unknown" to a value that every thread would compute identically, so they need no lock.
+constexpr int kMaxDevices = 64;
+static inline int current_device_index()
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+    return dev;
+}
+int device_sm_count(int dev);          // api.cu: multiprocessor count of device `dev`, cached
+
+// ---- tuning hook state (ortho_b200_set_decode_config) ------------------------------------------------
+// One record behind a mutex; every forward works on the snapshot it took when it started, so a
+// concurrent change of the hook never shows half-applied inside one call.
+struct Tuning {
+    int wr = 0, wk = 0, u = 0, s = 0;   // generic decode kernel tiling (wr == 0: built-in choice)
+    bool force_stream = false;          // streaming kernel with stream_s / stream_stages
+    int stream_s = 0, stream_stages = 0;
+    int prefill_above = 24;             // forwards with more tokens than this use the tensor-core kernels
+};
+constexpr int kPrefillAboveBuiltin = 24;
+Tuning tuning_snapshot();              // decode.cu
+
 // ---- the plan (definition shared by plan.cu / decode.cu / prefill.cu) -------------------------
 // entries[i] = (f16 bits of value << 16) | column   for CSR entry i (row-major order kept)
-// erow[i]    = output row of entry i
-// tile_ptr[t]= first entry of 128-row tile t (== row_ptr[min(128 t, N)]), t in [0, ceil(N/128)]
 struct Plan {
     uint32_t magic;
     int device;
@@ -32,8 +55,6 @@ struct Plan {
     int64_t max_row_nnz;
     int32_t *row_ptr;     // [N+1] device copy
     uint32_t *entries;    // [nnz]
-    int32_t *erow;        // [nnz]
-    int32_t *tile_ptr;    // [ceil(N/128)+1]
     // rows longer than kPlanHeavy entries are split into segments of at most kPlanSeg entries
     // for the prefill SpMM: segment v covers entries [vbeg[v], vend[v]); long row h (h < n_long) is
     // output row hrow[h] and owns segments [hptr[h], hptr[h+1]).  Built on the host at plan creation.
@@ -169,6 +190,6 @@ int64_t prefill_workspace_bytes(int64_t M, int64_t K, int64_t N);
 int64_t min_workspace_bytes(int64_t M, int64_t K, int64_t N);
 int set_decode_config(int wr, int wk, int u, int s);
 bool stream_kernel_selected(int64_t M, int64_t K);   // the forward of (M, K) will run decode_stream_kernel
-extern int g_prefill_above;   // forwards with more tokens than this use the prefill kernel (decode.cu) ...
-bool decode_regime(int64_t M, int64_t N, int64_t K);   // ... except narrow layers of up to 64 tokens: true = decode kernels
+// true = decode kernels: up to Tuning::prefill_above tokens, and narrow layers of up to 64 tokens
+bool decode_regime(int64_t M, int64_t N, int64_t K);
 }  // namespace ob

@@ -19,6 +19,7 @@
 #include <cooperative_groups.h>
 
 #include <cstdlib>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -257,13 +258,18 @@ decode_kernel(const DecodeParams p)
 // ---- host side ------------------------------------------------------------------------------
 
 struct DecodeCfg { int wr, wk, u, s; };
-static DecodeCfg g_override = {0, 0, 0, 0};
-static bool g_force_stream = false;
-// Forwards with more tokens than this go to the tcgen05 prefill kernel.  Measured on 8192->8192 / 8192->57344 /
-// 28672->8192: at 32 tokens the 128 x 256 tensor-core tile (mostly padding) takes 97 / 370 / 300 us where the
-// mma.sync kernel below takes 146 / 972 / 479 us; at 17 tokens the two are within a few per cent.
-int g_prefill_above = 24;
-constexpr int kPrefillAboveBuiltin = 24;
+
+// Tuning hook state.  prefill_above: forwards with more tokens go to the tcgen05 kernels.  Measured on
+// 8192->8192 / 8192->57344 / 28672->8192: at 32 tokens the 128 x 256 tensor-core tile (mostly padding) takes
+// 97 / 370 / 300 us where the mma.sync kernel below takes 146 / 972 / 479 us; at 17 tokens the two are within a
+// few per cent.
+static std::mutex g_tune_mu;
+static Tuning g_tune;
+Tuning tuning_snapshot()
+{
+    std::lock_guard<std::mutex> lock(g_tune_mu);
+    return g_tune;
+}
 
 // Which regime a forward runs in.  Above the token threshold the tensor-core kernel wins unless the layer (or
 // the shard of it that this GPU holds) has so few 128-row tiles that most SMs would idle for a whole K sweep:
@@ -272,58 +278,48 @@ constexpr int kPrefillAboveBuiltin = 24;
 // long K the balance tips back (K = 28672, N = 4096, M = 32: 272 against 216 us), hence the bound on N * K.
 // The narrow-layer exception only applies to the built-in threshold, so that the tuning hook can still force
 // either kernel.
-bool decode_regime(int64_t M, int64_t N, int64_t K)
+static bool decode_regime_of(const Tuning &t, int64_t M, int64_t N, int64_t K)
 {
-    if (M <= g_prefill_above) return true;
-    if (g_prefill_above != kPrefillAboveBuiltin || M > ORTHO_B200_DECODE_MAX_M) return false;
+    if (M <= t.prefill_above) return true;
+    if (t.prefill_above != kPrefillAboveBuiltin || M > ORTHO_B200_DECODE_MAX_M) return false;
     if (N * K > (int64_t)4096 * 8192) return false;
     return (M <= 32 && N <= 4096) || N <= 1024;
 }
-static bool g_use_tc = false;                        // tcgen05 decode kernel: opt-in through the tuning hook (slower than the
-                                                     // streaming kernel on the benchmark shapes so far)
-int launch_decode_stream(const FwdArgs &a);          // decode_stream.cu
-void set_stream_config(int s, int stages);
-int launch_decode_tc(const FwdArgs &a);              // decode_tc.cu
-void set_tc_config(int s, int stages);
+bool decode_regime(int64_t M, int64_t N, int64_t K) { return decode_regime_of(tuning_snapshot(), M, N, K); }
+
+int launch_decode_stream(const FwdArgs &a, int S, int stages);          // decode_stream.cu
 
 int set_decode_config(int wr, int wk, int u, int s)
 {
+    std::lock_guard<std::mutex> lock(g_tune_mu);
+    Tuning &t = g_tune;
     if (wr == -3) {       // forwards with more than s tokens (0 <= s <= 64) go to the tensor-core prefill kernel
         if (s < 0 || s > ORTHO_B200_DECODE_MAX_M) return ORTHO_B200_ERR_SHAPE;
-        g_prefill_above = s;
+        t.prefill_above = s;
         return ORTHO_B200_OK;
     }
-    if (wr == -2) {       // tcgen05 decode kernel with k_split = s CTAs per cluster and u weight stages (0 = built-in)
-        if (s < 0 || s > 8 || u < 0 || u > 8) return ORTHO_B200_ERR_SHAPE;
-        g_override = {0, 0, 0, 0};
-        g_force_stream = false;
-        g_use_tc = true;
-        set_tc_config(s, u);
-        return ORTHO_B200_OK;
-    }
-    g_use_tc = false;
-    set_tc_config(0, 0);
     if (wr == -1) {
         if ((s != 0 && s != 1 && s != 2 && s != 4 && s != 8) || u < 0 || u > 12 || u == 1) return ORTHO_B200_ERR_SHAPE;
-        g_override = {0, 0, 0, 0};
-        g_force_stream = true;
-        set_stream_config(s, u);
+        t.wr = t.wk = t.u = t.s = 0;
+        t.force_stream = true;
+        t.stream_s = s; t.stream_stages = u;
         return ORTHO_B200_OK;
     }
-    g_force_stream = false;
-    set_stream_config(0, 0);
-    if (wr <= 0 || wk <= 0 || u <= 0 || s <= 0) { g_override = {0, 0, 0, 0}; return ORTHO_B200_OK; }
+    if (wr < 0) return ORTHO_B200_ERR_SHAPE;
+    t.force_stream = false;
+    t.stream_s = t.stream_stages = 0;
+    if (wr <= 0 || wk <= 0 || u <= 0 || s <= 0) { t.wr = t.wk = t.u = t.s = 0; return ORTHO_B200_OK; }
     const bool shape_ok = (wr == 1 && wk == 8) || (wr == 2 && wk == 4) || (wr == 4 && wk == 2) ||
                           (wr == 8 && wk == 1) || (wr == 1 && wk == 4) || (wr == 2 && wk == 2);
     if (!shape_ok || (u != 2 && u != 4) || (s != 1 && s != 2 && s != 4 && s != 8))
         return ORTHO_B200_ERR_SHAPE;
-    g_override = {wr, wk, u, s};
+    t.wr = wr; t.wk = wk; t.u = u; t.s = s;
     return ORTHO_B200_OK;
 }
 
-static DecodeCfg choose(int64_t M, int64_t K, int64_t N)
+static DecodeCfg choose(const Tuning &t, int64_t M, int64_t K, int64_t N)
 {
-    if (g_override.wr > 0) return g_override;
+    if (t.wr > 0) return DecodeCfg{t.wr, t.wk, t.u, t.s};
     DecodeCfg c;
     if (M <= 8) { c.wr = 1; c.wk = 8; }
     else if (M <= 16) { c.wr = 2; c.wk = 4; }
@@ -358,10 +354,12 @@ static int launch_cfg(const FwdArgs &a, int S)
     const size_t smem = (size_t)a.M * p.pitch + (size_t)(WK + 1) * R * TOK * sizeof(float);
 
     auto kern = decode_kernel<MT, WR, WK, U>;
-    static bool smem_set = false;
-    if (!smem_set) {
+    static bool smem_set[kMaxDevices] = {};       // the attribute is per device
+    const int dev = current_device_index();
+    if (dev < 0) return ORTHO_B200_ERR_CUDA;
+    if (!smem_set[dev]) {
         OB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        smem_set = true;
+        smem_set[dev] = true;
     }
     if (smem > 227 * 1024) return ORTHO_B200_ERR_SHAPE;
     cudaLaunchConfig_t cfg = {};
@@ -396,20 +394,22 @@ static int launch_mt(const FwdArgs &a, const DecodeCfg &c)
 
 // M <= 16: persistent TMA streaming kernel, unless another kernel was asked for explicitly
 // (its TMA view needs whole 128-byte column blocks per row: K a multiple of 256)
+static bool stream_selected(const Tuning &t, int64_t M, int64_t K)
+{
+    return M <= 16 && (K % 256) == 0 && (t.force_stream || t.wr == 0);
+}
 bool stream_kernel_selected(int64_t M, int64_t K)
 {
-    return M <= g_prefill_above && !g_use_tc && M <= 16 && (K % 256) == 0 && (g_force_stream || g_override.wr == 0);
+    const Tuning t = tuning_snapshot();
+    return M <= t.prefill_above && stream_selected(t, M, K);
 }
 
 int launch_decode(const FwdArgs &a)
 {
     if (a.M > ORTHO_B200_DECODE_MAX_M) return ORTHO_B200_ERR_SHAPE;
-    if (g_use_tc) {
-        const int st = launch_decode_tc(a);
-        if (st != ORTHO_B200_ERR_SHAPE) return st;      // ERR_SHAPE: does not fit that kernel, use the others
-    }
-    if (a.M <= 16 && (a.K % 256) == 0 && (g_force_stream || g_override.wr == 0)) return launch_decode_stream(a);
-    const DecodeCfg c = choose(a.M, a.K, a.N);
+    const Tuning t = tuning_snapshot();
+    if (stream_selected(t, a.M, a.K)) return launch_decode_stream(a, t.stream_s, t.stream_stages);
+    const DecodeCfg c = choose(t, a.M, a.K, a.N);
     if (a.M <= 8) return launch_mt<1>(a, c);
     if (a.M <= 16) return launch_mt<2>(a, c);
     if (a.M <= 32) return launch_mt<4>(a, c);

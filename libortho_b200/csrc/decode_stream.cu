@@ -19,7 +19,9 @@
 //
 // No global scratch, no atomics: results are bitwise reproducible, and with alpha <= 0 or nnz == 0
 // the sparse stream is not touched at all, so the output equals the base-only output exactly.
+#include <atomic>
 #include <cstdlib>
+#include <mutex>
 
 #include "common.cuh"
 #include "gather.cuh"
@@ -433,9 +435,6 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
 // ---- host ------------------------------------------------------------------------------------
 int *kernel_status_word();   // api.cu
 
-static int g_stream_cfg[2] = {0, 0};   // {k_split, stages}; 0 = built-in choice
-void set_stream_config(int s, int stages) { g_stream_cfg[0] = s; g_stream_cfg[1] = stages; }
-
 static size_t stream_smem_bytes(int MV, int kbx, int64_t M, int boxes_per_cta, int stages, int ng = 1, int red_bufs = 2)
 {
     const size_t region = ((size_t)kWarps * stages * (16 * kbx * 128) + (((kWarps * stages + 1) * 8 + 127) & ~127) +
@@ -473,10 +472,12 @@ static int launch_stream_mv(const FwdArgs &a, const CUtensorMap &map, int S, int
     const size_t smem = stream_smem_bytes(MV, KBX, a.M, boxes_per_cta, stages, NG, red_bufs);
     if (smem > 227 * 1024) return ORTHO_B200_ERR_SHAPE;
     auto kern = decode_stream_kernel<MV, KBX, GATHER, NG>;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static bool attr_set[kMaxDevices] = {};       // the attribute is per device
+    const int dev = current_device_index();
+    if (dev < 0) return ORTHO_B200_ERR_CUDA;
+    if (!attr_set[dev]) {
         OB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        attr_set = true;
+        attr_set[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(NG * kWarps * 32, 1, 1);
@@ -494,22 +495,26 @@ static int launch_stream_mv(const FwdArgs &a, const CUtensorMap &map, int S, int
     cfg.attrs = attr;
     cfg.numAttrs = 2;
     // persistent grid: as many clusters as can be co-resident, never more than there are tiles
-    // (cached per cluster size and shared-memory footprint)
-    static struct { int s; size_t smem; int n; } cache[16];
-    static int cache_n = 0;
+    // (cached per device, cluster size and shared-memory footprint; a racing thread at worst asks twice)
+    static struct { int dev, s; size_t smem; int n; } cache[16];
+    static std::atomic<int> cache_n{0};
     int mc = 0;
-    for (int i = 0; i < cache_n; i++)
-        if (cache[i].s == S && cache[i].smem == smem) mc = cache[i].n;
+    const int have = cache_n.load(std::memory_order_acquire);
+    for (int i = 0; i < have && i < 16; i++)
+        if (cache[i].dev == dev && cache[i].s == S && cache[i].smem == smem) mc = cache[i].n;
     if (mc == 0) {
-        cfg.gridDim = dim3((unsigned)S, 148, 1);
+        const int sms = device_sm_count(dev);
+        cfg.gridDim = dim3((unsigned)S, (unsigned)sms, 1);
         cfg.numAttrs = 1;
         int n = 0;
         cudaError_t e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
-        if (e != cudaSuccess || n <= 0) { (void)cudaGetLastError(); n = 148 / S; }
+        if (e != cudaSuccess || n <= 0) { (void)cudaGetLastError(); n = sms / S; }
         cfg.numAttrs = 2;
         mc = n;
-        cache[cache_n % 16] = {S, smem, n};
-        if (cache_n < 16) cache_n++;
+        static std::mutex mu;
+        std::lock_guard<std::mutex> lock(mu);
+        const int slot = cache_n.load(std::memory_order_relaxed);
+        if (slot < 16) { cache[slot] = {dev, S, smem, n}; cache_n.store(slot + 1, std::memory_order_release); }
     }
     const int units = (int)ceil_div(p.ntiles, NG);       // a CTA takes NG tiles per round
     int Gc = mc < units ? mc : units;
@@ -519,13 +524,13 @@ static int launch_stream_mv(const FwdArgs &a, const CUtensorMap &map, int S, int
     return ORTHO_B200_OK;
 }
 
-int launch_decode_stream(const FwdArgs &a)
+int launch_decode_stream(const FwdArgs &a, int cfg_s, int cfg_stages)
 {
     if (a.M > 16) return ORTHO_B200_ERR_SHAPE;
     const int MV = a.M <= 1 ? 1 : a.M <= 2 ? 2 : a.M <= 4 ? 4 : a.M <= 8 ? 8 : 16;
     const int kbx = (MV <= 8) ? 2 : 1;
     const int nboxes = (int)ceil_div(a.K, 256 * kbx);
-    int S = g_stream_cfg[0], stages = g_stream_cfg[1], ng = 1, red_bufs = 2;
+    int S = cfg_s, stages = cfg_stages, ng = 1, red_bufs = 2;   // 0 = built-in choice
     if (S <= 0) {
         // one CTA per tile covers all of K when its activation slab fits; otherwise split K over the
         // smallest cluster that does

@@ -4,9 +4,8 @@
 // The reference kernels read CSR as three separate streams per row (row_ptr, then col_indices
 // and float values; src/dual_gemm.cu:106-130).  The re-layout keeps the CSR row-major order
 // (tools/sieve.py:131-136) but fuses column and value into one 32-bit word per entry
-// ({f16 value bits | 16-bit column}), records the output row of every entry so that a flat
-// entry range can be processed without a row search, and records the entry range of every
-// 128-row tile for the tensor-core kernel's epilogue.
+// ({f16 value bits | 16-bit column}) and keeps its own copy of the row pointers; rows that stand
+// out in length are cut into segments (built on the host) for the prefill-regime sparse pass.
 #include <new>
 #include <vector>
 
@@ -14,22 +13,17 @@
 
 namespace ob {
 
-// one warp per output row: pack the row's entries, tag them with the row, track the longest row
+// one warp per output row: pack the row's entries, track the longest row
 __global__ void relayout_rows_kernel(const int32_t *__restrict__ row_ptr, const int32_t *__restrict__ col,
                                      const __half *__restrict__ val, int N, int K,
-                                     uint32_t *__restrict__ entries, int32_t *__restrict__ erow,
-                                     int32_t *__restrict__ row_ptr_copy, int32_t *__restrict__ tile_ptr,
+                                     uint32_t *__restrict__ entries, int32_t *__restrict__ row_ptr_copy,
                                      int *__restrict__ max_row_nnz)
 {
     const int warps_per_block = blockDim.x >> 5;
     const int lane = threadIdx.x & 31;
     for (int n = blockIdx.x * warps_per_block + (threadIdx.x >> 5); n <= N; n += gridDim.x * warps_per_block) {
         const int e0 = row_ptr[n];
-        if (lane == 0) {
-            row_ptr_copy[n] = e0;
-            if ((n & 127) == 0) tile_ptr[n >> 7] = e0;
-            if (n == N && (N & 127) != 0) tile_ptr[(N + 127) >> 7] = e0;
-        }
+        if (lane == 0) row_ptr_copy[n] = e0;
         if (n == N) continue;
         const int e1 = row_ptr[n + 1];
         for (int e = e0 + lane; e < e1; e += 32) {
@@ -39,21 +33,26 @@ __global__ void relayout_rows_kernel(const int32_t *__restrict__ row_ptr, const 
             // explicit zero so that it contributes nothing
             if ((unsigned)c >= (unsigned)K) { c = 0; vb = 0; }
             entries[e] = ((uint32_t)vb << 16) | (uint32_t)c;
-            erow[e] = n;
         }
         if (lane == 0) atomicMax(max_row_nnz, e1 - e0);
     }
 }
 
-__global__ void plan_decode_dump_kernel(const uint32_t *__restrict__ entries, const int32_t *__restrict__ erow,
-                                        int64_t nnz, int32_t *__restrict__ rows, int32_t *__restrict__ cols,
+// one warp per output row: the row of an entry is recovered from the plan's own row pointers
+__global__ void plan_decode_dump_kernel(const uint32_t *__restrict__ entries, const int32_t *__restrict__ row_ptr,
+                                        int N, int32_t *__restrict__ rows, int32_t *__restrict__ cols,
                                         __half *__restrict__ vals)
 {
-    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < nnz; i += (int64_t)gridDim.x * blockDim.x) {
-        const uint32_t pk = entries[i];
-        rows[i] = erow[i];
-        cols[i] = (int32_t)(pk & 0xFFFFu);
-        vals[i] = __ushort_as_half((unsigned short)(pk >> 16));
+    const int warps_per_block = blockDim.x >> 5;
+    const int lane = threadIdx.x & 31;
+    for (int n = blockIdx.x * warps_per_block + (threadIdx.x >> 5); n < N; n += gridDim.x * warps_per_block) {
+        const int e0 = row_ptr[n], e1 = row_ptr[n + 1];
+        for (int e = e0 + lane; e < e1; e += 32) {
+            const uint32_t pk = entries[e];
+            rows[e] = n;
+            cols[e] = (int32_t)(pk & 0xFFFFu);
+            vals[e] = __ushort_as_half((unsigned short)(pk >> 16));
+        }
     }
 }
 
@@ -111,19 +110,16 @@ extern "C" int ortho_b200_plan_create(ortho_b200_plan **plan_out, const int32_t 
     Plan *pl = new (std::nothrow) Plan();
     if (!pl) return ORTHO_B200_ERR_ALLOC;
     pl->magic = kPlanMagic; pl->K = K; pl->N = N; pl->nnz = nnz; pl->max_row_nnz = 0;
-    pl->row_ptr = nullptr; pl->entries = nullptr; pl->erow = nullptr; pl->tile_ptr = nullptr;
+    pl->row_ptr = nullptr; pl->entries = nullptr;
     pl->n_virtual = 0; pl->n_long = 0; pl->vbeg = nullptr; pl->vend = nullptr; pl->hrow = nullptr; pl->hptr = nullptr;
     pl->heavy = kPlanHeavy;
     cudaError_t e = cudaGetDevice(&pl->device);
     if (e != cudaSuccess) { note_cuda_error(e); delete pl; return ORTHO_B200_ERR_CUDA; }
     if (nnz > 0) {
         cudaStream_t st = (cudaStream_t)stream;
-        const int64_t ntiles = ceil_div(N, 128);
         int *d_max = nullptr;
         e = cudaMalloc(&pl->row_ptr, sizeof(int32_t) * (N + 1));
         if (e == cudaSuccess) e = cudaMalloc(&pl->entries, sizeof(uint32_t) * nnz);
-        if (e == cudaSuccess) e = cudaMalloc(&pl->erow, sizeof(int32_t) * nnz);
-        if (e == cudaSuccess) e = cudaMalloc(&pl->tile_ptr, sizeof(int32_t) * (ntiles + 1));
         if (e == cudaSuccess) e = cudaMalloc(&d_max, sizeof(int));
         if (e == cudaSuccess) e = cudaMemsetAsync(d_max, 0, sizeof(int), st);
         if (e == cudaSuccess) {
@@ -131,8 +127,7 @@ extern "C" int ortho_b200_plan_create(ortho_b200_plan **plan_out, const int32_t 
             int64_t blocks = ceil_div(N + 1, wpb);
             if (blocks > 148 * 16) blocks = 148 * 16;
             relayout_rows_kernel<<<(unsigned)blocks, threads, 0, st>>>(
-                row_ptr, col_indices, (const __half *)values_f16, (int)N, (int)K, pl->entries, pl->erow,
-                pl->row_ptr, pl->tile_ptr, d_max);
+                row_ptr, col_indices, (const __half *)values_f16, (int)N, (int)K, pl->entries, pl->row_ptr, d_max);
             count_launch();
             e = cudaGetLastError();
         }
@@ -198,8 +193,6 @@ extern "C" int ortho_b200_plan_destroy(ortho_b200_plan *plan)
     if (pl->magic != kPlanMagic) return ORTHO_B200_ERR_PLAN;
     if (pl->row_ptr) cudaFree(pl->row_ptr);
     if (pl->entries) cudaFree(pl->entries);
-    if (pl->erow) cudaFree(pl->erow);
-    if (pl->tile_ptr) cudaFree(pl->tile_ptr);
     if (pl->vbeg) cudaFree(pl->vbeg);
     if (pl->vend) cudaFree(pl->vend);
     if (pl->hrow) cudaFree(pl->hrow);
@@ -237,10 +230,10 @@ extern "C" int ortho_b200_plan_decode_dump(const ortho_b200_plan *plan, int32_t 
     if (!pl || pl->magic != kPlanMagic) return ORTHO_B200_ERR_PLAN;
     if (pl->nnz == 0) return ORTHO_B200_OK;
     if (!rows_out || !cols_out || !values_f16_out) return ORTHO_B200_ERR_NULL;
-    int64_t blocks = ceil_div(pl->nnz, 256);
-    if (blocks > 148 * 8) blocks = 148 * 8;
+    int64_t blocks = ceil_div(pl->N, 8);
+    if (blocks > 148 * 16) blocks = 148 * 16;
     plan_decode_dump_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
-        pl->entries, pl->erow, pl->nnz, rows_out, cols_out, (__half *)values_f16_out);
+        pl->entries, pl->row_ptr, (int)pl->N, rows_out, cols_out, (__half *)values_f16_out);
     count_launch();
     OB_CUDA(cudaGetLastError());
     return ORTHO_B200_OK;

@@ -420,15 +420,14 @@ int launch_prefill(const FwdArgs &a)
         p.gather = 1;
         if (a.gather_fused) *a.gather_fused = true;
     }
-    static bool attr_set = false;
-    static int num_sms = 148;
-    if (!attr_set) {
+    static bool attr_set[kMaxDevices] = {};       // the attribute is per device
+    const int dev = current_device_index();
+    if (dev < 0) return ORTHO_B200_ERR_CUDA;
+    if (!attr_set[dev]) {
         OB_CUDA(cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
-        int dev = 0;
-        OB_CUDA(cudaGetDevice(&dev));
-        OB_CUDA(cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev));
-        attr_set = true;
+        attr_set[dev] = true;
     }
+    const int num_sms = device_sm_count(dev);
     // split-K of the last partial wave: worth it when the leftover tiles occupy at most half of the SMs
     // and the caller's workspace has room for their partial sums behind the sparse pre-pass's part
     {

@@ -57,10 +57,14 @@ extern "C" int ortho_b200_forward_static_scratch(const void *q_weight, const voi
         M > 0x7fffffffLL || N > 0x7fffff00LL || nnz > 0x7fffffffLL)
         return ORTHO_B200_ERR_SHAPE;
     if ((((uintptr_t)q_weight | (uintptr_t)x_f16 | (uintptr_t)y_f16) & 15u) != 0) return ORTHO_B200_ERR_ALIGN;
+    if (((uintptr_t)q_scales_f16 & 1u) != 0) return ORTHO_B200_ERR_ALIGN;
     const bool has_ortho = (alpha > 0.0f) && (nnz > 0);
     if (has_ortho && (!ortho_values_f16 || !ortho_col_indices || !ortho_row_ptr)) return ORTHO_B200_ERR_NULL;
 
-    const int64_t need = has_ortho ? min_workspace_bytes(M, K, N) : 0;
+    // the same kernel choice as ortho_b200_forward makes for these sizes, so that both entries give the
+    // same bits; only the tensor-core regime with an active sparse term needs scratch
+    const bool decode = decode_regime(M, N, K);
+    const int64_t need = (has_ortho && !decode) ? min_workspace_bytes(M, K, N) : 0;
     if (need > (int64_t)ORTHO_B200_STATIC_SCRATCH_BYTES) return ORTHO_B200_ERR_SCRATCH_LIMIT;
 
     int major = 0, dev = 0;
@@ -88,6 +92,6 @@ extern "C" int ortho_b200_forward_static_scratch(const void *q_weight, const voi
     a.workspace = scratch;
     a.workspace_bytes = (int64_t)ORTHO_B200_STATIC_SCRATCH_BYTES;
     a.stream = (cudaStream_t)stream;
-    if (M <= ORTHO_B200_DECODE_MAX_M) return launch_decode(a);
+    if (decode) return launch_decode(a);
     return launch_prefill(a);
 }

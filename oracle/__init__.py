@@ -30,9 +30,21 @@ _PATHS = {
 }
 
 
-def build(ref_root: str = "/root/reference", quiet: bool = True) -> None:
+def reference_root():
+    """Where the reference's source tree lies: ``$LIBORTHO_REF``, else a ``reference`` directory
+    beside this repository; None when neither holds ``src/ortho.c``."""
+    cands = [os.environ.get("LIBORTHO_REF"), os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")]
+    for c in cands:
+        if c and os.path.isfile(os.path.join(c, "src", "ortho.c")):
+            return os.path.abspath(c)
+    return None
+
+
+def build(ref_root=None, quiet: bool = True) -> None:
     """Compile the checker libraries (``make -C oracle``).  The ``_ref`` libraries are only
-    rebuilt when the reference tree is present; otherwise the prebuilt files are kept."""
+    rebuilt when the reference tree is found (``ref_root`` or ``reference_root()``); otherwise the
+    prebuilt files are kept."""
+    ref_root = ref_root or reference_root() or ""
     out = subprocess.run(["make", "-C", _HERE, f"REF={ref_root}", "all"],
                          capture_output=True, text=True)
     if out.returncode != 0:

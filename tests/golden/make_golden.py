@@ -16,10 +16,10 @@ packer_small.npz      buffers produced by the reference's Python packer
                       (torch_bind/ortho_linear.py:79-128 with tools/sieve.py) for a seeded 48x64
                       layer, plus the sieve outputs they were built from.
 cfg_small.npz         reference-forward outputs for seeded small layers from
-                      libortho_b200.workloads (ragged N, Zipf rows, an empty ortho, alpha sweep).
+                      workloads (ragged N, Zipf rows, an empty ortho, alpha sweep).
 cfg0_y.npz            reference-forward outputs of the single-layer benchmark configuration
                       (4096x4096, M=8, 1 % density, alpha 0 and 1); inputs are regenerated from the
-                      seed by libortho_b200.workloads.
+                      seed by workloads.
 """
 import ctypes
 import os
@@ -32,10 +32,12 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests"))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
-
 import oracle  # noqa: E402
-from libortho_b200 import workloads as wl  # noqa: E402
+
+REF = sys.argv[1] if len(sys.argv) > 1 else oracle.reference_root()
+if not REF:
+    sys.exit("usage: make_golden.py <path of the reference tree>   (or set LIBORTHO_REF)")
+import workloads as wl  # noqa: E402
 
 RAND_MAX = 2147483647
 

@@ -8,7 +8,8 @@ import torch.distributed as dist
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 
-from libortho_b200 import OrthoLinear, _lib, workloads as wl        # noqa: E402
+from libortho_b200 import OrthoLinear, _lib
+import workloads as wl        # noqa: E402
 from libortho_b200.sharded import ShardedOrthoLinear               # noqa: E402
 
 

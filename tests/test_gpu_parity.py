@@ -5,7 +5,8 @@ import torch
 
 from conftest import assert_close, errors, golden, layer_oracle
 from cases import SMALL_CASES
-from libortho_b200 import OrthoLinear, _C_ops, _lib, workloads as wl
+from libortho_b200 import OrthoLinear, _C_ops, _lib
+import workloads as wl
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -168,7 +169,14 @@ def test_decode_sweep_shapes_against_oracle(oracle_mod, K, N):
         assert np.isfinite(y).all()
 
 
-@pytest.mark.parametrize("K,N", [(8192, 10240), (28672, 8192)])
+def sampled_oracle(oracle_mod, cpu_layer, rows, x_cpu, alpha):
+    """Oracle output for the listed rows (rows are independent in the reference, src/ortho.c:354-366:
+    a one-row slice of the layer is a smaller layer with the same arithmetic) and the given tokens."""
+    sub = [cpu_layer.rows(r, r + 1) for r in rows]
+    return np.concatenate([layer_oracle(oracle_mod, s_, x_cpu, alpha, threads=1) for s_ in sub], axis=1)
+
+
+@pytest.mark.parametrize("K,N", wl.CFG3_SHAPES)
 def test_sharded_config_shapes_against_oracle(oracle_mod, K, N):
     """Llama-70B-style shapes (0.3 % ortho) at M in {1, 32, 4096}: a row sample of the output against
     the oracle, for all tokens at M <= 32 and for a seeded token sample at M = 4096 (tokens and rows
@@ -246,7 +254,8 @@ def test_error_statuses_surface_as_exceptions():
 
 @pytest.mark.parametrize("K,N,M", [(384, 200, 200), (1024, 272, 130), (4096, 512, 257), (64, 64, 65), (2048, 1024, 1024)])
 def test_tensor_core_path_base_only_against_oracle(oracle_mod, K, N, M):
-    """M > 64 takes the tcgen05 kernel.  alpha = 0: base term only, ragged tiles in M, N and K."""
+    """More than 24 tokens on a layer this wide take the tcgen05 kernel.  alpha = 0: base term only, ragged
+    tiles in M, N and K."""
     layer = wl.make_layer(K, N, 0.01, seed=91)
     x = wl.make_input(M, K, seed=91)
     y = run_layer(layer.to(DEV), x.to(DEV), 0.0).float().cpu().numpy()
@@ -286,18 +295,64 @@ def test_tensor_core_path_with_sparse_term_against_oracle(oracle_mod, kind, K, N
         _lib.check(st, "ortho_b200_forward")
 
 
-@pytest.mark.parametrize("K,N,M,d,alpha,split", [(256, 128, 1, 0.0, 1.0, 1), (1024, 300, 16, 0.02, 1.0, 2),
-                                                  (4096, 1100, 5, 0.005, 0.5, 0), (11008, 512, 32, 0.005, 0.5, 0),
-                                                  (2048, 260, 20, 0.01, 1.0, 3)])
-def test_tcgen05_decode_kernel_against_oracle(oracle_mod, K, N, M, d, alpha, split):
-    """The opt-in tcgen05 decode kernel (weights converted into tensor memory, cluster split-K with a
-    distributed-shared-memory reduction) through the tuning hook."""
-    layer = wl.make_layer(K, N, d, seed=95)
-    x = wl.make_input(M, K, seed=95)
-    try:
-        assert _lib.lib().ortho_b200_set_decode_config(-2, 0, 0, split) == 0
-        y = run_layer(layer.to(DEV), x.to(DEV), alpha)
-    finally:
-        _lib.lib().ortho_b200_set_decode_config(0, 0, 0, 0)
+@pytest.mark.parametrize("M", wl.CFG2_M)
+def test_prefill_configuration_at_its_own_shape(oracle_mod, M):
+    """8192 x 8192, 0.1 % ortho with Zipf(1.2) row loads, alpha = 0.5, exactly as the benchmark builds it, with
+    plan and full workspace (long-row segments and the split-K of the last wave are both live): the longest
+    rows, tile-edge rows and a seeded row sample against the oracle for a seeded token sample."""
+    K, N = wl.CFG2_SHAPE
+    layer = wl.make_zipf_layer(K, N, wl.CFG2_DENSITY, seed=0, device=DEV, alpha=wl.CFG2_ALPHA)
+    cpu = layer.to("cpu")
+    counts = (cpu.row_ptr[1:] - cpu.row_ptr[:-1]).long()
+    assert int(counts.max()) > 4096                      # the head of the Zipf law is really there
+    g = torch.Generator().manual_seed(11)
+    rows = sorted(set(torch.topk(counts, 8).indices.tolist()) | {0, 127, 128, N - 129, N - 1}
+                  | set(torch.randperm(N, generator=g)[:40].tolist()))
+    plan = _C_ops.Plan(layer.row_ptr, layer.col, layer.vals, K, N)
+    ws = torch.empty(_C_ops.workspace_bytes(M, K, N, plan), dtype=torch.uint8, device=DEV)
+    x = wl.make_input(M, K, seed=M, device=DEV)
+    y = torch.empty(M, N, dtype=torch.float16, device=DEV)
+    _C_ops.forward(layer.base_weight, layer.base_scales, layer.vals, layer.col, layer.row_ptr, x, y, wl.CFG2_ALPHA,
+                   plan=plan, workspace=ws)
+    torch.cuda.synchronize()
     assert _lib.lib().ortho_b200_query_kernel_status() == 0
-    assert_close(y.float().cpu().numpy(), layer_oracle(oracle_mod, layer, x, alpha), f"tc decode {K}x{N} M={M}")
+    toks = sorted({0, 255, 256, M - 1} | set(torch.randperm(M, generator=g)[:60].tolist()))
+    ref = sampled_oracle(oracle_mod, cpu, rows, x[toks].cpu(), wl.CFG2_ALPHA)
+    assert_close(y[toks][:, rows].float().cpu().numpy(), ref, f"prefill configuration M={M}")
+    assert bool(torch.isfinite(y).all())
+    # base only: bit-identical to the layer without entries (the kill switch)
+    y0 = torch.empty_like(y)
+    _C_ops.forward(layer.base_weight, layer.base_scales, layer.vals, layer.col, layer.row_ptr, x, y0, 0.0, plan=plan, workspace=ws)
+    ye = torch.empty_like(y)
+    _C_ops.forward(layer.base_weight, layer.base_scales, None, None, None, x, ye, 1.0, workspace=ws)
+    assert torch.equal(y0, ye)
+
+
+@pytest.mark.parametrize("variant", ["threshold", "top1pct"])
+def test_sieve_derived_layer_alpha_sweep(oracle_mod, variant):
+    """Sieve-derived split (W ~ N(0, 0.02^2), low-rank-plus-noise calibration, curvature threshold 10): the
+    threshold leaves the ortho part empty, so every alpha must give the same bits; the keep-top-1 % variant
+    exercises a sieve-shaped non-empty ortho.  M in {1, 2048}, alpha in {0, 0.25, 0.5, 1} against the oracle."""
+    cpu = wl.make_sieve_layer() if variant == "threshold" else wl.make_sieve_layer(sparsity_target=0.01)
+    assert (cpu.nnz == 0) == (variant == "threshold")
+    layer = cpu.to(DEV)
+    K, N = cpu.K, cpu.N
+    g = torch.Generator().manual_seed(13)
+    rows = sorted({0, 15, 16, 127, 128, N - 1} | set(torch.randperm(N, generator=g)[:40].tolist()))
+    for M in (1, 2048):
+        x = wl.make_input(M, K, seed=M, device=DEV)
+        toks = list(range(M)) if M <= 64 else sorted({0, 255, 256, M - 1} | set(torch.randperm(M, generator=g)[:60].tolist()))
+        outs = {}
+        for alpha in (0.0, 0.25, 0.5, 1.0):
+            y = run_layer(layer, x, alpha)
+            assert _lib.lib().ortho_b200_query_kernel_status() == 0
+            ref = sampled_oracle(oracle_mod, cpu, rows, x[toks].cpu(), alpha)
+            assert_close(y[toks][:, rows].float().cpu().numpy(), ref, f"sieve {variant} M={M} alpha={alpha}")
+            outs[alpha] = y
+        if cpu.nnz == 0:
+            for alpha in (0.25, 0.5, 1.0):
+                assert torch.equal(outs[alpha], outs[0.0])
+        else:
+            d1 = (outs[1.0].float() - outs[0.0].float())
+            assert d1.abs().max() > 1e-3
+            assert torch.allclose(outs[0.5].float() - outs[0.0].float(), 0.5 * d1, atol=1.5e-2, rtol=0)

@@ -9,7 +9,8 @@ import pytest
 import torch
 
 from conftest import ROOT, assert_close, layer_oracle
-from libortho_b200 import _C_ops, workloads as wl
+from libortho_b200 import _C_ops
+import workloads as wl
 from libortho_b200.sharded import shard_bounds, slice_rows
 
 pytestmark = pytest.mark.gpu

@@ -9,7 +9,8 @@ import pytest
 import torch
 
 from conftest import ROOT, golden
-from libortho_b200 import OrthoLinear, _lib, sieve, workloads as wl
+from libortho_b200 import OrthoLinear, _lib, sieve
+import workloads as wl
 
 
 def test_packer_matches_reference_buffers():

@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 
 from conftest import golden, layer_oracle
-from libortho_b200 import workloads as wl
+import workloads as wl
 
 
 def test_unpack_rule_matches_numpy_statement(oracle_mod):

@@ -11,7 +11,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from conftest import ROOT
-from libortho_b200 import workloads as wl
+import workloads as wl
 from libortho_b200.sharded import ShardedOrthoLinear, shard_bounds, slice_rows
 
 

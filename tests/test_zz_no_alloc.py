@@ -12,8 +12,9 @@ import numpy as np
 import pytest
 import torch
 
-from conftest import REL_FRO_TOL, MAX_ABS_TOL, errors
-from libortho_b200 import _C_ops, _lib, workloads as wl
+from conftest import REL_FRO_TOL, MAX_ABS_TOL, assert_close, errors, layer_oracle
+from libortho_b200 import _C_ops, _lib
+import workloads as wl
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -33,8 +34,11 @@ def _static(layer, x, alpha):
 
 
 def _ordinary(layer, x, alpha):
+    """The ordinary entry point without a plan and with a freshly allocated workspace of the size of the
+    built-in array, so that both entries make the same choices and must produce the same bits."""
     y = torch.empty(x.shape[0], layer.N, dtype=torch.float16, device=x.device)
-    _C_ops.forward(layer.base_weight, layer.base_scales, layer.vals, layer.col, layer.row_ptr, x, y, alpha)
+    ws = torch.empty(LIMIT, dtype=torch.uint8, device=x.device)
+    _C_ops.forward(layer.base_weight, layer.base_scales, layer.vals, layer.col, layer.row_ptr, x, y, alpha, workspace=ws)
     return y
 
 
@@ -43,7 +47,7 @@ def _check(y, ref, what):
     assert rel <= REL_FRO_TOL and mx <= MAX_ABS_TOL, f"{what}: rel_fro={rel:.3e} max_abs={mx:.3e}"
 
 
-def test_two_calls_in_a_row_match_the_ordinary_forward():
+def test_two_calls_in_a_row_match_the_ordinary_forward(oracle_mod):
     # two different layers and token counts back to back: the second call finds the first call's
     # transposed activations and sparse sums still in the shared array and must not be affected
     a = wl.make_layer(1024, 520, 0.01, seed=101, device=DEV)
@@ -59,6 +63,10 @@ def test_two_calls_in_a_row_match_the_ordinary_forward():
     assert _lib.lib().ortho_b200_query_kernel_status() == 0
     _check(y1, ra, "first call")
     _check(y2, rb, "second call")
+    assert torch.equal(y1, ra) and torch.equal(y2, rb)      # both entries are reproducible and route alike
+    # and against the CPU oracle, not only against the other CUDA entry
+    assert_close(y1.float().cpu().numpy(), layer_oracle(oracle_mod, a, xa, 1.0), "first call vs oracle")
+    assert_close(y2.float().cpu().numpy(), layer_oracle(oracle_mod, b, xb, 0.5), "second call vs oracle")
     # same inputs again after the array has been overwritten by the other layer
     st3, y3 = _static(a, xa, 1.0)
     torch.cuda.synchronize()
@@ -86,3 +94,19 @@ def test_regimes_without_scratch_and_the_size_limit():
     st, _ = _static(layer, xbig, 1.0)
     assert st == 10 and b"scratch" in _lib.lib().ortho_b200_strerror(st)
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("M", [25, 32, 64])
+def test_token_counts_between_the_regimes_route_like_the_ordinary_forward(oracle_mod, M):
+    """25..64 tokens: a wide layer takes the tensor-core kernel (scratch from the built-in array), a
+    narrow one the streaming kernels (no scratch); either way the bits equal the ordinary entry's."""
+    wide = wl.make_layer(1024, 4352, 0.01, seed=105, device=DEV)        # N > 4096: tensor-core regime
+    narrow = wl.make_layer(1024, 520, 0.01, seed=106, device=DEV)
+    for layer in (wide, narrow):
+        x = wl.make_input(M, layer.K, seed=M, device=DEV)
+        st, y = _static(layer, x, 1.0)
+        torch.cuda.synchronize()
+        assert st == 0
+        assert _lib.lib().ortho_b200_query_kernel_status() == 0
+        assert torch.equal(y, _ordinary(layer, x, 1.0))
+        assert_close(y.float().cpu().numpy(), layer_oracle(oracle_mod, layer, x, 1.0), f"N={layer.N} M={M}")

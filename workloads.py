@@ -54,7 +54,7 @@ class Layer:
                      self.col[e0:e1].contiguous(), self.vals[e0:e1].contiguous(), self.alpha)
 
     def to_module(self):
-        from .ortho_linear import OrthoLinear
+        from libortho_b200.ortho_linear import OrthoLinear
         m = OrthoLinear(self.K, self.N, device=self.base_weight.device)
         m.base_weight = self.base_weight
         m.base_scales = self.base_scales
@@ -222,8 +222,8 @@ def make_sieve_layer(K: int = 4096, N: int = 4096, n_cal: int = 2048, rank: int 
     H = X^T X / n + 0.01 mean(diag H) I, inverted on the host in FP64; the Hessian sieve splits
     W into base and ortho at the stated threshold (or keeps the top ``sparsity_target``
     fraction); the layer is then packed with ``OrthoLinear.load_from_weights``."""
-    from .ortho_linear import OrthoLinear
-    from .sieve import hessian_sieve
+    from libortho_b200.ortho_linear import OrthoLinear
+    from libortho_b200.sieve import hessian_sieve
     g = _gen(seed, "cpu")
     W = torch.randn(N, K, generator=g) * 0.02
     A = torch.randn(n_cal, rank, generator=g)
