@@ -231,6 +231,24 @@ ORTHO_B200_API int ortho_b200_csr_count(const float *w_ortho, int64_t N, int64_t
 ORTHO_B200_API int ortho_b200_csr_fill(const float *w_ortho, int64_t N, int64_t K, const int32_t *row_ptr,
                        int32_t *col_out, void *val_f16_out, void *stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Device-side Hessian sieve: splits FP32 weights W [N, K] that are already on the GPU into the
+ * INT4-representable base and the sparse residual, bit-identical to hessian_sieve / quantize_int4 of
+ * the reference (tools/sieve.py:13-23, 25-76):
+ *   base  = clamp(round_half_even(W / s), -8, 7) * s with s = max(rowmax|W|, 1e-8) / 7
+ *   ortho = (W - base) where (W - base)^2 / (h_inv_diag[k] + 1e-6) > threshold, else (signed) zero
+ * keep_top_k < 0: threshold = curvature_thresh.  keep_top_k >= 0: threshold = the keep_top_k-th largest
+ * score (the caller passes int(sparsity_target * N * K); 0 keeps nothing), found on the device by a
+ * byte-wise radix select without storing the scores.  h_inv_diag is the FP32 [K] diagonal.  scratch:
+ * ortho_b200_sieve_scratch_bytes(N) bytes, 256-byte aligned.  K a multiple of 4, pointers 16-byte aligned.
+ * The outputs feed ortho_b200_pack_base / ortho_b200_csr_count / ortho_b200_csr_fill.
+ * ------------------------------------------------------------------------------------------- */
+ORTHO_B200_API int64_t ortho_b200_sieve_scratch_bytes(int64_t N);
+ORTHO_B200_API int ortho_b200_sieve(const float *w, const float *h_inv_diag, int64_t N, int64_t K,
+                       float curvature_thresh, int64_t keep_top_k,
+                       float *w_base_out, float *w_ortho_out,
+                       void *scratch, int64_t scratch_bytes, void *stream);
+
 /* Synchronises the device and reports whether any kernel of this library gave up on a bounded
  * wait since the last query (ERR_KERNEL, and the flag is cleared) or not (OK).  Replaces the
  * cudaDeviceSynchronize + error check at the end of the reference dispatcher

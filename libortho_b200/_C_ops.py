@@ -309,3 +309,27 @@ def pack_ortho_csr(w_ortho: torch.Tensor):
             _lib.check(_lib.lib().ortho_b200_csr_fill(w.data_ptr(), N, K, row_ptr.data_ptr(), col.data_ptr(), val.data_ptr(),
                                                      stream), "ortho_b200_csr_fill")
     return row_ptr, col, val
+
+
+def hessian_sieve(weight: torch.Tensor, h_inv_diag: torch.Tensor, curvature_thresh: float = 10.0,
+                  keep_top_k: int = -1):
+    """Device-side Hessian sieve of an FP32 ``[N, K]`` CUDA tensor: ``(w_base, w_ortho)`` FP32 ``[N, K]``,
+    bit-identical to the torch chain of ``libortho_b200.sieve.hessian_sieve``.  ``keep_top_k < 0`` uses the
+    curvature threshold, otherwise the ``keep_top_k``-th largest score is the threshold."""
+    if not weight.is_cuda or weight.dtype != torch.float32 or weight.dim() != 2:
+        raise TypeError("weight must be a 2-D float32 CUDA tensor")
+    w = weight.contiguous()
+    N, K = w.shape
+    dev = w.device
+    h = h_inv_diag.to(device=dev, dtype=torch.float32).contiguous()
+    if h.dim() != 1 or h.numel() != K:
+        raise ValueError("h_inv_diag must hold one entry per input feature")
+    wb, wo = torch.empty_like(w), torch.empty_like(w)
+    need = int(_lib.lib().ortho_b200_sieve_scratch_bytes(N))
+    scratch = torch.empty(need, dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        st = _lib.lib().ortho_b200_sieve(w.data_ptr(), h.data_ptr(), N, K, float(curvature_thresh), int(keep_top_k),
+                                        wb.data_ptr(), wo.data_ptr(), scratch.data_ptr(), need,
+                                        torch.cuda.current_stream(dev).cuda_stream)
+    _lib.check(st, "ortho_b200_sieve")
+    return wb, wo

@@ -69,6 +69,10 @@ def _declare(l):
     l.ortho_b200_csr_count.argtypes = [vp, i64, i64, vp, vp]
     l.ortho_b200_csr_fill.restype = c.c_int
     l.ortho_b200_csr_fill.argtypes = [vp, i64, i64, vp, vp, vp, vp]
+    l.ortho_b200_sieve_scratch_bytes.restype = i64
+    l.ortho_b200_sieve_scratch_bytes.argtypes = [i64]
+    l.ortho_b200_sieve.restype = c.c_int
+    l.ortho_b200_sieve.argtypes = [vp, vp, i64, i64, c.c_float, i64, vp, vp, vp, i64, vp]
     l.ortho_b200_comm_create.restype = c.c_int
     l.ortho_b200_comm_create.argtypes = [c.c_int, c.c_int, i64, c.POINTER(vp)]
     l.ortho_b200_comm_export.restype = c.c_int
@@ -101,6 +105,7 @@ EXPORTS = [
     "ortho_b200_comm_set_timeout_ms", "ortho_b200_comm_destroy", "ortho_b200_forward_gather",
     "ortho_b200_comm_set_deferred", "ortho_b200_comm_wait",
     "ortho_b200_pack_base", "ortho_b200_csr_count", "ortho_b200_csr_fill",
+    "ortho_b200_sieve_scratch_bytes", "ortho_b200_sieve",
 ]
 
 

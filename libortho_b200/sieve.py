@@ -1,4 +1,5 @@
-"""Offline producers of the layer's inputs (host-side torch code, not on the hot path).
+"""Producers of the layer's inputs (not on the hot path): host-side torch code, and for FP32 weights that
+already live on the GPU the device-side sieve (``csrc/sieve.cu``) with bit-identical results.
 
 Same call surface as the reference's ``tools/sieve.py`` so that callers can switch imports:
 ``quantize_int4`` (``tools/sieve.py:13-23``), ``hessian_sieve`` (``:25-76``),
@@ -31,9 +32,14 @@ def hessian_sieve(weight: torch.Tensor, H_inv: torch.Tensor, curvature_thresh: f
     to its diagonal.  The residual is kept where score > threshold, the threshold being
     ``curvature_thresh`` or, when ``sparsity_target`` is given, the k-th largest score with
     k = int(sparsity_target * numel) ("keep the top fraction"; k == 0 keeps nothing)."""
+    d = torch.diag(H_inv) if H_inv.dim() > 1 else H_inv
+    if weight.is_cuda and weight.dtype == torch.float32 and weight.dim() == 2 and weight.shape[1] % 4 == 0:
+        # weights already on the GPU: the device-side sieve produces the same bits as the chain below
+        from . import _C_ops
+        k = -1 if sparsity_target is None else int(sparsity_target * weight.numel())
+        return _C_ops.hessian_sieve(weight, d, curvature_thresh, k)
     w_base = quantize_int4(weight)
     residual = weight - w_base
-    d = torch.diag(H_inv) if H_inv.dim() > 1 else H_inv
     score = residual.pow(2) / (d + 1e-6).unsqueeze(0)
     if sparsity_target is None:
         thresh = curvature_thresh
