@@ -2,21 +2,26 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (``config.workload``): the Llama-7B-style decode sweep -- four layers (in->out:
-4096->12288, 4096->4096, 4096->22016, 11008->4096), M in {1, 4, 16} FP16 tokens each, INT4 base
-from W~N(0,0.02^2), 0.5 % uniform FP16 ortho ~N(0,0.05^2), alpha=1, seeded synthetic tensors.
-One "step" is one pass over the sweep (12 forwards).  Steps rotate over several distinct copies
-of the four layers so that every forward streams its weights from HBM rather than from L2.
+Workload (``config.workload``), the same for every N: the Llama-2-70B-style projections in the decode
+regime -- four layers (in->out: 8192->10240, 8192->8192, 8192->57344, 28672->8192), one FP16 token each,
+INT4 base from W~N(0,0.02^2), 0.3 % uniform FP16 ortho ~N(0,0.05^2), alpha=1, seeded synthetic tensors.
+One "step" is one pass over the four layers.  With N > 1 (launched by torch.distributed.run, one rank
+per GPU) every layer is sharded over output rows, each rank runs its shard and the kernel itself stores
+its output slice into every rank's peer-mapped buffer (``--exchange nccl``: an NCCL all-gather instead);
+``scaling`` is "strong" (the layers are fixed, the per-GPU share shrinks).  Steps rotate over as many
+distinct copies of the layers as it takes for a GPU's share to exceed the L2 several times.
 
-``value``   decode GB/s = algorithmic bytes of the step / device time, inputs resident in HBM, the
-            step replayed as a CUDA graph (kernels back to back, timed with CUDA events).
-``e2e``     the same metric through ``OrthoLinear.forward`` with host buffers: per forward, X is
-            copied from pinned host memory, and Y is copied back, inside the timed region.
-``roofline`` HBM roofline of the decode kernel from the same timed region.
+``value``    decode GB/s = algorithmic bytes of the step (whole layers) / device time (max over ranks),
+             inputs resident in HBM, the step replayed as a CUDA graph, timed with CUDA events.
+``e2e``      the same metric through ``OrthoLinear.forward`` / ``ShardedOrthoLinear.forward`` with host
+             buffers: per forward X comes from pinned host memory and Y goes back, inside the timed region.
+``roofline`` HBM roofline of the decode kernel from the same timed region (per GPU).
 ``cpu_baseline`` the reference's own CPU forward timed on this host (N=1 only).
-``prefill`` (extra) tensor-core regime, 8192x8192 with Zipf-row ortho, TFLOP/s per M.
-With N > 1 (launched by torch.distributed.run) every layer is sharded over output rows, each
-rank runs its shard and the outputs are all-gathered with NCCL; ``scaling`` is "strong".
+``regimes``  (extra, every N) the same four layers at M=32 (GB/s) and M=4096 (TFLOP/s) with the exchange
+             cost; ``decode_sweep_7b`` and ``prefill`` (extra, N=1) the Llama-7B-style decode sweep
+             (M in {1,4,16}, 0.5 % ortho) and the 8192x8192 Zipf-row prefill configuration.
+With N > 1 the gathered output of every layer is compared with the unsharded forward and the kernels'
+status word is read after the timed loop; a mismatch or a timed-out wait makes the run fail.
 """
 from __future__ import annotations
 
@@ -33,11 +38,14 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 METRIC = "OrthoLinear decode GB/s (% HBM peak) & prefill TFLOP/s at 1/2/4/8 B200"
-WORKLOAD = "decode sweep: (4096->12288, 4096->4096, 4096->22016, 11008->4096) x M{1,4,16}, 0.5% ortho, alpha=1"
-N_COPIES = 6          # distinct weight sets rotated through (6 x ~100 MB >> 126 MB of L2)
+WORKLOAD = ("70B-style decode: (8192->10240, 8192->8192, 8192->57344, 28672->8192) x M=1, INT4 base + 0.3% ortho, "
+            "alpha=1, N-sharded over the GPUs with output gather")
+L2_BYTES = 126 << 20
 
-
-NCU_TRAFFIC_RATIO = 47.15 / 47.98    # measured DRAM traffic / algorithmic bytes of the captured decode launch
+# DRAM bytes moved per algorithmic byte by the streaming decode kernel, from an ncu capture of one launch
+# (dram__bytes_read.sum + dram__bytes_write.sum = 47.15 MB for the 47.98 MB 4096->22016 M=1 launch); the
+# kernel reads every weight byte once, so traffic grows in proportion to the algorithmic bytes
+NCU_TRAFFIC_RATIO = 47.15 / 47.98
 
 
 def peaks():
@@ -89,37 +97,40 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def sweep_items():
+def _cpu_impl():
+    import oracle
+    impl, kind = ("reference_fast", "reference") if oracle.available("reference_fast") else ("port", "port")
+    if impl == "port":
+        oracle.build()
+    return oracle, impl, kind
+
+
+def _cpu_layers():
+    """The four layers of the workload as numpy arrays for the CPU forward (seed 0)."""
     import workloads as wl
-    return [(K, N, M) for M in wl.CFG1_M for (K, N) in wl.CFG1_SHAPES]
+    out = []
+    for (K, N) in wl.CFG3_SHAPES:
+        L = wl.make_layer(K, N, wl.CFG3_DENSITY, seed=0)
+        out.append((L, (L.base_weight.numpy(), L.base_scales.float().numpy(), L.row_ptr.numpy(), L.col.numpy(),
+                        L.vals.float().numpy()), wl.make_input(1, K, seed=1).float().numpy()))
+    return out
 
 
 # ------------------------------------------------------------------------------------------------
 def run_reference(args):
     """The reference's own CPU forward (unmodified src/ortho.c behind oracle/_ref, built with the
-    reference's flags) on this host's cores; each step is one pass over the same decode sweep."""
+    reference's flags) on all host threads; each step is one pass over the same four layers at M=1."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    import numpy as np
-    import oracle
-    import workloads as wl
-    impl, kind = ("reference_fast", "reference") if oracle.available("reference_fast") else ("port", "port")
-    if impl == "port":
-        oracle.build()
+    oracle, impl, kind = _cpu_impl()
     threads = oracle.host_threads()
-    layers = {}
-    for (K, N) in wl.CFG1_SHAPES:
-        L = wl.make_layer(K, N, wl.CFG1_DENSITY, seed=0)
-        layers[(K, N)] = (L, L.base_weight.numpy(), L.base_scales.float().numpy(), L.row_ptr.numpy(), L.col.numpy(),
-                          L.vals.float().numpy())
-    xs = {(K, M): wl.make_input(M, K, seed=M).float().numpy() for (K, N, M) in sweep_items()}
-    step_bytes = sum(layers[(K, N)][0].algorithmic_bytes(M) for (K, N, M) in sweep_items())
+    layers = _cpu_layers()
+    step_bytes = sum(L.algorithmic_bytes(1) for L, _, _ in layers)
 
     def step():
-        for (K, N, M) in sweep_items():
-            _, pw, sc, rp, co, va = layers[(K, N)]
-            oracle.forward_csr(pw, sc, rp, co, va, xs[(K, M)], 1.0, impl=impl, threads=threads)
+        for _, a, x in layers:
+            oracle.forward_csr(*a, x, 1.0, impl=impl, threads=threads)
 
     for _ in range(max(0, args.warmup)):
         step()
@@ -128,12 +139,12 @@ def run_reference(args):
         step()
     dt = time.perf_counter() - t0
     val = step_bytes * args.steps / dt / 1e9
-    sample = f"{args.steps} full passes of the decode sweep (12 forwards each), {threads} threads"
+    sample = f"{args.steps} full passes over the four layers at M=1, {threads} threads (rows split over threads)"
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "device": "host CPU"},
+        "config": {"workload": WORKLOAD},
         "cpu_baseline": {"value": val, "unit": "GB/s", "cores": threads, "kind": kind, "sample": sample},
         "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -141,7 +152,60 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+def cpu_baseline():
+    """Reference CPU forward (oracle/_ref, reference flags) on this host: passes over the workload for ~10 s."""
+    oracle, impl, kind = _cpu_impl()
+    threads = oracle.host_threads()
+    layers = _cpu_layers()
+    step_bytes = sum(L.algorithmic_bytes(1) for L, _, _ in layers)
+    n, t_total = 0, 0.0
+    while n < 3 or (t_total < 10.0 and n < 200):
+        t0 = time.perf_counter()
+        for _, a, x in layers:
+            oracle.forward_csr(*a, x, 1.0, impl=impl, threads=threads)
+        t_total += time.perf_counter() - t0
+        n += 1
+    return {"value": step_bytes * n / t_total / 1e9, "unit": "GB/s", "cores": threads, "kind": kind,
+            "sample": f"{n} full passes over the four layers at M=1, {t_total:.2f} s wall", "ms_per_step": t_total / n * 1e3}
+
+
 # ------------------------------------------------------------------------------------------------
+class _Timer:
+    """CUDA-graph timing helper: a graph of ``n`` calls ``fn(i)`` is replayed; device time per call from CUDA
+    events on the launch stream, median over replays, max over ranks."""
+
+    def __init__(self, torch, dist, dev, stream, world):
+        self.torch, self.dist, self.dev, self.stream, self.world = torch, dist, dev, stream, world
+
+    def us_per_call(self, fn, n, replays=5, warm=2):
+        torch = self.torch
+        with torch.cuda.stream(self.stream):
+            fn(0)                                   # first call of a kernel variant happens outside the capture
+            self.stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=self.stream):
+                for i in range(n):
+                    fn(i)
+            for _ in range(warm):
+                g.replay()
+            self.stream.synchronize()
+            if self.world > 1:
+                self.dist.barrier()
+            ts = []
+            for _ in range(replays):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(self.stream)
+                g.replay()
+                e1.record(self.stream)
+                e1.synchronize()
+                ts.append(e0.elapsed_time(e1) * 1e3 / n)
+        t = torch.tensor([statistics.median(ts)], device=self.dev)
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        del g
+        return float(t.item())
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -158,45 +222,43 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
     pk = peaks()
     lib = _lib.lib()
+    stream = torch.cuda.Stream(dev)
+    timer = _Timer(torch, dist, dev, stream, world)
+    shapes = wl.CFG3_SHAPES
+    failures = []
 
-    items = sweep_items()
-    # ---- build N_COPIES sets of (sharded) layers, plans and output buffers ------------------
-    sets = []
-    for c in range(N_COPIES):
+    # ---- the four layers, sharded over the ranks; enough distinct copies for a GPU's share to exceed L2 -------
+    per_gpu_set = sum(K * N // 2 for (K, N) in shapes) // world
+    n_copies = max(2, min(8, -(-int(2.5 * L2_BYTES) // per_gpu_set)))
+    sets, fulls = [], {}
+    for c in range(n_copies):
         layers = {}
-        for (K, N) in wl.CFG1_SHAPES:
-            L = wl.make_layer(K, N, wl.CFG1_DENSITY, seed=c, device=dev)
-            if world > 1:
-                n0, n1 = shard_bounds(N, world)[rank]
-                full = L
-                L = full.rows(n0, n1)
-                L._full_bytes = {M: full.algorithmic_bytes(M) for M in wl.CFG1_M}
-                del full
-            else:
-                L._full_bytes = {M: L.algorithmic_bytes(M) for M in wl.CFG1_M}
-            plan = _C_ops.Plan(L.row_ptr, L.col, L.vals, L.K, L.N)
-            layers[(K, N)] = (L, plan)
+        for (K, N) in shapes:
+            full = wl.make_layer(K, N, wl.CFG3_DENSITY, seed=c, device=dev)
+            n0, n1 = shard_bounds(N, world)[rank]
+            L = full.rows(n0, n1) if world > 1 else full
+            L._full_bytes = {M: full.algorithmic_bytes(M) for M in wl.CFG3_M}
+            L._full_flops = {M: full.algorithmic_flops(M) for M in wl.CFG3_M}
+            L._n0 = n0
+            if c == 0 and world > 1:
+                fulls[(K, N)] = full              # kept for the check of the gathered output
+            del full
+            layers[(K, N)] = (L, _C_ops.Plan(L.row_ptr, L.col, L.vals, L.K, L.N))
         sets.append(layers)
     torch.cuda.empty_cache()
-    step_bytes = sum(sets[0][(K, N)][0]._full_bytes[M] for (K, N, M) in items)
-    xs = {(K, M): wl.make_input(M, K, seed=M, device=dev) for (K, N, M) in items}
-    ys = {(K, N, M): torch.empty(M, sets[0][(K, N)][0].N, dtype=torch.float16, device=dev) for (K, N, M) in items}
-    yg = {(K, N, M): torch.empty(world * M, sets[0][(K, N)][0].N, dtype=torch.float16, device=dev)
-          for (K, N, M) in items} if world > 1 else None
+    step_bytes = sum(sets[0][kn][0]._full_bytes[1] for kn in shapes)
+    xs = {(K, M): wl.make_input(M, K, seed=M, device=dev) for (K, N) in shapes for M in wl.CFG3_M}
 
-    # multi-GPU exchange: peer stores issued by the decode kernel itself (default), or NCCL
-    exchange, comm, comm_off = "none", None, {}
+    # multi-GPU exchange: peer stores issued by the kernels themselves (default), or NCCL
+    exchange, comm = "none", None
+    max_n = max(N for _, N in shapes)
+    region = {M: (2 * M * max_n + 255) // 256 * 256 for M in wl.CFG3_M}
     if world > 1:
         exchange = args.exchange
         if exchange == "peer":
             try:
-                off = 0
-                for (K, N, M) in items:
-                    comm_off[(K, N, M)] = off
-                    off += (2 * M * N + 255) // 256 * 256
-                comm = _C_ops.Comm(rank, world, off, device=dev)
+                comm = _C_ops.Comm(rank, world, 2 * region[max(wl.CFG3_M)], device=dev)
                 comm.connect_group()
-                comm.set_deferred(not args.no_deferred)
             except Exception as e:       # no inter-process mapping on this box: the NCCL exchange still measures the path
                 print(f"[bench] peer-mapped buffers unavailable ({e}); using the NCCL all-gather", file=sys.stderr)
                 exchange, comm = "nccl", None
@@ -204,28 +266,65 @@ def run_ours(args):
             dist.all_reduce(flags, op=dist.ReduceOp.MIN)
             if int(flags.item()) == 0:
                 exchange, comm = "nccl", None
+    ys = {}
+
+    def out_buffers(M):
+        if M not in ys:
+            ys[M] = {kn: torch.empty(M, sets[0][kn][0].N, dtype=torch.float16, device=dev) for kn in shapes}
+            if world > 1 and exchange == "nccl":
+                ys[(M, "g")] = {kn: torch.empty(world * M, sets[0][kn][0].N, dtype=torch.float16, device=dev) for kn in shapes}
+        return ys[M]
+
+    wss = {}
+
+    def workspace(M, kn):
+        L, plan = sets[0][kn]
+        need = max(_C_ops.workspace_bytes(M, L.K, L.N, p) for (_, p) in (s[kn] for s in sets))
+        cur = wss.get("ws")
+        if cur is None or cur.numel() < need:
+            wss["ws"] = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
+        return wss["ws"]
+
+    slot = [0]
+
+    def forward(c, kn, M, gather=True):
+        """One forward of layer kn (copy c) at M tokens: the shard's kernel plus, with N > 1, the exchange."""
+        L, plan = sets[c][kn]
+        K, N = kn
+        x = xs[(K, M)]
+        ws = workspace(M, kn)
+        if world > 1 and gather and exchange == "peer":
+            off = slot[0] * region[M]
+            slot[0] ^= 1
+            return _C_ops.forward_gather(L.base_weight, L.base_scales, L.vals, L.col, L.row_ptr, x, 1.0, comm, off, N, L._n0,
+                                         plan=plan, workspace=ws)
+        y = out_buffers(M)[kn]
+        _C_ops.forward(L.base_weight, L.base_scales, L.vals, L.col, L.row_ptr, x, y, 1.0, plan=plan, workspace=ws)
+        if world > 1 and gather:
+            dist.all_gather_into_tensor(ys[(M, "g")][kn], y)
+            return ys[(M, "g")][kn]
+        return y
 
     def run_step(c):
-        for (K, N, M) in items:
-            L, plan = sets[c][(K, N)]
-            if exchange == "peer":
-                _C_ops.forward_gather(L.base_weight, L.base_scales, L.vals, L.col, L.row_ptr, xs[(K, M)], 1.0,
-                                      comm, comm_off[(K, N, M)], N, shard_bounds(N, world)[rank][0], plan=plan)
-                continue
-            _C_ops.forward(L.base_weight, L.base_scales, L.vals, L.col, L.row_ptr, xs[(K, M)], ys[(K, N, M)], 1.0, plan=plan)
-            if world > 1:
-                dist.all_gather_into_tensor(yg[(K, N, M)], ys[(K, N, M)])
+        for kn in shapes:
+            forward(c, kn, 1)
         if exchange == "peer":
             comm.wait()          # deferred mode: every forward waited for its predecessor's exchange; this is the last one's
 
-    # ---- capture one CUDA graph per weight set --------------------------------------------------
-    stream = torch.cuda.Stream(dev)
+    for M in wl.CFG3_M:
+        out_buffers(M)
+        for kn in shapes:
+            workspace(M, kn)
+    if exchange == "peer":
+        comm.set_deferred(not args.no_deferred)
+
+    # ---- headline: one CUDA graph per weight copy, K timed steps -------------------------------------------
     graphs = []
     launches_per_step = 0
     with torch.cuda.stream(stream):
         run_step(0)
         stream.synchronize()
-        for c in range(N_COPIES):
+        for c in range(n_copies):
             g = torch.cuda.CUDAGraph()
             l0 = lib.ortho_b200_launch_count()
             with torch.cuda.graph(g, stream=stream):
@@ -238,15 +337,16 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    warm = max(3, args.warmup)
     with torch.cuda.stream(stream):
-        for i in range(max(3, args.warmup)):
-            graphs[i % N_COPIES].replay()
+        for i in range(warm):
+            graphs[i % n_copies].replay()
         barrier()
         sampler = ClockSampler(local) if rank == 0 else None
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record(stream)
         for i in range(args.steps):
-            graphs[i % N_COPIES].replay()
+            graphs[i % n_copies].replay()
         ev1.record(stream)
         barrier()
         ms = ev0.elapsed_time(ev1)
@@ -256,43 +356,85 @@ def run_ours(args):
     ms = float(tms.item())
     clocks = sampler.stop() if sampler else None
     value = step_bytes * args.steps / (ms * 1e-3) / 1e9
-
-    # ---- end to end through OrthoLinear.forward with host buffers -------------------------------
-    mods = [{kn: sets[c][kn][0].to_module() for kn in sets[c]} for c in range(N_COPIES)]
+    status = torch.tensor([lib.ortho_b200_query_kernel_status()], device=dev)
+    if world > 1:
+        dist.all_reduce(status, op=dist.ReduceOp.MAX)
+    if int(status.item()) != 0:
+        failures.append("a kernel gave up on a bounded wait inside the timed loop")
+    del graphs
     if exchange == "peer":
-        for c in range(N_COPIES):
-            for (K, N) in list(mods[c]):
-                sh = ShardedOrthoLinear(K, N, device=dev)
-                sh.local = mods[c][(K, N)]
-                sh.enable_peer_gather(max(wl.CFG1_M))
-                mods[c][(K, N)] = sh
-    hx = {(K, M): xs[(K, M)].cpu().pin_memory() for (K, N, M) in items}
-    hy = {(K, N, M): torch.empty(M, N, dtype=torch.float16).pin_memory() for (K, N, M) in items}
-    h2d = sum(hx[(K, M)].numel() * 2 for (K, N, M) in items)
-    d2h = sum(hy[k].numel() * 2 for k in hy)
+        comm.set_deferred(False)
+
+    # ---- N > 1: the gathered output of every layer against the unsharded forward ------------------------------
+    gather_checked, gather_max_abs = None, 0.0
+    if world > 1:
+        ok = True
+        for kn in shapes:
+            K, N = kn
+            full = fulls[kn]
+            for M in (1, 32):
+                yg = forward(0, kn, M)
+                if exchange == "nccl":
+                    yg = yg.view(world, M, -1).permute(1, 0, 2).reshape(M, -1)
+                yr = torch.empty(M, N, dtype=torch.float16, device=dev)
+                _C_ops.forward(full.base_weight, full.base_scales, full.vals, full.col, full.row_ptr, xs[(K, M)], yr, 1.0,
+                               workspace=torch.empty(max(256, _C_ops.workspace_bytes(M, K, N)), dtype=torch.uint8, device=dev))
+                torch.cuda.synchronize()
+                d = float((yg.float() - yr.float()).abs().max().item())
+                gather_max_abs = max(gather_max_abs, d)
+                # the shard and the whole layer run the same arithmetic per row; a different K split may change the
+                # FP32 summation order, so: equal up to FP16 rounding
+                if not (d <= 2e-2) or not bool(torch.isfinite(yg).all()):
+                    ok = False
+                    failures.append(f"gathered output of {K}->{N} at M={M} differs from the unsharded forward by {d}")
+                dist.barrier()
+        st2 = torch.tensor([lib.ortho_b200_query_kernel_status(), 0 if ok else 1], device=dev)
+        dist.all_reduce(st2, op=dist.ReduceOp.MAX)
+        gather_checked = bool(int(st2[0].item()) == 0 and int(st2[1].item()) == 0)
+        if int(st2[0].item()) != 0:
+            failures.append("a kernel gave up on a bounded wait during the gather check")
+        fulls.clear()
+        torch.cuda.empty_cache()
+
+    # ---- end to end through the module API with host buffers -----------------------------------------------------
+    mods = []
+    e2e_comm = None
+    if exchange == "peer":
+        e2e_comm = _C_ops.Comm(rank, world, len(shapes) * ShardedOrthoLinear.peer_gather_bytes(1, max_n), device=dev)
+        e2e_comm.connect_group()
+    for c in range(n_copies):
+        d = {}
+        for i, kn in enumerate(shapes):
+            m = sets[c][kn][0].to_module()
+            if world > 1:
+                sh = ShardedOrthoLinear(kn[0], kn[1], device=dev)
+                sh.local = m
+                if exchange == "peer":
+                    sh.enable_peer_gather(1, comm=e2e_comm, offset_bytes=i * ShardedOrthoLinear.peer_gather_bytes(1, max_n))
+                m = sh
+            d[kn] = m
+        mods.append(d)
+    hx = {K: xs[(K, 1)].cpu().pin_memory() for (K, N) in shapes}
+    hy = {kn: torch.empty(1, kn[1], dtype=torch.float16).pin_memory() for kn in shapes}
+    h2d = sum(hx[K].numel() * 2 for (K, N) in shapes)
+    d2h = sum(hy[kn].numel() * 2 for kn in shapes)
 
     def e2e_step(c):
-        for (K, N, M) in items:
-            xd = hx[(K, M)].to(dev, non_blocking=True)
-            y = mods[c][(K, N)](xd)
-            if exchange == "peer":
-                hy[(K, N, M)].copy_(y, non_blocking=True)
-            elif world > 1:
-                dist.all_gather_into_tensor(yg[(K, N, M)], y)
-                hy[(K, N, M)].copy_(yg[(K, N, M)].view(world, M, -1).permute(1, 0, 2).reshape(M, -1), non_blocking=True)
-            else:
-                hy[(K, N, M)].copy_(y, non_blocking=True)
+        for kn in shapes:
+            xd = hx[kn[0]].to(dev, non_blocking=True)
+            y = mods[c][kn](xd)
+            hy[kn].copy_(y, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
-    for i in range(max(3, N_COPIES)):       # touches every weight set once: plans are built on first use
-        e2e_step(i % N_COPIES)
+    for i in range(max(3, n_copies)):       # touches every weight copy once: plans are built on first use
+        e2e_step(i % n_copies)
     barrier()
-    e2e_steps = max(3, min(args.steps, 20))
+    e2e_steps = max(3, min(args.steps, 50))
     l_before = lib.ortho_b200_launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
     for i in range(e2e_steps):
-        e2e_step(i % N_COPIES)
+        e2e_step(i % n_copies)
     ev1.record()
     barrier()
     e2e_launches = lib.ortho_b200_launch_count() - l_before
@@ -300,85 +442,140 @@ def run_ours(args):
     if world > 1:
         dist.all_reduce(tms, op=dist.ReduceOp.MAX)
     e2e_val = step_bytes * e2e_steps / (float(tms.item()) * 1e-3) / 1e9
+    del mods
 
-    # ---- per-(shape, M) detail and the prefill regime (rank 0 / single GPU extras) ---------------
-    detail, prefill = {}, {}
-    if world == 1:
-        for (K, N, M) in items:
-            us = time_forward_us(lambda c: sets[c][(K, N)], xs[(K, M)], ys[(K, N, M)], stream)
-            gbs = sets[0][(K, N)][0].algorithmic_bytes(M) / us / 1e3
-            detail[f"{K}x{N}:M{M}"] = {"us": round(us, 2), "GB/s": round(gbs, 1), "frac_hbm": round(gbs / pk["hbm_gbs"], 3)}
-        if not args.no_prefill:
-            del sets, mods
-            torch.cuda.empty_cache()
-            prefill = bench_prefill(dev, pk)
+    # ---- the same layers in the other regimes (every N) and per-layer detail -----------------------------------------
+    regimes = {}
+    if not args.no_regimes:
+        for kn in shapes:
+            K, N = kn
+            for M in wl.CFG3_M:
+                n = (2 * n_copies) if M <= 32 else 2
+                t_all = timer.us_per_call(lambda i: forward(i % n_copies, kn, M), n, replays=5 if M <= 32 else 3)
+                row = {"us": round(t_all, 2)}
+                fb, ff = sets[0][kn][0]._full_bytes[M], sets[0][kn][0]._full_flops[M]
+                if M <= 32:
+                    row["GB/s"] = round(fb / t_all / 1e3, 1)
+                    row["frac_hbm_per_gpu"] = round(fb / t_all / 1e3 / world / pk["hbm_gbs"], 3)
+                else:
+                    row["TFLOP/s"] = round(ff / t_all / 1e6, 1)
+                    row["frac_of_measured_sustained_per_gpu"] = round(ff / t_all / 1e6 / world / pk["tf_sustained"], 3)
+                if world > 1:
+                    t_loc = timer.us_per_call(lambda i: forward(i % n_copies, kn, M, gather=False), n, replays=5 if M <= 32 else 3)
+                    row["shard_only_us"] = round(t_loc, 2)
+                    row["exchange_us"] = round(t_all - t_loc, 2)
+                regimes[f"{K}x{N}:M{M}"] = row
+        st3 = torch.tensor([lib.ortho_b200_query_kernel_status()], device=dev)
+        if world > 1:
+            dist.all_reduce(st3, op=dist.ReduceOp.MAX)
+        if int(st3.item()) != 0:
+            failures.append("a kernel gave up on a bounded wait in the regime sweep")
+
+    sweep7b, prefill = {}, {}
+    if world == 1 and not args.no_extras:
+        del sets
+        wss.clear(); ys.clear()
+        torch.cuda.empty_cache()
+        sweep7b = bench_decode_sweep_7b(dev, pk, stream)
+        torch.cuda.empty_cache()
+        prefill = bench_prefill(dev, pk)
 
     if rank == 0:
+        per_gpu = value / world
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "warmup": warm, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "parallelism": f"N-sharded x{world} + all-gather" if world > 1 else "single GPU",
-                       "exchange": {"peer": "peer stores issued by the decode kernel (ortho_b200_forward_gather)" +
-                                            ("" if args.no_deferred else "; each forward waits for its predecessor's flags, the step ends with a wait"),
-                                    "nccl": "NCCL all_gather_into_tensor after the kernel", "none": None}[exchange],
-                       "l2": f"rotation over {N_COPIES} distinct weight sets (~100 MB each) > 126 MB L2",
-                       "timing": "CUDA graph replay per step, CUDA events on the launch stream, max over ranks"},
+            "config": {"workload": WORKLOAD},
+            "run": {"parallelism": f"N-sharded x{world} + output gather" if world > 1 else "single GPU",
+                    "exchange": {"peer": "peer stores issued by the kernels (ortho_b200_forward_gather)" +
+                                         ("" if args.no_deferred else "; each forward waits for its predecessor's flags, the step ends with a wait"),
+                                 "nccl": "NCCL all_gather_into_tensor after the kernel", "none": None}[exchange],
+                    "l2": f"rotation over {n_copies} distinct copies of the layers ({per_gpu_set * n_copies >> 20} MB per GPU) > 126 MB L2",
+                    "timing": "CUDA graph replay per step, CUDA events on the launch stream, max over ranks"},
             "clocks": clocks,
             "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "steps": e2e_steps, "api": "OrthoLinear.forward, pinned host X in, Y out, per forward"},
+                    "steps": e2e_steps, "api": ("ShardedOrthoLinear.forward" if world > 1 else "OrthoLinear.forward") +
+                                               ", pinned host X in, Y out, per forward"},
             "gpu_launches": int(launches_per_step * args.steps + e2e_launches),
-            "roofline": {"bound": "hbm", "achieved": value if world == 1 else value / world, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                         "frac": (value if world == 1 else value / world) / pk["hbm_gbs"],
-                         # DRAM bytes per launch: ncu read + write of one captured launch (47.15 MB for the
-                         # 47.98 MB 4096->22016 M=1 launch, profiles/), scaled by algorithmic bytes
-                         "traffic": NCU_TRAFFIC_RATIO * step_bytes / max(1, len(items)) / world,
+            "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                         "frac": per_gpu / pk["hbm_gbs"],
+                         "traffic": NCU_TRAFFIC_RATIO * step_bytes / len(shapes) / world,
+                         "traffic_source": "ncu capture of one launch of this kernel (DRAM bytes / algorithmic bytes = 0.983), scaled by algorithmic bytes",
                          "peak_source": pk["source"], "kernel": "ob::decode_stream_kernel",
                          "launches_per_step": launches_per_step,
-                         "algorithmic_bytes_per_launch": step_bytes / max(1, len(items)) / world},
-            "percent_of_nominal_8TBs": value / world / 8000.0 * 100.0,
+                         "algorithmic_bytes_per_launch": step_bytes / len(shapes) / world},
+            "percent_of_nominal_8TBs": per_gpu / 8000.0 * 100.0,
         }
-        if detail:
-            line["decode_detail"] = detail
+        if world > 1:
+            line["gather_checked"] = gather_checked
+            line["gather_max_abs_diff"] = gather_max_abs
+        if regimes:
+            line["regimes"] = regimes
+        if sweep7b:
+            line["decode_sweep_7b"] = sweep7b
         if prefill:
             line["prefill"] = prefill
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline()
+        if failures:
+            line["failures"] = failures
         print(json.dumps(line))
+    rc = 1 if failures else 0
     if world > 1:
-        # NCCL kernels live inside the captured graphs; tearing the communicator down while those
-        # graphs exist has hung at exit, so: drop the graphs, meet once more, and leave without the
-        # collective teardown
-        del graphs
+        # tearing the NCCL communicator down while CUDA graphs that hold its kernels exist has hung at exit:
+        # meet once more and leave without the collective teardown
         dist.barrier()
         torch.cuda.synchronize()
         sys.stdout.flush()
         sys.stderr.flush()
-        os._exit(0)
+        os._exit(rc)
+    if rc:
+        sys.exit(rc)
 
 
-def time_forward_us(get_layer, x, y, stream, reps=2, replays=5):
-    """Median device time of one forward, from a CUDA graph of reps*N_COPIES back-to-back launches
-    that rotate over the weight copies (so that each launch streams from HBM)."""
+def bench_decode_sweep_7b(dev, pk, stream):
+    """Llama-7B-style decode sweep on one GPU: (4096->12288, 4096->4096, 4096->22016, 11008->4096) x M in {1,4,16},
+    0.5 % ortho, alpha=1; the 12 forwards as one CUDA graph rotating over 6 weight copies (~100 MB each), and
+    per (layer, M) the fused forward beside the base-only one (alpha=0)."""
     import torch
     from libortho_b200 import _C_ops
-    with torch.cuda.stream(stream):
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g, stream=stream):
-            for r in range(reps * N_COPIES):
-                L, plan = get_layer(r % N_COPIES)
-                _C_ops.forward(L.base_weight, L.base_scales, L.vals, L.col, L.row_ptr, x, y, 1.0, plan=plan)
-        g.replay()
-        stream.synchronize()
-        ts = []
-        for _ in range(replays):
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(stream)
-            g.replay()
-            e1.record(stream)
-            e1.synchronize()
-            ts.append(e0.elapsed_time(e1) * 1e3 / (reps * N_COPIES))
-    return statistics.median(ts)
+    import workloads as wl
+    copies = 6
+    sets = []
+    for c in range(copies):
+        d = {}
+        for (K, N) in wl.CFG1_SHAPES:
+            L = wl.make_layer(K, N, wl.CFG1_DENSITY, seed=c, device=dev)
+            d[(K, N)] = (L, _C_ops.Plan(L.row_ptr, L.col, L.vals, K, N))
+        sets.append(d)
+    items = [(K, N, M) for M in wl.CFG1_M for (K, N) in wl.CFG1_SHAPES]
+    xs = {(K, M): wl.make_input(M, K, seed=M, device=dev) for (K, N, M) in items}
+    ys = {(K, N, M): torch.empty(M, N, dtype=torch.float16, device=dev) for (K, N, M) in items}
+    need = max(_C_ops.workspace_bytes(M, K, N, sets[0][(K, N)][1]) for (K, N, M) in items)
+    ws = torch.empty(max(256, need), dtype=torch.uint8, device=dev)
+    timer = _Timer(torch, None, dev, stream, 1)
+
+    def fwd(c, K, N, M, alpha=1.0):
+        L, plan = sets[c][(K, N)]
+        _C_ops.forward(L.base_weight, L.base_scales, L.vals, L.col, L.row_ptr, xs[(K, M)], ys[(K, N, M)], alpha, plan=plan, workspace=ws)
+
+    def step(i):
+        for (K, N, M) in items:
+            fwd(i % copies, K, N, M)
+
+    us_step = timer.us_per_call(step, copies, replays=7)
+    step_bytes = sum(sets[0][(K, N)][0].algorithmic_bytes(M) for (K, N, M) in items)
+    out = {"us_per_step": round(us_step, 2), "GB/s": round(step_bytes / us_step / 1e3, 1),
+           "frac_hbm": round(step_bytes / us_step / 1e3 / pk["hbm_gbs"], 4), "forwards_per_step": len(items), "detail": {}}
+    for (K, N, M) in items:
+        L = sets[0][(K, N)][0]
+        us = timer.us_per_call(lambda i: fwd(i % copies, K, N, M), 2 * copies)
+        us0 = timer.us_per_call(lambda i: fwd(i % copies, K, N, M, 0.0), 2 * copies)
+        gbs = L.algorithmic_bytes(M) / us / 1e3
+        out["detail"][f"{K}x{N}:M{M}"] = {"us": round(us, 2), "GB/s": round(gbs, 1), "frac_hbm": round(gbs / pk["hbm_gbs"], 3),
+                                          "base_only_us": round(us0, 2), "sparse_cost": round(us / us0 - 1.0, 3)}
+    return out
 
 
 def bench_prefill(dev, pk):
@@ -414,28 +611,7 @@ def bench_prefill(dev, pk):
     return out
 
 
-def cpu_baseline():
-    """Reference CPU forward (oracle/_ref, reference flags) on this host: one pass over the sweep."""
-    import oracle
-    import workloads as wl
-    impl, kind = ("reference_fast", "reference") if oracle.available("reference_fast") else ("port", "port")
-    if impl == "port":
-        oracle.build()
-    threads = oracle.host_threads()
-    total_bytes, t_total = 0, 0.0
-    for (K, N) in wl.CFG1_SHAPES:
-        L = wl.make_layer(K, N, wl.CFG1_DENSITY, seed=0)
-        a = (L.base_weight.numpy(), L.base_scales.float().numpy(), L.row_ptr.numpy(), L.col.numpy(), L.vals.float().numpy())
-        for M in wl.CFG1_M:
-            x = wl.make_input(M, K, seed=M).float().numpy()
-            t0 = time.perf_counter()
-            oracle.forward_csr(*a, x, 1.0, impl=impl, threads=threads)
-            t_total += time.perf_counter() - t0
-            total_bytes += L.algorithmic_bytes(M)
-    return {"value": total_bytes / t_total / 1e9, "unit": "GB/s", "cores": threads, "kind": kind,
-            "sample": f"one full pass of the decode sweep (12 forwards), {t_total:.2f} s wall",
-            "ms_per_step": t_total * 1e3}
-
+N_COPIES = 6          # weight copies the single-GPU report rotates through (decode-sized forwards)
 
 def run_report(args):
     """All BASELINE.json configurations on one GPU, as a markdown table (``--report PATH``).  Decode-sized
@@ -644,10 +820,11 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--no-regimes", action="store_true", help="skip the M=32 / M=4096 sweep over the same layers")
+    ap.add_argument("--no-extras", action="store_true", help="skip the 7B-style decode sweep and the prefill configuration (N=1)")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
-                    help="multi-GPU output exchange: peer stores from the decode kernel, or an NCCL all-gather")
+                    help="multi-GPU output exchange: peer stores from the kernels, or an NCCL all-gather")
     ap.add_argument("--no-deferred", action="store_true",
                     help="peer exchange: every forward waits for its own exchange instead of the next one waiting for it")
     ap.add_argument("--report", default=None, metavar="PATH",

@@ -132,6 +132,42 @@ ORTHO_B200_API int ortho_b200_forward(const void *q_weight, const void *q_scales
                        void *workspace, int64_t workspace_bytes, void *stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Forward of several layers that share the activations, with an optional bias per layer.
+ *
+ * Takes the place of (a) one operator call per projection where a model keeps Q / K / V or gate / up as
+ * separate layers -- the reference launches and synchronises once per layer
+ * (src/dual_gemm.cu:317-346,366; call site torch_bind/ortho_linear.py:139-151) -- and (b) the separate
+ * element-wise `output += bias` after the kernel (torch_bind/ortho_linear.py:71-74,164-166): bias_f32
+ * (FP32 [N], may be NULL) is added in the kernels' FP32 epilogue before the single FP16 rounding.
+ * Every layer has its own alpha (the reference's kill switch, per layer).  All layers read x [M, K];
+ * layer l writes y_f16 [M, N] with row pitch ldy (0 = N).  For M <= 16 and K a multiple of 256 the tiles
+ * of all layers are walked by one persistent kernel launch; otherwise the layers run one after the other on
+ * the stream, sharing the workspace (ortho_b200_multi_workspace_bytes = the largest any of them needs).
+ * n_layers <= ORTHO_B200_MULTI_MAX_LAYERS.  n_layers == 1 is the ordinary forward plus the bias.
+ * ------------------------------------------------------------------------------------------- */
+#define ORTHO_B200_MULTI_MAX_LAYERS 4
+typedef struct ortho_b200_layer_desc {
+    const void *q_weight;               /* u8  [N, K/2] */
+    const void *q_scales_f16;           /* f16 [N] */
+    const void *ortho_values_f16;       /* f16 [nnz]   (may be NULL with a plan or when nnz == 0) */
+    const int32_t *ortho_col_indices;   /* i32 [nnz] */
+    const int32_t *ortho_row_ptr;       /* i32 [N+1] */
+    int64_t nnz;
+    const ortho_b200_plan *plan;        /* optional */
+    const float *bias_f32;              /* optional FP32 [N] */
+    void *y_f16;                        /* f16 [M, N], row pitch ldy */
+    int64_t N;
+    int64_t ldy;                        /* elements between token rows of y; 0 = N */
+    float alpha;
+    int32_t reserved;                   /* set to 0 */
+} ortho_b200_layer_desc;
+
+ORTHO_B200_API int64_t ortho_b200_multi_workspace_bytes(const ortho_b200_layer_desc *layers, int n_layers, int64_t M, int64_t K);
+ORTHO_B200_API int ortho_b200_forward_multi(const ortho_b200_layer_desc *layers, int n_layers,
+                       const void *x_f16, int64_t M, int64_t K,
+                       void *workspace, int64_t workspace_bytes, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Forward for callers that cannot allocate device memory.  It has no counterpart in the reference.
  *
  * Who needs it: code that runs where cudaMalloc must not be called -- a host application that owns

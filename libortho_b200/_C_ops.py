@@ -144,6 +144,64 @@ def forward(q_weight: torch.Tensor, q_scales: torch.Tensor, ortho_values: torch.
     _lib.check(st, "ortho_b200_forward")
 
 
+def forward_multi(layers, input: torch.Tensor, outputs, alphas=None, biases=None, plans=None,
+                  workspace: Optional[torch.Tensor] = None) -> None:
+    """Several layers that read the same ``input`` [M, K] (separate Q / K / V or gate / up projections), each
+    with its own alpha and an optional FP32 bias fused into the kernel: ``layers`` is a sequence of
+    ``(q_weight, q_scales, ortho_values, ortho_col_indices, ortho_row_ptr)`` tuples, ``outputs`` the matching
+    FP16 ``[M, N_l]`` tensors written in place.  Up to 16 tokens (K a multiple of 256) run as ONE kernel launch."""
+    n = len(layers)
+    if n == 0:
+        return
+    if n > 4:
+        raise ValueError("at most 4 layers per call")
+    if not input.is_cuda:
+        raise RuntimeError("libortho_b200 has no CPU path: `input` must be a CUDA tensor")
+    if input.dtype != torch.float16 or input.dim() != 2 or not input.is_contiguous():
+        raise TypeError("input must be a contiguous float16 [M, K] tensor")
+    M, K = input.shape
+    dev = input.device
+    descs = (_lib.LayerDesc * n)()
+    keep = []
+    for i, (qw, qs, ov, oc, orp) in enumerate(layers):
+        y = outputs[i]
+        N = y.shape[1]
+        if (qw.dtype != torch.uint8 or qs.dtype != torch.float16 or y.dtype != torch.float16 or not y.is_contiguous()
+                or tuple(qw.shape) != (N, K // 2) or qs.numel() != N or y.shape[0] != M):
+            raise ValueError(f"layer {i}: dtype or shape mismatch")
+        nnz = int(ov.numel()) if ov is not None else 0
+        plan = plans[i] if plans is not None else None
+        if nnz and plan is None and (ov.dtype != torch.float16 or oc.dtype != torch.int32 or orp.dtype != torch.int32
+                                     or orp.numel() != N + 1 or oc.numel() != nnz):
+            raise ValueError(f"layer {i}: CSR arrays have inconsistent dtypes or sizes")
+        b = biases[i] if biases is not None else None
+        if b is not None:
+            if b.dtype != torch.float32 or b.numel() != N or not b.is_contiguous() or b.device != dev:
+                raise ValueError(f"layer {i}: bias must be a contiguous float32 [N] tensor on the input's device")
+            keep.append(b)
+        d = descs[i]
+        d.q_weight, d.q_scales_f16 = qw.data_ptr(), qs.data_ptr()
+        d.ortho_values_f16 = ov.data_ptr() if nnz else None
+        d.ortho_col_indices = oc.data_ptr() if nnz else None
+        d.ortho_row_ptr = orp.data_ptr() if nnz else None
+        d.nnz = nnz
+        d.plan = plan.handle if plan is not None else None
+        d.bias_f32 = b.data_ptr() if b is not None else None
+        d.y_f16, d.N, d.ldy = y.data_ptr(), N, 0
+        d.alpha = float(alphas[i]) if alphas is not None else 1.0
+        d.reserved = 0
+    need = int(_lib.lib().ortho_b200_multi_workspace_bytes(descs, n, M, K))
+    ws_ptr, ws_bytes = None, 0
+    if need > 0:
+        if workspace is None or workspace.numel() * workspace.element_size() < need:
+            workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+        ws_ptr, ws_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
+    with torch.cuda.device(dev):
+        st = _lib.lib().ortho_b200_forward_multi(descs, n, input.data_ptr(), M, K, ws_ptr, ws_bytes,
+                                                 torch.cuda.current_stream(dev).cuda_stream)
+    _lib.check(st, "ortho_b200_forward_multi")
+
+
 COMM_HANDLE_BYTES = 64
 
 

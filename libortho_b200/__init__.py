@@ -7,6 +7,7 @@ first operator call does, and fails loudly if it has not been built.
 """
 from .ortho_linear import OrthoLinear  # noqa: F401
 from . import _C_ops  # noqa: F401
+from .convert import set_alpha_all, swap_linear  # noqa: F401
 
-__all__ = ["OrthoLinear", "_C_ops"]
+__all__ = ["OrthoLinear", "_C_ops", "swap_linear", "set_alpha_all"]
 __version__ = "0.1.0"

@@ -18,6 +18,15 @@ DECODE_MAX_M = 64
 _lib = None
 
 
+class LayerDesc(ctypes.Structure):
+    """``ortho_b200_layer_desc`` of ``include/ortho_b200.h``."""
+    _fields_ = [("q_weight", ctypes.c_void_p), ("q_scales_f16", ctypes.c_void_p),
+                ("ortho_values_f16", ctypes.c_void_p), ("ortho_col_indices", ctypes.c_void_p),
+                ("ortho_row_ptr", ctypes.c_void_p), ("nnz", ctypes.c_int64),
+                ("plan", ctypes.c_void_p), ("bias_f32", ctypes.c_void_p), ("y_f16", ctypes.c_void_p),
+                ("N", ctypes.c_int64), ("ldy", ctypes.c_int64), ("alpha", ctypes.c_float), ("reserved", ctypes.c_int32)]
+
+
 class OrthoB200Error(RuntimeError):
     def __init__(self, status: int, where: str):
         self.status = status
@@ -55,6 +64,10 @@ def _declare(l):
     l.ortho_b200_forward.restype = c.c_int
     l.ortho_b200_forward.argtypes = [vp, vp, vp, i32p, i32p, i64, vp, vp, i64, i64, i64, c.c_float,
                                      vp, vp, i64, vp]
+    l.ortho_b200_forward_multi.restype = c.c_int
+    l.ortho_b200_forward_multi.argtypes = [c.POINTER(LayerDesc), c.c_int, vp, i64, i64, vp, i64, vp]
+    l.ortho_b200_multi_workspace_bytes.restype = i64
+    l.ortho_b200_multi_workspace_bytes.argtypes = [c.POINTER(LayerDesc), c.c_int, i64, i64]
     l.ortho_b200_forward_static_scratch.restype = c.c_int
     l.ortho_b200_forward_static_scratch.argtypes = [vp, vp, vp, i32p, i32p, i64, vp, vp, i64, i64, i64, c.c_float, vp]
     l.ortho_b200_set_decode_config.restype = c.c_int
@@ -106,6 +119,7 @@ EXPORTS = [
     "ortho_b200_comm_set_deferred", "ortho_b200_comm_wait",
     "ortho_b200_pack_base", "ortho_b200_csr_count", "ortho_b200_csr_fill",
     "ortho_b200_sieve_scratch_bytes", "ortho_b200_sieve",
+    "ortho_b200_forward_multi", "ortho_b200_multi_workspace_bytes",
 ]
 
 

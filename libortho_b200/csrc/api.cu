@@ -130,7 +130,26 @@ int forward_impl(const void *q_weight, const void *q_scales_f16,
                  int64_t M, int64_t K, int64_t N, float alpha,
                  const ortho_b200_plan *plan,
                  void *workspace, int64_t workspace_bytes, void *stream,
-                 int64_t ldy, const GatherView *gv, bool *gather_fused)
+                 int64_t ldy, const GatherView *gv, bool *gather_fused, const float *bias_f32)
+{
+    FwdArgs a;
+    const int st = make_fwd_args(a, q_weight, q_scales_f16, ortho_values_f16, ortho_col_indices, ortho_row_ptr, nnz,
+                                 x_f16, y_f16, M, K, N, alpha, plan, workspace, workspace_bytes, stream, ldy, bias_f32);
+    if (st != ORTHO_B200_OK || M == 0) return st;
+    a.gv = gv; a.gather_fused = gather_fused;
+    if (decode_regime(M, N, K)) return launch_decode(a);
+    return launch_prefill(a);
+}
+
+// validates one layer's arguments and fills the launchers' argument record
+int make_fwd_args(FwdArgs &a, const void *q_weight, const void *q_scales_f16,
+                  const void *ortho_values_f16, const int32_t *ortho_col_indices,
+                  const int32_t *ortho_row_ptr, int64_t nnz,
+                  const void *x_f16, void *y_f16,
+                  int64_t M, int64_t K, int64_t N, float alpha,
+                  const ortho_b200_plan *plan,
+                  void *workspace, int64_t workspace_bytes, void *stream,
+                  int64_t ldy, const float *bias_f32)
 {
     if (M == 0) return ORTHO_B200_OK;
     if (!q_weight || !q_scales_f16 || !x_f16 || !y_f16) return ORTHO_B200_ERR_NULL;
@@ -138,7 +157,7 @@ int forward_impl(const void *q_weight, const void *q_scales_f16,
         M > 0x7fffffffLL || N > 0x7fffff00LL || nnz > 0x7fffffffLL)
         return ORTHO_B200_ERR_SHAPE;
     if ((((uintptr_t)q_weight | (uintptr_t)x_f16 | (uintptr_t)y_f16) & 15u) != 0) return ORTHO_B200_ERR_ALIGN;
-    if (((uintptr_t)q_scales_f16 & 1u) != 0) return ORTHO_B200_ERR_ALIGN;
+    if (((uintptr_t)q_scales_f16 & 1u) != 0 || ((uintptr_t)bias_f32 & 3u) != 0) return ORTHO_B200_ERR_ALIGN;
 
     const Plan *pl = reinterpret_cast<const Plan *>(plan);
     if (pl) {
@@ -154,11 +173,11 @@ int forward_impl(const void *q_weight, const void *q_scales_f16,
     int st = check_device();
     if (st != ORTHO_B200_OK) return st;
 
-    FwdArgs a;
     a.w = (const uint8_t *)q_weight;
     a.scales = (const __half *)q_scales_f16;
     a.x = (const __half *)x_f16;
     a.y = (__half *)y_f16;
+    a.bias = bias_f32;
     a.has_ortho = has_ortho ? 1 : 0;
     a.alpha = alpha;
     a.M = M; a.K = K; a.N = N; a.nnz = nnz;
@@ -174,10 +193,8 @@ int forward_impl(const void *q_weight, const void *q_scales_f16,
     a.workspace = workspace; a.workspace_bytes = workspace_bytes;
     a.stream = (cudaStream_t)stream;
     if (ldy != 0 && ldy < N) return ORTHO_B200_ERR_SHAPE;
-    a.ldy = ldy; a.gv = gv; a.gather_fused = gather_fused;
-
-    if (decode_regime(M, N, K)) return launch_decode(a);
-    return launch_prefill(a);
+    a.ldy = ldy; a.gv = nullptr; a.gather_fused = nullptr;
+    return ORTHO_B200_OK;
 }
 }  // namespace ob
 
@@ -191,5 +208,47 @@ extern "C" int ortho_b200_forward(const void *q_weight, const void *q_scales_f16
 {
     return ob::forward_impl(q_weight, q_scales_f16, ortho_values_f16, ortho_col_indices, ortho_row_ptr, nnz,
                             x_f16, y_f16, M, K, N, alpha, plan, workspace, workspace_bytes, stream,
-                            0, nullptr, nullptr);
+                            0, nullptr, nullptr, nullptr);
+}
+
+// Several layers that read the same activations (separate Q / K / V or gate / up projections): in the
+// decode regime their tiles are walked by ONE persistent launch, so that the fixed cost of a launch
+// (a few microseconds on layers that stream for 5-20) is paid once per group instead of once per layer;
+// elsewhere the layers run one after the other on the stream.  The reference reaches the operator with
+// one blocking launch per layer (src/dual_gemm.cu:317-346,366; torch_bind/ortho_linear.py:139-151).
+extern "C" int ortho_b200_forward_multi(const ortho_b200_layer_desc *layers, int n_layers,
+                                        const void *x_f16, int64_t M, int64_t K,
+                                        void *workspace, int64_t workspace_bytes, void *stream)
+{
+    if (n_layers < 0 || (n_layers > 0 && !layers)) return ORTHO_B200_ERR_NULL;
+    if (n_layers == 0 || M == 0) return ORTHO_B200_OK;
+    if (n_layers > ORTHO_B200_MULTI_MAX_LAYERS) return ORTHO_B200_ERR_SHAPE;
+    FwdArgs a[ORTHO_B200_MULTI_MAX_LAYERS];
+    bool all_stream = true;
+    for (int l = 0; l < n_layers; l++) {
+        const ortho_b200_layer_desc &d = layers[l];
+        const int st = make_fwd_args(a[l], d.q_weight, d.q_scales_f16, d.ortho_values_f16, d.ortho_col_indices,
+                                     d.ortho_row_ptr, d.nnz, x_f16, d.y_f16, M, K, d.N, d.alpha, d.plan,
+                                     workspace, workspace_bytes, stream, d.ldy, d.bias_f32);
+        if (st != ORTHO_B200_OK) return st;
+        all_stream = all_stream && decode_regime(M, d.N, K) && stream_kernel_selected(M, K);
+    }
+    if (all_stream && n_layers > 1) return launch_decode_multi(a, n_layers);
+    for (int l = 0; l < n_layers; l++) {
+        const int st = decode_regime(M, a[l].N, K) ? launch_decode(a[l]) : launch_prefill(a[l]);
+        if (st != ORTHO_B200_OK) return st;
+    }
+    return ORTHO_B200_OK;
+}
+
+extern "C" int64_t ortho_b200_multi_workspace_bytes(const ortho_b200_layer_desc *layers, int n_layers, int64_t M, int64_t K)
+{
+    int64_t need = 0;
+    for (int l = 0; l < n_layers; l++) {
+        const ortho_b200_layer_desc &d = layers[l];
+        const int64_t w = d.plan ? ortho_b200_plan_workspace_bytes(d.plan, M) : ortho_b200_workspace_bytes(M, K, d.N);
+        if (w < 0) return -1;
+        need = w > need ? w : need;
+    }
+    return need;
 }

@@ -165,6 +165,7 @@ __device__ __forceinline__ uint4 ldg_stream(const void *p) {
 namespace ob {
 struct FwdArgs {
     const uint8_t *w; const __half *scales; const __half *x; __half *y;
+    const float *bias = nullptr;          // optional FP32 [N]: added in the FP32 epilogue, before the FP16 rounding
     OrthoView ortho; int has_ortho; float alpha;
     int64_t M, K, N, nnz;
     const Plan *plan;
@@ -184,7 +185,13 @@ int forward_impl(const void *q_weight, const void *q_scales_f16, const void *ort
                  const int32_t *ortho_col_indices, const int32_t *ortho_row_ptr, int64_t nnz,
                  const void *x_f16, void *y_f16, int64_t M, int64_t K, int64_t N, float alpha,
                  const ortho_b200_plan *plan, void *workspace, int64_t workspace_bytes, void *stream,
-                 int64_t ldy, const struct GatherView *gv, bool *gather_fused);
+                 int64_t ldy, const struct GatherView *gv, bool *gather_fused, const float *bias_f32 = nullptr);
+int make_fwd_args(FwdArgs &a, const void *q_weight, const void *q_scales_f16, const void *ortho_values_f16,
+                  const int32_t *ortho_col_indices, const int32_t *ortho_row_ptr, int64_t nnz,
+                  const void *x_f16, void *y_f16, int64_t M, int64_t K, int64_t N, float alpha,
+                  const ortho_b200_plan *plan, void *workspace, int64_t workspace_bytes, void *stream,
+                  int64_t ldy, const float *bias_f32);
+int launch_decode_multi(const FwdArgs *layers, int nl);   // decode.cu: one streaming launch for layers that share x
 int launch_prefill(const FwdArgs &a);
 int64_t prefill_workspace_bytes(int64_t M, int64_t K, int64_t N);
 int64_t min_workspace_bytes(int64_t M, int64_t K, int64_t N);

@@ -29,6 +29,7 @@ namespace ob {
 
 struct DecodeParams {
     const uint8_t *w; const __half *scales; const __half *x; __half *y;
+    const float *bias;   // optional FP32 [N]
     OrthoView ov; int has_ortho; float alpha;
     int M, K, N;
     long long ldy;    // elements between token rows of y
@@ -248,6 +249,7 @@ decode_kernel(const DecodeParams p)
                 }
                 float v = __half2float(p.scales[n]) * s;
                 if (p.has_ortho) v = fmaf(p.alpha, osm[i * TOK + m], v);
+                if (p.bias) v += p.bias[n];
                 p.y[(size_t)m * (size_t)p.ldy + n] = __float2half_rn(v);
             }
         }
@@ -288,6 +290,7 @@ static bool decode_regime_of(const Tuning &t, int64_t M, int64_t N, int64_t K)
 bool decode_regime(int64_t M, int64_t N, int64_t K) { return decode_regime_of(tuning_snapshot(), M, N, K); }
 
 int launch_decode_stream(const FwdArgs &a, int S, int stages);          // decode_stream.cu
+int launch_decode_stream_multi(const FwdArgs *layers, int nl, int S, int stages);
 
 int set_decode_config(int wr, int wk, int u, int s)
 {
@@ -339,7 +342,7 @@ template <int MT, int WR, int WK, int U>
 static int launch_cfg(const FwdArgs &a, int S)
 {
     DecodeParams p;
-    p.w = a.w; p.scales = a.scales; p.x = a.x; p.y = a.y;
+    p.w = a.w; p.scales = a.scales; p.x = a.x; p.y = a.y; p.bias = a.bias;
     p.ov = a.ortho; p.has_ortho = a.has_ortho; p.alpha = a.alpha;
     p.M = (int)a.M; p.K = (int)a.K; p.N = (int)a.N; p.ldy = a.pitch_y();
     p.T = (int)ceil_div(a.K, 128);
@@ -402,6 +405,12 @@ bool stream_kernel_selected(int64_t M, int64_t K)
 {
     const Tuning t = tuning_snapshot();
     return M <= t.prefill_above && stream_selected(t, M, K);
+}
+
+int launch_decode_multi(const FwdArgs *layers, int nl)
+{
+    const Tuning t = tuning_snapshot();
+    return launch_decode_stream_multi(layers, nl, t.stream_s, t.stream_stages);
 }
 
 int launch_decode(const FwdArgs &a)

@@ -21,6 +21,7 @@
 // the sparse stream is not touched at all, so the output equals the base-only output exactly.
 #include <atomic>
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 #include "common.cuh"
@@ -33,12 +34,25 @@ namespace ob {
 // parameter: 2 for M <= 8, 1 for M = 9..16 where the activation slab limits the K range per CTA).
 constexpr int kWarps = 8;
 
-struct StreamParams {
-    const __half *scales; const __half *x; __half *y;
+// One launch may walk the tiles of several layers that share the activations (same X, same K): the tile
+// sequence is the concatenation of the layers' 16-row tiles, layer l owning tiles [tile0, next tile0).
+constexpr int kMaxLayers = 4;
+struct StreamLayer {
+    const __half *scales; __half *y; const float *bias;   // bias: optional FP32 [N], added before the FP16 rounding
     OrthoView ov; int has_ortho; float alpha;
-    int M, K, N;
+    int N;         // output rows of this layer
+    int ldy;       // elements between token rows of y
+    int tile0;     // first tile of this layer in the launch's tile sequence
+};
+struct StreamMaps { CUtensorMap m[kMaxLayers]; };
+struct StreamParams {
+    StreamLayer L[kMaxLayers];
+    int nl;        // layers in this launch
+    int any_ortho; // some layer has an active sparse term
+    const __half *x;
+    int M, K;
     int nboxes;    // ceil(K / weights per box row)
-    int ntiles;    // ceil(N / 16)
+    int ntiles;    // 16-row tiles of all layers together
     int pitch;     // bytes between token rows of the staged activation slab
     int stages;    // ring depth per warp
     int red_bufs;  // 2: partial sums double-buffered; 1 (S == 1 only): one buffer and a group barrier per tile
@@ -95,9 +109,22 @@ __device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.
 // NG = warp groups per CTA.  A group is the 8-warp unit described above, with its own rings, tile barrier
 // and reduction buffers; the groups of a CTA work on different tiles and share one activation slab, which
 // is what limits residency for 8 and 16 tokens (NG = 2: one CTA of 16 warps per SM instead of one of 8).
-template <int MV, int KBX, bool GATHER, int NG>
+// NL = 1: one layer (every per-layer lookup is resolved at compile time); NL = kMaxLayers: up to that many.
+template <int NL>
+__device__ __forceinline__ int layer_of(const StreamParams &p, int tile)
+{
+    int l = 0;
+    if constexpr (NL > 1) {
+#pragma unroll
+        for (int i = 1; i < NL; i++)
+            if (i < p.nl && tile >= p.L[i].tile0) l = i;
+    }
+    return l;
+}
+
+template <int MV, int KBX, bool GATHER, int NG, int NL>
 __global__ void __launch_bounds__(NG * kWarps * 32, NG == 2 ? 1 : 2)
-decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParams p,
+decode_stream_kernel(const __grid_constant__ StreamMaps maps, const StreamParams p,
                      const typename StreamGatherArg<GATHER>::type gp)
 {
     constexpr int kKbx = KBX;
@@ -115,7 +142,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
     const int S = (int)cluster_nctarank();
     const int rank = (int)cluster_ctarank();
     const int cid = blockIdx.y * NG + grp, G = gridDim.y * NG;
-    const int K = p.K, N = p.N, M = p.M;
+    const int K = p.K, M = p.M;
 
     // ---- shared memory carve-up ----------------------------------------------------------------
     // the 128-byte TMA swizzle is a function of the shared-memory address: ring slots sit on 1 KB
@@ -148,7 +175,8 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
     int i_ti = 0, i_bi = 0, i_st = 0, i_left = total;
     auto issue = [&]() {   // lane 0 only
         mbar_arrive_expect_tx(&my_bars[i_st], kBoxBytes);
-        tma_load_3d(my_ring + (size_t)i_st * kBoxBytes, &wmap, &my_bars[i_st], 0, (wb0 + i_bi) * kKbx, (cid + i_ti * G) * 16);
+        const int T = cid + i_ti * G, l = layer_of<NL>(p, T);
+        tma_load_3d(my_ring + (size_t)i_st * kBoxBytes, &maps.m[l], &my_bars[i_st], 0, (wb0 + i_bi) * kKbx, (T - p.L[l].tile0) * 16);
         if (++i_bi == nbw) { i_bi = 0; ++i_ti; }
         if (++i_st == p.stages) i_st = 0;
         --i_left;
@@ -157,7 +185,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
     // weights and the sparse structure are constants of the layer: they are prefetched before the
     // grid dependency is resolved; activations are only touched after griddep_wait()
     if (lane == 0) {
-        prefetch_tensormap(&wmap);
+        for (int l = 0; l < (NL == 1 ? 1 : p.nl); l++) prefetch_tensormap(&maps.m[l]);
         for (int s = 0; s < p.stages; s++) mbar_init(&my_bars[s], 1);
         if (warp == 0) mbar_init(tbar, kWarps * 32);
         fence_mbar_init();
@@ -170,32 +198,36 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
     int rp_cur[2][2] = {{0, 0}, {0, 0}}, rp_nxt[2][2] = {{0, 0}, {0, 0}};
     uint32_t ent[2][2] = {{0, 0}, {0, 0}};
     auto load_rp = [&](int ti, int (&rp)[2][2]) {
+        const int T = cid + ti * G;
+        const StreamLayer &Ly = p.L[layer_of<NL>(p, T)];
 #pragma unroll
         for (int r = 0; r < 2; r++) {
-            const int n = (cid + ti * G) * 16 + warp + 8 * r;
+            const int n = (T - Ly.tile0) * 16 + warp + 8 * r;
             rp[r][0] = rp[r][1] = 0;
-            if (ti < nt && n < N) { rp[r][0] = p.ov.row_ptr[n]; rp[r][1] = p.ov.row_ptr[n + 1]; }
+            if (ti < nt && Ly.has_ortho && n < Ly.N) { rp[r][0] = Ly.ov.row_ptr[n]; rp[r][1] = Ly.ov.row_ptr[n + 1]; }
         }
     };
-    auto load_entry = [&](int e) -> uint32_t {
-        if (p.ov.entries) return p.ov.entries[e];
-        const int c = p.ov.col[e];
-        const unsigned short vb = __half_as_ushort(p.ov.val[e]);
+    auto load_entry = [&](const OrthoView &ov, int e) -> uint32_t {
+        if (ov.entries) return ov.entries[e];
+        const int c = ov.col[e];
+        const unsigned short vb = __half_as_ushort(ov.val[e]);
         return ((unsigned)c >= (unsigned)K) ? 0u : (((uint32_t)vb << 16) | (uint32_t)c);
     };
-    auto load_ent = [&](const int (&rp)[2][2], uint32_t (&en)[2][2]) {
+    // entries of local tile ti (whose row pointers are rp); rows without entries load nothing
+    auto load_ent = [&](int ti, const int (&rp)[2][2], uint32_t (&en)[2][2]) {
+        const OrthoView &ov = p.L[layer_of<NL>(p, cid + ti * G)].ov;
 #pragma unroll
         for (int r = 0; r < 2; r++)
 #pragma unroll
             for (int q = 0; q < 2; q++) {
                 const int e = rp[r][0] + q * 32 + lane;
-                en[r][q] = (e < rp[r][1]) ? load_entry(e) : 0u;
+                en[r][q] = (e < rp[r][1]) ? load_entry(ov, e) : 0u;
             }
     };
-    if (p.has_ortho) {
+    if (p.any_ortho) {
         load_rp(0, rp_cur);
         load_rp(1, rp_nxt);
-        load_ent(rp_cur, ent);
+        load_ent(0, rp_cur, ent);
     }
 
     griddep_wait();
@@ -260,14 +292,16 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
 
     // the row scale a finalizing thread needs is fetched one tile early, so that the finalize of
     // tile i (executed while tile i+1 is in flight) never waits on global memory
-    float sc_prev = 0.f;
+    float sc_prev = 0.f, bias_prev = 0.f;
     const int rmask = p.red_bufs - 1;          // 1: alternate the partial-sum buffers, 0: single buffer
     auto finalize = [&](int ti) {
         const int buf = ti & 1, rbuf = ti & rmask;
         if (fin_on) {
             const int m = fin_m, i = fin_i;
-            const int n = (cid + ti * G) * 16 + i;
-            if (n < N) {
+            const int T = cid + ti * G;
+            const StreamLayer &Ly = p.L[layer_of<NL>(p, T)];
+            const int n = (T - Ly.tile0) * 16 + i;
+            if (n < Ly.N) {
                 const uint32_t red_base = smem_u32(red + (size_t)rbuf * kWarps * 16 * MV);
                 const uint32_t osm_base = smem_u32(osm + (size_t)buf * 16 * MV);
                 float s = 0.f, o = 0.f;
@@ -275,19 +309,20 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
                     const float *rb = red + (size_t)rbuf * kWarps * 16 * MV + i * MV + m;
 #pragma unroll
                     for (int w = 0; w < kWarps; w++) s += rb[w * 16 * MV];
-                    if (p.has_ortho) o = osm[(size_t)buf * 16 * MV + i * MV + m];
+                    if (Ly.has_ortho) o = osm[(size_t)buf * 16 * MV + i * MV + m];
                 } else {
                     for (int r2 = 0; r2 < S; r2++) {
                         const uint32_t rb = mapa_shared(red_base, (uint32_t)r2);
 #pragma unroll
                         for (int w = 0; w < kWarps; w++) s += ld_dsmem_f32(rb + (uint32_t)((w * 16 * MV + i * MV + m) * 4));
-                        if (p.has_ortho) o += ld_dsmem_f32(mapa_shared(osm_base, (uint32_t)r2) + (uint32_t)((i * MV + m) * 4));
+                        if (Ly.has_ortho) o += ld_dsmem_f32(mapa_shared(osm_base, (uint32_t)r2) + (uint32_t)((i * MV + m) * 4));
                     }
                 }
                 float v = sc_prev * s;
-                if (p.has_ortho) v = fmaf(p.alpha, o, v);
+                if (Ly.has_ortho) v = fmaf(Ly.alpha, o, v);
+                v += bias_prev;                                  // 0 when the layer has no bias
                 if constexpr (!GATHER) {
-                    p.y[(size_t)m * N + n] = __float2half_rn(v);
+                    Ly.y[(size_t)m * Ly.ldy + n] = __float2half_rn(v);
                 } else {
                     const __half hv = __float2half_rn(v);
                     const size_t at = (size_t)m * gp.ldy + n;
@@ -298,10 +333,15 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
     };
 
     for (int ti = 0; ti < nt_loop; ti++) {
-        float sc_new = 0.f;
+        float sc_new = 0.f, bias_new = 0.f;
+        const int l_cur = layer_of<NL>(p, cid + ti * G);
         if (fin_on) {
-            const int n = (cid + ti * G) * 16 + fin_i;
-            if (n < N) sc_new = __half2float(p.scales[n]);
+            const StreamLayer &Ly = p.L[l_cur];
+            const int n = (cid + ti * G - Ly.tile0) * 16 + fin_i;
+            if (ti < nt && n < Ly.N) {
+                sc_new = __half2float(Ly.scales[n]);
+                if (Ly.bias) bias_new = Ly.bias[n];
+            }
         }
 #pragma unroll
         for (int c = 0; c < NCH; c++)
@@ -311,9 +351,9 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
         // sparse stream, pipeline stages A/B: row pointers two tiles ahead, entries one tile ahead
         int rp_fut[2][2] = {{0, 0}, {0, 0}};
         uint32_t ent_nxt[2][2] = {{0, 0}, {0, 0}};
-        if (p.has_ortho) {
+        if (p.any_ortho) {
             load_rp(ti + 2, rp_fut);
-            load_ent(rp_nxt, ent_nxt);
+            load_ent(ti + 1, rp_nxt, ent_nxt);
         }
 
         // ---- base: consume this warp's boxes of the tile ---------------------------------------
@@ -353,7 +393,8 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
 
         // ---- sparse stream, stage C: this tile's rows from the prefetched entries ---------------
         float osum[2] = {0.f, 0.f};
-        if (p.has_ortho) {
+        if (p.any_ortho) {
+            const OrthoView &ov_cur = p.L[l_cur].ov;
 #pragma unroll
             for (int r = 0; r < 2; r++) {
                 float a[MV];
@@ -377,7 +418,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
                 };
                 if (e0 + lane < e1) apply(ent[r][0]);
                 if (e0 + 32 + lane < e1) apply(ent[r][1]);
-                for (int e = e0 + 64 + lane; e < e1; e += 32) apply(load_entry(e));
+                for (int e = e0 + 64 + lane; e < e1; e += 32) apply(load_entry(ov_cur, e));
                 osum[r] = butterfly_reduce<MV>(a, lane);
             }
         }
@@ -402,7 +443,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
                     }
                 }
             }
-            if (p.has_ortho && (lane & (LPG - 1)) == 0) {
+            if (p.any_ortho && (lane & (LPG - 1)) == 0) {
                 float *o = osm + (size_t)(ti & 1) * 16 * MV;
                 o[warp * MV + lane / LPG] = osum[0];
                 o[(warp + 8) * MV + lane / LPG] = osum[1];
@@ -410,8 +451,9 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParam
         }
         tile_arrive();
         sc_prev = sc_new;
+        bias_prev = bias_new;
 
-        if (p.has_ortho) {
+        if (p.any_ortho) {
 #pragma unroll
             for (int r = 0; r < 2; r++) {
                 rp_cur[r][0] = rp_nxt[r][0]; rp_cur[r][1] = rp_nxt[r][1];
@@ -442,15 +484,28 @@ static size_t stream_smem_bytes(int MV, int kbx, int64_t M, int boxes_per_cta, i
     return 1024 + (size_t)ng * region + (size_t)M * (boxes_per_cta * 512 * kbx + 64);
 }
 
-template <int MV, int KBX, bool GATHER, int NG = 1>
-static int launch_stream_mv(const FwdArgs &a, const CUtensorMap &map, int S, int stages, int red_bufs)
+// layers[0..nl): layers that share x, M, K and the stream (nl == 1 for the ordinary forward)
+template <int MV, int KBX, bool GATHER, int NG, int NL>
+static int launch_stream_mv(const FwdArgs *layers, int nl, const StreamMaps &maps, int S, int stages, int red_bufs)
 {
     constexpr int kBoxK = 256 * KBX;
+    const FwdArgs &a = layers[0];
     StreamParams p;
-    p.scales = a.scales; p.x = a.x; p.y = a.y; p.ov = a.ortho; p.has_ortho = a.has_ortho; p.alpha = a.alpha;
-    p.M = (int)a.M; p.K = (int)a.K; p.N = (int)a.N;
+    memset(&p, 0, sizeof(p));
+    p.nl = nl;
+    int tiles = 0;
+    for (int l = 0; l < nl; l++) {
+        const FwdArgs &f = layers[l];
+        StreamLayer &Ly = p.L[l];
+        Ly.scales = f.scales; Ly.y = f.y; Ly.bias = f.bias; Ly.ov = f.ortho; Ly.has_ortho = f.has_ortho; Ly.alpha = f.alpha;
+        Ly.N = (int)f.N; Ly.ldy = (int)f.pitch_y(); Ly.tile0 = tiles;
+        tiles += (int)ceil_div(f.N, 16);
+        p.any_ortho |= f.has_ortho;
+    }
+    p.x = a.x;
+    p.M = (int)a.M; p.K = (int)a.K;
     p.nboxes = (int)ceil_div(a.K, kBoxK);
-    p.ntiles = (int)ceil_div(a.N, 16);
+    p.ntiles = tiles;
     const int boxes_per_cta = (int)ceil_div(p.nboxes, S);
     p.pitch = boxes_per_cta * kBoxK * 2 + 64;
     p.stages = stages;
@@ -471,7 +526,7 @@ static int launch_stream_mv(const FwdArgs &a, const CUtensorMap &map, int S, int
     }
     const size_t smem = stream_smem_bytes(MV, KBX, a.M, boxes_per_cta, stages, NG, red_bufs);
     if (smem > 227 * 1024) return ORTHO_B200_ERR_SHAPE;
-    auto kern = decode_stream_kernel<MV, KBX, GATHER, NG>;
+    auto kern = decode_stream_kernel<MV, KBX, GATHER, NG, NL>;
     static bool attr_set[kMaxDevices] = {};       // the attribute is per device
     const int dev = current_device_index();
     if (dev < 0) return ORTHO_B200_ERR_CUDA;
@@ -519,14 +574,17 @@ static int launch_stream_mv(const FwdArgs &a, const CUtensorMap &map, int S, int
     const int units = (int)ceil_div(p.ntiles, NG);       // a CTA takes NG tiles per round
     int Gc = mc < units ? mc : units;
     cfg.gridDim = dim3((unsigned)S, (unsigned)Gc, 1);
-    OB_CUDA(cudaLaunchKernelEx(&cfg, kern, map, p, gp));
+    OB_CUDA(cudaLaunchKernelEx(&cfg, kern, maps, p, gp));
     count_launch();
     return ORTHO_B200_OK;
 }
 
-int launch_decode_stream(const FwdArgs &a, int cfg_s, int cfg_stages)
+// One launch for nl layers that share x, M, K (M <= 16, K a multiple of 256, nl <= kMaxLayers).  More than one
+// layer: plain outputs only (no peer gather).
+int launch_decode_stream_multi(const FwdArgs *layers, int nl, int cfg_s, int cfg_stages)
 {
-    if (a.M > 16) return ORTHO_B200_ERR_SHAPE;
+    const FwdArgs &a = layers[0];
+    if (a.M > 16 || nl < 1 || nl > kMaxLayers) return ORTHO_B200_ERR_SHAPE;
     const int MV = a.M <= 1 ? 1 : a.M <= 2 ? 2 : a.M <= 4 ? 4 : a.M <= 8 ? 8 : 16;
     const int kbx = (MV <= 8) ? 2 : 1;
     const int nboxes = (int)ceil_div(a.K, 256 * kbx);
@@ -554,15 +612,19 @@ int launch_decode_stream(const FwdArgs &a, int cfg_s, int cfg_stages)
     }
     while (stages > 2 && stream_smem_bytes(MV, kbx, a.M, bpc, stages, ng, red_bufs) > 227 * 1024) stages--;
 
-    // [N][K/2 / 128][128 B] view of the packed base; blocks past the end of a row read as zero
-    CUtensorMap map;
-    if (!make_tensor_map_rows_of_128B(&map, a.w, (uint64_t)a.N, (uint64_t)(a.K / 2), 16, (uint32_t)kbx))
-        return ORTHO_B200_ERR_CUDA;
-    // the GATHER instantiation also serves any output whose pitch is not N
-    const bool gather = a.gv || a.pitch_y() != a.N;
+    // per layer a [N][K/2 / 128][128 B] view of the packed base; blocks past the end of a row read as zero
+    StreamMaps maps;
+    memset(&maps, 0, sizeof(maps));
+    for (int l = 0; l < nl; l++)
+        if (!make_tensor_map_rows_of_128B(&maps.m[l], layers[l].w, (uint64_t)layers[l].N, (uint64_t)(a.K / 2), 16, (uint32_t)kbx))
+            return ORTHO_B200_ERR_CUDA;
+    // the GATHER instantiation serves the peer gather and, for one layer, any output whose pitch is not N
+    const bool gather = nl == 1 && (a.gv || a.pitch_y() != a.N);
+    if (nl > 1 && a.gv) return ORTHO_B200_ERR_SHAPE;
 #define OB_STREAM(MV_, KBX_, NG_) \
-    (gather ? launch_stream_mv<MV_, KBX_, true, NG_>(a, map, S, stages, red_bufs) \
-            : launch_stream_mv<MV_, KBX_, false, NG_>(a, map, S, stages, red_bufs))
+    (nl > 1 ? launch_stream_mv<MV_, KBX_, false, NG_, kMaxLayers>(layers, nl, maps, S, stages, red_bufs) \
+     : gather ? launch_stream_mv<MV_, KBX_, true, NG_, 1>(layers, nl, maps, S, stages, red_bufs) \
+              : launch_stream_mv<MV_, KBX_, false, NG_, 1>(layers, nl, maps, S, stages, red_bufs))
     switch (MV) {
         case 1: return ng == 2 ? OB_STREAM(1, 2, 2) : OB_STREAM(1, 2, 1);
         case 2: return ng == 2 ? OB_STREAM(2, 2, 2) : OB_STREAM(2, 2, 1);
@@ -571,6 +633,11 @@ int launch_decode_stream(const FwdArgs &a, int cfg_s, int cfg_stages)
         default: return ng == 2 ? OB_STREAM(16, 1, 2) : OB_STREAM(16, 1, 1);
     }
 #undef OB_STREAM
+}
+
+int launch_decode_stream(const FwdArgs &a, int cfg_s, int cfg_stages)
+{
+    return launch_decode_stream_multi(&a, 1, cfg_s, cfg_stages);
 }
 
 }  // namespace ob

@@ -1,0 +1,488 @@
+// Forward for a few tokens up to 128 on the 5th-generation tensor cores, with the operand roles of prefill.cu
+// exchanged: the TOKENS are the M operand of the MMA (128 TMEM lanes, zero rows beyond the real token
+// count) and the WEIGHT rows are its N operand (256 per instruction).
+//
+// Why: on this part one tcgen05.mma (kind::f16, K = 16) occupies the tensor pipe for about 185 cycles whatever
+// its M and N are, so the weight bytes a kernel can push through the pipe depend only on how many weight rows
+// one instruction covers: 128 as the M operand (prefill.cu: ~1.6 TB/s of packed INT4 per GPU), 256 as the N
+// operand (here: ~3.2 TB/s), against ~2.3 / 1.2 TB/s for legacy mma.sync at 32 / 64 tokens.  Replaces, for
+// this token range, the reference's one-thread-per-output kernel (src/dual_gemm.cu:176-225) and its WMMA
+// variant (src/dual_gemm_tensor_core.cu:215-337).
+//
+//     D[m, n] = sum_k x[m, k] * w_int[n, k]        (tcgen05.mma, A and B from shared memory, FP32 in TMEM)
+//     y[m, n] = scale[n] * D[m, n] + alpha * O[m, n] + bias[n]
+//
+// The packed INT4 bytes come in by TMA (256 rows x 128 B = 256 k per load, 128-byte swizzle); eight converter
+// warps (one thread per weight row) unpack them to exact small-integer FP16 and write the K-major, 128-byte
+// swizzled B tile (256 rows x 64 k) straight into shared memory; the token tile (128 x 64 k) is a plain TMA load.
+// Two 256-column accumulators alternate, so the epilogue of one unit runs under the MMAs of the next.
+// Epilogue thread = token (TMEM lane), columns = weight rows: every thread stores runs of 32 consecutive
+// outputs of its own token row, no transposition.
+//
+// Work split (stream-K): the sequence of all (row tile, k block) pairs is cut into one contiguous share per
+// CTA, so every SM does the same number of MMAs however few row tiles the layer has.  A CTA whose share starts
+// inside a row tile leaves that tile's partial FP32 sums in its slot of the workspace and raises a flag; the CTA
+// that holds the tile's first k block adds the partials of the CTAs behind it, in CTA order (fixed order:
+// reproducible), in its epilogue.  A share's only partial piece is processed first and the piece that collects
+// partials last, so the bounded flag wait does not normally wait at all.
+//
+// The sparse term is computed ahead into O[m][n] (token-major FP32, in the workspace) by ortho_tokens_kernel
+// from the once-transposed activations, one warp per 8 weight rows, and added in the FP32 epilogue.
+#include <cstring>
+
+#include "common.cuh"
+#include "gather.cuh"
+#include "umma.cuh"
+
+namespace ob {
+
+int *kernel_status_word();
+int launch_transpose_x(const __half *x, __half *xt, int M, int K, int Mp, cudaStream_t stream);   // spmm.cu
+
+namespace md {
+constexpr int TN = 256;                 // weight rows per tile (MMA N)
+constexpr int TMK = 128;                // token lanes (MMA M)
+constexpr int KB = 64;                  // k per pipeline stage
+constexpr int WKB = 4;                  // k blocks covered by one packed-weight load
+constexpr int W_BYTES = TN * 128;       // 32 KB
+constexpr int X_BYTES = TMK * KB * 2;   // 16 KB
+constexpr int B_BYTES = TN * KB * 2;    // 32 KB
+constexpr int WST = 2, XST = 3, BST = 3;
+constexpr int CONV_WARPS = 8;
+constexpr int EPI_WARP0 = 2 + CONV_WARPS;
+constexpr int EPI_WARPS = 4;
+constexpr int NWARPS = EPI_WARP0 + EPI_WARPS;
+constexpr int TMEM_COLS = 512;
+
+struct Params {
+    const __half *scales; const float *bias; __half *y;
+    int M, K, N;
+    long long ldy;
+    int tiles_n, kblocks;
+    long long total;            // tiles_n * kblocks
+    int mrows;                  // token rows kept per partial slot (M rounded up to 32)
+    float *slots; int *flags;   // slots[cta][mrows][256], flags[cta]
+    const float *o; float alpha; int has_ortho;    // O[m][n], row pitch N
+    int *status;
+    int gather;
+    GatherView gv;
+};
+
+struct Smem {
+    uint64_t w_full[WST], w_empty[WST];
+    uint64_t x_full[XST], x_empty[XST];
+    uint64_t b_full[BST], b_empty[BST];
+    uint64_t d_full[2], d_empty[2];
+    uint32_t tmem_base;
+    float sc[TN], bs[TN];
+};
+constexpr size_t kSmemBytes = 1024 + (size_t)WST * W_BYTES + (size_t)XST * X_BYTES + (size_t)BST * B_BYTES + sizeof(Smem) + 256;
+
+struct Seg { int t, kb0, kb1; };
+}  // namespace md
+
+__global__ void __launch_bounds__(md::NWARPS * 32, 1)
+mid_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, const md::Params p)
+{
+    using namespace md;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char *base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    unsigned char *ws = base;
+    unsigned char *xs = ws + (size_t)WST * W_BYTES;
+    unsigned char *bsm = xs + (size_t)XST * X_BYTES;
+    Smem *sm = reinterpret_cast<Smem *>(bsm + (size_t)BST * B_BYTES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int cta = blockIdx.x, G = gridDim.x;
+    const long long r_begin = p.total * cta / G, r_end = p.total * (cta + 1) / G;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < WST; s++) { mbar_init(&sm->w_full[s], 1); mbar_init(&sm->w_empty[s], CONV_WARPS); }
+        for (int s = 0; s < XST; s++) { mbar_init(&sm->x_full[s], 1); mbar_init(&sm->x_empty[s], 1); }
+        for (int s = 0; s < BST; s++) { mbar_init(&sm->b_full[s], CONV_WARPS); mbar_init(&sm->b_empty[s], 1); }
+        for (int s = 0; s < 2; s++) { mbar_init(&sm->d_full[s], 1); mbar_init(&sm->d_empty[s], EPI_WARPS); }
+        fence_mbar_init();
+        prefetch_tensormap(&xmap);
+        prefetch_tensormap(&wmap);
+    }
+    if (warp == 1) { tmem_alloc(&sm->tmem_base, TMEM_COLS); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sm->tmem_base;
+    bool dead = false;
+    auto wait = [&](uint64_t *bar, uint32_t parity) {
+        if (dead) return;
+        if (!mbar_wait(bar, parity, 1u << 24)) { dead = true; atomicExch(p.status, 1); }
+    };
+    // the pieces of this CTA's share, in order: (row tile, k blocks [kb0, kb1))
+    auto next_seg = [&](long long &pos, Seg &sg) -> bool {
+        if (pos >= r_end) return false;
+        sg.t = (int)(pos / p.kblocks);
+        sg.kb0 = (int)(pos - (long long)sg.t * p.kblocks);
+        const long long left = r_end - pos;
+        sg.kb1 = (int)((long long)(p.kblocks - sg.kb0) < left ? p.kblocks : sg.kb0 + left);
+        pos += sg.kb1 - sg.kb0;
+        return true;
+    };
+
+    if (warp == 0) {
+        // ================= TMA producer =================
+        if (lane == 0) {
+            int xi = 0, wi = 0; uint32_t xph = 0, wph = 0;
+            long long pos = r_begin; Seg sg;
+            while (next_seg(pos, sg)) {
+                for (int kb = sg.kb0; kb < sg.kb1; kb++) {
+                    if ((kb % WKB) == 0 || kb == sg.kb0) {
+                        wait(&sm->w_empty[wi], wph ^ 1u);
+                        mbar_arrive_expect_tx(&sm->w_full[wi], W_BYTES);
+                        tma_load_2d(ws + (size_t)wi * W_BYTES, &wmap, &sm->w_full[wi], (kb / WKB) * 128, sg.t * TN);
+                        if (++wi == WST) { wi = 0; wph ^= 1u; }
+                    }
+                    wait(&sm->x_empty[xi], xph ^ 1u);
+                    mbar_arrive_expect_tx(&sm->x_full[xi], X_BYTES);
+                    tma_load_2d(xs + (size_t)xi * X_BYTES, &xmap, &sm->x_full[xi], kb * KB, 0);
+                    if (++xi == XST) { xi = 0; xph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ================= MMA issuer =================
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc_f16(TMK, TN);
+            const uint64_t adesc0 = umma_desc_sw128(smem_u32(xs));
+            const uint64_t bdesc0 = umma_desc_sw128(smem_u32(bsm));
+            int xi = 0, bi = 0; uint32_t xph = 0, bph = 0;
+            long long pos = r_begin; Seg sg; int it = 0;
+            while (next_seg(pos, sg)) {
+                const int a = it & 1;
+                wait(&sm->d_empty[a], (uint32_t)(((it >> 1) & 1) ^ 1));      // the epilogue has drained this accumulator
+                tc_fence_after();
+                const uint32_t d_tmem = tmem + (uint32_t)(a * TN);
+                for (int kb = sg.kb0; kb < sg.kb1; kb++) {
+                    wait(&sm->x_full[xi], xph);
+                    wait(&sm->b_full[bi], bph);
+                    tc_fence_after();
+                    const uint64_t ad = adesc0 + (uint64_t)(xi * (X_BYTES >> 4));
+                    const uint64_t bd = bdesc0 + (uint64_t)(bi * (B_BYTES >> 4));
+#pragma unroll
+                    for (int kk = 0; kk < KB / 16; kk++)
+                        umma_f16_ss(d_tmem, ad + (uint64_t)(2 * kk), bd + (uint64_t)(2 * kk), idesc, (kb != sg.kb0 || kk != 0) ? 1u : 0u);
+                    umma_commit(&sm->x_empty[xi]);
+                    umma_commit(&sm->b_empty[bi]);
+                    if (++xi == XST) { xi = 0; xph ^= 1u; }
+                    if (++bi == BST) { bi = 0; bph ^= 1u; }
+                }
+                umma_commit(&sm->d_full[a]);
+                it++;
+            }
+        }
+    } else if (warp < EPI_WARP0) {
+        // ================= converters: packed INT4 (smem) -> FP16 B tile (smem, K-major, 128-byte swizzle) =================
+        const int row = (warp - 2) * 32 + lane;          // weight row inside the tile
+        const uint32_t swz = (uint32_t)(row & 7);
+        int wi = 0, bi = 0; uint32_t wph = 0, bph = 0;
+        long long pos = r_begin; Seg sg;
+        while (next_seg(pos, sg)) {
+            for (int kb = sg.kb0; kb < sg.kb1; kb++) {
+                const int sub = kb % WKB;
+                if (sub == 0 || kb == sg.kb0) wait(&sm->w_full[wi], wph);
+                const unsigned char *wrow = ws + (size_t)wi * W_BYTES + row * 128;
+                const uint4 w0 = *reinterpret_cast<const uint4 *>(wrow + ((((uint32_t)(2 * sub)) ^ swz) << 4));
+                const uint4 w1 = *reinterpret_cast<const uint4 *>(wrow + ((((uint32_t)(2 * sub + 1)) ^ swz) << 4));
+                if (sub == WKB - 1 || kb == sg.kb1 - 1) {
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sm->w_empty[wi]);
+                    if (++wi == WST) { wi = 0; wph ^= 1u; }
+                }
+                const uint32_t ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                wait(&sm->b_empty[bi], bph ^ 1u);
+                unsigned char *brow = bsm + (size_t)bi * B_BYTES + row * 128;
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    uint32_t o[4];
+                    int4x8_to_half2x4_natural(ww[j], o);
+                    *reinterpret_cast<uint4 *>(brow + ((((uint32_t)j) ^ swz) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                }
+                fence_proxy_async();                     // the tensor core reads shared memory through the async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sm->b_full[bi]);
+                if (++bi == BST) { bi = 0; bph ^= 1u; }
+            }
+        }
+    } else {
+        // ================= epilogue: TMEM -> (+ partials) -> scale, sparse term, bias -> FP16 -> global =================
+        const int q = warp & 3;                          // TMEM lane quarter of this warp
+        const int tok = q * 32 + lane;                   // token of this thread
+        const int et = (warp - EPI_WARP0) * 32 + lane;   // 0..127 among the epilogue threads
+        const bool warp_on = q * 32 < p.M;               // this warp's lanes hold real tokens
+        const bool vec_ok = (p.ldy % 8) == 0 && (reinterpret_cast<uintptr_t>(p.y) & 15u) == 0;
+        long long pos = r_begin; Seg sg; int it = 0;
+        while (next_seg(pos, sg)) {
+            const int a = it & 1;
+            const int n0 = sg.t * TN;
+            const bool owner = sg.kb0 == 0;
+            // contributors: the CTAs behind this one whose share starts inside the same row tile
+            int c_first = 0, c_last = -1;
+            if (owner && sg.kb1 < p.kblocks) {
+                c_first = cta + 1;
+                c_last = cta;
+                const long long tile_end = (long long)(sg.t + 1) * p.kblocks;
+                while (c_last + 1 < G && p.total * (c_last + 1) / G < tile_end) c_last++;
+            }
+            if (owner) {
+                for (int i = et; i < TN; i += EPI_WARPS * 32) {
+                    const int n = n0 + i;
+                    sm->sc[i] = n < p.N ? __half2float(p.scales[n]) : 0.f;
+                    sm->bs[i] = (p.bias && n < p.N) ? p.bias[n] : 0.f;
+                }
+            }
+            wait(&sm->d_full[a], (uint32_t)((it >> 1) & 1));
+            tc_fence_after();
+            if (owner && c_last >= c_first) {
+                if (et == 0 && !dead) {                  // bounded wait for the contributors' flags
+                    for (int c = c_first; c <= c_last; c++) {
+                        int seen = 0;
+                        for (unsigned spin = 0; spin < (1u << 22); spin++) {
+                            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(p.flags + c) : "memory");
+                            if (seen) break;
+                            __nanosleep(64);
+                        }
+                        if (!seen) { atomicExch(p.status, 1); break; }
+                    }
+                }
+            }
+            named_bar_sync(1, EPI_WARPS * 32);           // scales staged, flags seen
+            if (warp_on) {
+                const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * TN);
+                if (!owner) {
+                    float *dst = p.slots + ((size_t)cta * p.mrows + tok) * TN;
+                    for (int c = 0; c < TN / 32; c++) {
+                        uint32_t r[32];
+                        tmem_ld_32x32b_x32(taddr + (uint32_t)(c * 32), r);
+                        tmem_ld_wait();
+                        float4 *d4 = reinterpret_cast<float4 *>(dst + c * 32);
+#pragma unroll
+                        for (int j4 = 0; j4 < 8; j4++)
+                            d4[j4] = make_float4(__uint_as_float(r[4 * j4]), __uint_as_float(r[4 * j4 + 1]),
+                                                 __uint_as_float(r[4 * j4 + 2]), __uint_as_float(r[4 * j4 + 3]));
+                    }
+                } else {
+                    for (int c = 0; c < TN / 32; c++) {
+                        const int nc = n0 + c * 32;
+                        if (nc >= p.N) break;
+                        uint32_t r[32];
+                        tmem_ld_32x32b_x32(taddr + (uint32_t)(c * 32), r);
+                        tmem_ld_wait();
+                        float v[32];
+#pragma unroll
+                        for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
+                        for (int cc = c_first; cc <= c_last; cc++) {
+                            const float4 *s4 = reinterpret_cast<const float4 *>(p.slots + ((size_t)cc * p.mrows + tok) * TN + c * 32);
+#pragma unroll
+                            for (int j4 = 0; j4 < 8; j4++) {
+                                const float4 t4 = __ldcg(s4 + j4);
+                                v[4 * j4] += t4.x; v[4 * j4 + 1] += t4.y; v[4 * j4 + 2] += t4.z; v[4 * j4 + 3] += t4.w;
+                            }
+                        }
+                        if (tok < p.M) {
+#pragma unroll
+                            for (int j = 0; j < 32; j++) v[j] = fmaf(v[j], sm->sc[c * 32 + j], sm->bs[c * 32 + j]);
+                            if (p.has_ortho) {
+                                const float *orow = p.o + (size_t)tok * p.N + nc;
+                                if (nc + 32 <= p.N && (p.N % 4) == 0) {
+#pragma unroll
+                                    for (int j4 = 0; j4 < 8; j4++) {
+                                        const float4 o4 = *reinterpret_cast<const float4 *>(orow + 4 * j4);
+                                        v[4 * j4] = fmaf(p.alpha, o4.x, v[4 * j4]); v[4 * j4 + 1] = fmaf(p.alpha, o4.y, v[4 * j4 + 1]);
+                                        v[4 * j4 + 2] = fmaf(p.alpha, o4.z, v[4 * j4 + 2]); v[4 * j4 + 3] = fmaf(p.alpha, o4.w, v[4 * j4 + 3]);
+                                    }
+                                } else {
+                                    for (int j = 0; j < 32 && nc + j < p.N; j++) v[j] = fmaf(p.alpha, orow[j], v[j]);
+                                }
+                            }
+                            uint32_t h[16];
+#pragma unroll
+                            for (int j = 0; j < 16; j++) {
+                                const __half2 hh = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+                                h[j] = *reinterpret_cast<const uint32_t *>(&hh);
+                            }
+                            const size_t at = (size_t)tok * (size_t)p.ldy + nc;
+                            const int nranks = p.gather ? p.gv.world : 1;
+                            for (int rk = 0; rk < nranks; rk++) {
+                                __half *dst = (p.gather ? p.gv.y[rk] : p.y) + at;
+                                if (vec_ok && nc + 32 <= p.N && (nc % 8) == 0) {
+#pragma unroll
+                                    for (int j4 = 0; j4 < 4; j4++)
+                                        reinterpret_cast<uint4 *>(dst)[j4] = make_uint4(h[4 * j4], h[4 * j4 + 1], h[4 * j4 + 2], h[4 * j4 + 3]);
+                                } else {
+                                    const __half *hs = reinterpret_cast<const __half *>(h);
+                                    for (int j = 0; j < 32 && nc + j < p.N; j++) dst[j] = hs[j];
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm->d_empty[a]);
+            if (!owner) {
+                __threadfence();
+                named_bar_sync(1, EPI_WARPS * 32);
+                if (et == 0) asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p.flags + cta), "r"(1) : "memory");
+            } else {
+                named_bar_sync(1, EPI_WARPS * 32);       // the staged scales are rewritten by the next piece
+            }
+            it++;
+        }
+    }
+
+    if (p.gather) {
+        if (!gather_signal_and_wait(p.gv, gridDim.x)) atomicExch(p.status, 2);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
+}
+
+// O[m][n] = sum over the entries of row n of v * x[m, c]   (FP32, token-major with row pitch N; alpha is applied
+// in the epilogue).  One warp per 8 consecutive weight rows; a lane holds TPL consecutive tokens (Mp = 32 * TPL)
+// and reads them from the transposed activations Xt[k][Mp] with one load per entry; entries are fetched 32 at a
+// time with one coalesced load and broadcast by shuffles.
+template <int TPL>
+__global__ void __launch_bounds__(256)
+ortho_tokens_kernel(const OrthoView ov, const __half *__restrict__ xt, float *__restrict__ o, int M, int K, int N)
+{
+    constexpr int Mp = 32 * TPL;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_first = (blockIdx.x * 8 + warp) * 8;
+    for (int r = 0; r < 8; r++) {
+        const int n = n_first + r;
+        if (n >= N) return;
+        const int e0 = ov.row_ptr[n], e1 = ov.row_ptr[n + 1];
+        float acc[TPL];
+#pragma unroll
+        for (int i = 0; i < TPL; i++) acc[i] = 0.f;
+        for (int eb = e0; eb < e1; eb += 32) {
+            int cl = 0; float vl = 0.f;
+            if (eb + lane < e1) {
+                if (ov.entries) {
+                    const uint32_t pk = ov.entries[eb + lane];
+                    cl = (int)(pk & 0xFFFFu);
+                    vl = __half2float(__ushort_as_half((unsigned short)(pk >> 16)));
+                } else {
+                    cl = ov.col[eb + lane];
+                    vl = __half2float(ov.val[eb + lane]);
+                    if ((unsigned)cl >= (unsigned)K) { cl = 0; vl = 0.f; }
+                }
+            }
+            const int nb = min(32, e1 - eb);
+            for (int j0 = 0; j0 < nb; j0 += 4) {
+                float vv[4]; const __half *xp[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const int c = __shfl_sync(0xffffffffu, cl, (j0 + j) & 31);
+                    vv[j] = __shfl_sync(0xffffffffu, vl, (j0 + j) & 31);      // slots past the row hold v = 0, c = 0
+                    xp[j] = xt + (size_t)c * Mp + lane * TPL;
+                }
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    if constexpr (TPL == 1) {
+                        acc[0] = fmaf(vv[j], __half2float(*xp[j]), acc[0]);
+                    } else if constexpr (TPL == 2) {
+                        const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(xp[j]));
+                        acc[0] = fmaf(vv[j], f.x, acc[0]); acc[1] = fmaf(vv[j], f.y, acc[1]);
+                    } else {
+                        const uint2 u = *reinterpret_cast<const uint2 *>(xp[j]);
+                        const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&u.x));
+                        const float2 f1 = __half22float2(*reinterpret_cast<const __half2 *>(&u.y));
+                        acc[0] = fmaf(vv[j], f0.x, acc[0]); acc[1] = fmaf(vv[j], f0.y, acc[1]);
+                        acc[2] = fmaf(vv[j], f1.x, acc[2]); acc[3] = fmaf(vv[j], f1.y, acc[3]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < TPL; i++) {
+            const int m = lane * TPL + i;
+            if (m < M) o[(size_t)m * N + n] = acc[i];
+        }
+    }
+}
+
+// workspace: [ Xt : K * Mp halves ][ O : M * N floats ][ partial slots : SMs * mrows * 256 floats ][ flags ]
+static int64_t mid_mp(int64_t M) { return M <= 32 ? 32 : M <= 64 ? 64 : 128; }
+static int64_t mid_xt_bytes(int64_t M, int64_t K) { return ((K * mid_mp(M) * 2 + 255) / 256) * 256; }
+static int64_t mid_o_bytes(int64_t M, int64_t N) { return ((M * N * 4 + 255) / 256) * 256; }
+static int64_t mid_slot_bytes(int64_t M, int sms) { return (int64_t)sms * ((M + 31) / 32 * 32) * md::TN * 4; }
+int64_t mid_workspace_bytes(int64_t M, int64_t K, int64_t N)
+{
+    return mid_xt_bytes(M, K) + mid_o_bytes(M, N) + mid_slot_bytes(M, 160) + 1024;
+}
+
+int launch_mid(const FwdArgs &a)
+{
+    using namespace md;
+    if (a.M > TMK || a.M < 1) return ORTHO_B200_ERR_SHAPE;
+    if (!a.workspace || a.workspace_bytes < mid_workspace_bytes(a.M, a.K, a.N)) return ORTHO_B200_ERR_WORKSPACE;
+    if (((uintptr_t)a.workspace & 255u) != 0) return ORTHO_B200_ERR_ALIGN;
+    const int dev = current_device_index();
+    if (dev < 0) return ORTHO_B200_ERR_CUDA;
+    const int num_sms = device_sm_count(dev);
+    if (num_sms > 160) return ORTHO_B200_ERR_DEVICE;
+    unsigned char *wsb = reinterpret_cast<unsigned char *>(a.workspace);
+    __half *xt = reinterpret_cast<__half *>(wsb);
+    float *o = reinterpret_cast<float *>(wsb + mid_xt_bytes(a.M, a.K));
+    float *slots = reinterpret_cast<float *>(wsb + mid_xt_bytes(a.M, a.K) + mid_o_bytes(a.M, a.N));
+    int *flags = reinterpret_cast<int *>(wsb + mid_xt_bytes(a.M, a.K) + mid_o_bytes(a.M, a.N) + mid_slot_bytes(a.M, 160));
+
+    Params p;
+    memset(&p, 0, sizeof(p));
+    p.scales = a.scales; p.bias = a.bias; p.y = a.y; p.M = (int)a.M; p.K = (int)a.K; p.N = (int)a.N; p.ldy = a.pitch_y();
+    p.tiles_n = (int)ceil_div(a.N, TN); p.kblocks = (int)ceil_div(a.K, KB);
+    p.total = (long long)p.tiles_n * p.kblocks;
+    p.mrows = (int)((a.M + 31) / 32 * 32);
+    p.slots = slots; p.flags = flags;
+    p.alpha = a.alpha; p.has_ortho = 0; p.o = nullptr;
+    p.status = kernel_status_word();
+    if (!p.status) return ORTHO_B200_ERR_CUDA;
+    if (a.has_ortho) {
+        const int Mp = (int)mid_mp(a.M);
+        int st = launch_transpose_x(a.x, xt, (int)a.M, (int)a.K, Mp, a.stream);
+        if (st != ORTHO_B200_OK) return st;
+        const unsigned blocks = (unsigned)ceil_div(a.N, 64);
+        if (Mp == 32) ortho_tokens_kernel<1><<<blocks, 256, 0, a.stream>>>(a.ortho, xt, o, (int)a.M, (int)a.K, (int)a.N);
+        else if (Mp == 64) ortho_tokens_kernel<2><<<blocks, 256, 0, a.stream>>>(a.ortho, xt, o, (int)a.M, (int)a.K, (int)a.N);
+        else ortho_tokens_kernel<4><<<blocks, 256, 0, a.stream>>>(a.ortho, xt, o, (int)a.M, (int)a.K, (int)a.N);
+        count_launch();
+        OB_CUDA(cudaGetLastError());
+        p.o = o; p.has_ortho = 1;
+    }
+    CUtensorMap xmap, wmap;
+    if (!make_tensor_map_2d(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.x, (uint64_t)a.M, (uint64_t)a.K,
+                            (uint64_t)a.K * 2, TMK, KB, CU_TENSOR_MAP_SWIZZLE_128B))
+        return ORTHO_B200_ERR_CUDA;
+    if (!make_tensor_map_2d(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.w, (uint64_t)a.N, (uint64_t)(a.K / 2),
+                            (uint64_t)(a.K / 2), TN, 128, CU_TENSOR_MAP_SWIZZLE_128B))
+        return ORTHO_B200_ERR_CUDA;
+    p.gather = 0;
+    if (a.gv && a.gv->world > 1) {
+        p.gv = *a.gv;
+        p.gather = 1;
+        if (a.gather_fused) *a.gather_fused = true;
+    }
+    static bool attr_set[kMaxDevices] = {};
+    if (!attr_set[dev]) {
+        OB_CUDA(cudaFuncSetAttribute(mid_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+        attr_set[dev] = true;
+    }
+    const long long grid = p.total < num_sms ? p.total : num_sms;
+    OB_CUDA(cudaMemsetAsync(flags, 0, (size_t)grid * sizeof(int), a.stream));
+    mid_kernel<<<(unsigned)grid, NWARPS * 32, kSmemBytes, a.stream>>>(xmap, wmap, p);
+    count_launch();
+    OB_CUDA(cudaGetLastError());
+    return ORTHO_B200_OK;
+}
+
+}  // namespace ob

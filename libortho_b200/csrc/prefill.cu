@@ -59,6 +59,7 @@ constexpr int A_STAGE_COLS = NH * (KB / 2);
 
 struct Params {
     const __half *scales; __half *y;
+    const float *bias;      // optional FP32 [N], added in the FP32 epilogue
     int M, K, N;
     long long ldy;          // elements between token rows of y
     int tiles_n, tiles_m, kblocks;
@@ -268,6 +269,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
             }
             const int n = nbase + q * 32 + lane;
             const float sc = (n < p.N) ? __half2float(p.scales[n]) : 0.f;
+            const float bs = (p.bias && n < p.N) ? p.bias[n] : 0.f;
             const float *orow = nullptr;               // this row's sparse term, if it has any entries
             if (p.has_ortho && n < p.N && p.row_ptr[n + 1] > p.row_ptr[n]) orow = p.o + (size_t)n * p.Mp + mt * TM;
             // the sparse term of a chunk is fetched one chunk ahead (the first one before the
@@ -325,15 +327,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                 if (orow) {                            // y = scale * D + alpha * O, one FP16 rounding
 #pragma unroll
                     for (int j4 = 0; j4 < 8; j4++) {
-                        ys[(4 * j4 + 0) * YS_PITCH + q * 32 + lane] = __float2half_rn(fmaf(p.alpha, ov[j4].x, __uint_as_float(r[4 * j4 + 0]) * sc));
-                        ys[(4 * j4 + 1) * YS_PITCH + q * 32 + lane] = __float2half_rn(fmaf(p.alpha, ov[j4].y, __uint_as_float(r[4 * j4 + 1]) * sc));
-                        ys[(4 * j4 + 2) * YS_PITCH + q * 32 + lane] = __float2half_rn(fmaf(p.alpha, ov[j4].z, __uint_as_float(r[4 * j4 + 2]) * sc));
-                        ys[(4 * j4 + 3) * YS_PITCH + q * 32 + lane] = __float2half_rn(fmaf(p.alpha, ov[j4].w, __uint_as_float(r[4 * j4 + 3]) * sc));
+                        ys[(4 * j4 + 0) * YS_PITCH + q * 32 + lane] = __float2half_rn(fmaf(p.alpha, ov[j4].x, fmaf(__uint_as_float(r[4 * j4 + 0]), sc, bs)));
+                        ys[(4 * j4 + 1) * YS_PITCH + q * 32 + lane] = __float2half_rn(fmaf(p.alpha, ov[j4].y, fmaf(__uint_as_float(r[4 * j4 + 1]), sc, bs)));
+                        ys[(4 * j4 + 2) * YS_PITCH + q * 32 + lane] = __float2half_rn(fmaf(p.alpha, ov[j4].z, fmaf(__uint_as_float(r[4 * j4 + 2]), sc, bs)));
+                        ys[(4 * j4 + 3) * YS_PITCH + q * 32 + lane] = __float2half_rn(fmaf(p.alpha, ov[j4].w, fmaf(__uint_as_float(r[4 * j4 + 3]), sc, bs)));
                     }
                     if (c + ESETS < TM / 32) load_o(c + ESETS);
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 32; j++) ys[j * YS_PITCH + q * 32 + lane] = __float2half_rn(__uint_as_float(r[j]) * sc);
+                    for (int j = 0; j < 32; j++) ys[j * YS_PITCH + q * 32 + lane] = __float2half_rn(fmaf(__uint_as_float(r[j]), sc, bs));
                 }
                 named_bar_sync(1 + eset, 128);
 #pragma unroll
@@ -409,7 +411,7 @@ int launch_prefill(const FwdArgs &a)
     if (!make_tensor_map_2d(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.w, (uint64_t)a.N, (uint64_t)(a.K / 2),
                             (uint64_t)(a.K / 2), TN, 128, CU_TENSOR_MAP_SWIZZLE_128B))
         return ORTHO_B200_ERR_CUDA;
-    p.scales = a.scales; p.y = a.y; p.M = (int)a.M; p.K = (int)a.K; p.N = (int)a.N; p.ldy = a.pitch_y();
+    p.scales = a.scales; p.y = a.y; p.bias = a.bias; p.M = (int)a.M; p.K = (int)a.K; p.N = (int)a.N; p.ldy = a.pitch_y();
     p.tiles_n = (int)ceil_div(a.N, TN); p.tiles_m = (int)ceil_div(a.M, TM); p.kblocks = (int)ceil_div(a.K, KB);
     p.status = kernel_status_word();
     if (!p.status) return ORTHO_B200_ERR_CUDA;

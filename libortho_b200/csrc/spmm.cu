@@ -42,6 +42,15 @@ transpose_x_kernel(const __half *__restrict__ x, __half *__restrict__ xt, int M,
     }
 }
 
+int launch_transpose_x(const __half *x, __half *xt, int M, int K, int Mp, cudaStream_t stream)
+{
+    dim3 tg((unsigned)ceil_div(K, 64), (unsigned)ceil_div(Mp, 64));
+    transpose_x_kernel<<<tg, 256, 0, stream>>>(x, xt, M, K, Mp);
+    count_launch();
+    OB_CUDA(cudaGetLastError());
+    return ORTHO_B200_OK;
+}
+
 struct SpmmParams {
     OrthoView ov;
     const int32_t *rbeg, *rend;    // entry range of work row r: [rbeg[r], rend[r]) (row_ptr / row_ptr + 1, or segments)

@@ -22,9 +22,37 @@ import torch
 import torch.nn as nn
 
 from . import _C_ops as _C
+from . import _lib
 from .sieve import pack_ortho_sparse
 
 _ORTHO_BUFFERS = ("ortho_values", "ortho_col_indices", "ortho_row_ptr")
+_WATCHED = frozenset(("base_weight", "base_scales", "bias") + _ORTHO_BUFFERS)
+
+
+class _SharedWorkspace:
+    """One grow-on-demand scratch buffer per device, shared by every module on it (a model with hundreds of
+    layers runs them one at a time).  Forwards that use it must be issued on one stream at a time."""
+    _by_device = {}
+
+    def __init__(self):
+        self.tensor: Optional[torch.Tensor] = None
+        self.gen = 0
+
+    @classmethod
+    def get(cls, device: torch.device, nbytes: int) -> "_SharedWorkspace":
+        w = cls._by_device.get(device)
+        if w is None:
+            w = cls._by_device[device] = cls()
+        if nbytes > 0 and (w.tensor is None or w.tensor.numel() < nbytes):
+            w.tensor = torch.empty(nbytes, dtype=torch.uint8, device=device)
+            w.gen += 1
+        return w
+
+
+class _Bound:
+    """Everything about one (module, token count) forward that does not change from call to call: the C
+    argument record with all buffer pointers, the plan, the workspace.  Built (and validated) once."""
+    __slots__ = ("descs", "ws", "ws_gen", "ws_ptr", "ws_bytes", "key", "fused_bias")
 
 
 class OrthoLinear(nn.Module):
@@ -51,7 +79,7 @@ class OrthoLinear(nn.Module):
         self._plan: Optional[_C.Plan] = None
         self._plan_key = None
         self._ws_need = {}
-        self._workspace: Optional[torch.Tensor] = None
+        self._bound = {}
 
     def set_alpha(self, alpha: float):
         self.alpha = alpha
@@ -94,11 +122,16 @@ class OrthoLinear(nn.Module):
         self._plan = None
         self._plan_key = None
         self._ws_need = {}
+        self._bound = {}
+
+    def __setattr__(self, name, value):
+        super().__setattr__(name, value)
+        if name in _WATCHED and "_bound" in self.__dict__:     # a buffer was replaced: cached pointers are stale
+            self._invalidate()
 
     def _apply(self, fn, recurse=True):
         out = super()._apply(fn, recurse)
         self._invalidate()
-        self._workspace = None
         return out
 
     def _load_from_state_dict(self, state_dict, prefix, *args, **kwargs):
@@ -126,10 +159,8 @@ class OrthoLinear(nn.Module):
             self._ws_need = {}
         return self._plan
 
-    def _get_workspace(self, M: int) -> Optional[torch.Tensor]:
+    def _workspace_bytes(self, M: int) -> int:
         sparse = self.alpha > 0 and self.ortho_values.numel() > 0
-        if not sparse and M <= 24:
-            return None
         plan = self._get_plan() if sparse else None
         key = (M, id(plan))
         need = self._ws_need.get(key)
@@ -138,12 +169,66 @@ class OrthoLinear(nn.Module):
             if len(self._ws_need) > 64:
                 self._ws_need.clear()
             self._ws_need[key] = need
+        return need
+
+    def _get_workspace(self, M: int) -> Optional[torch.Tensor]:
+        """The device's shared scratch buffer, grown to what a forward of M tokens needs (None if nothing)."""
+        need = self._workspace_bytes(M)
         if need == 0:
             return None
-        if (self._workspace is None or self._workspace.numel() < need
-                or self._workspace.device != self.base_weight.device):
-            self._workspace = torch.empty(need, dtype=torch.uint8, device=self.base_weight.device)
-        return self._workspace
+        return _SharedWorkspace.get(self.base_weight.device, need).tensor
+
+    def _versions(self):
+        """What a cached call record depends on besides the token count: the storage of every buffer (a
+        ``.data =`` assignment swaps it without going through ``__setattr__``) and the contents of the CSR
+        buffers (in-place edits show up in their version counters)."""
+        ov, oc, orp, b = self.ortho_values, self.ortho_col_indices, self.ortho_row_ptr, self.bias
+        return (self.base_weight.data_ptr(), self.base_scales.data_ptr(), ov.data_ptr(), oc.data_ptr(), orp.data_ptr(),
+                ov._version, oc._version, orp._version, (b.data_ptr(), b.dtype) if b is not None else None)
+
+    def _bind(self, M: int, dev: torch.device) -> _Bound:
+        N, K = self.out_features, self.in_features
+        bw, bs = self.base_weight, self.base_scales
+        if bw.dtype != torch.uint8 or bs.dtype != torch.float16:
+            raise TypeError("base_weight must be uint8 (packed INT4) and base_scales float16")
+        if tuple(bw.shape) != (N, K // 2) or bs.numel() != N or not bw.is_contiguous() or not bs.is_contiguous():
+            raise ValueError("base_weight / base_scales do not match (out_features, in_features // 2) / (out_features,)")
+        nnz = int(self.ortho_values.numel())
+        sparse = self.alpha > 0 and nnz > 0
+        tensors = [bw, bs] + ([self.ortho_values, self.ortho_col_indices, self.ortho_row_ptr] if nnz else [])
+        if any(t.device != dev for t in tensors):
+            raise RuntimeError("all buffers must live on the input's device")
+        if nnz:
+            if (self.ortho_values.dtype != torch.float16 or self.ortho_col_indices.dtype != torch.int32
+                    or self.ortho_row_ptr.dtype != torch.int32):
+                raise TypeError("ortho buffers must be float16 / int32 / int32")
+            if self.ortho_row_ptr.numel() != N + 1 or self.ortho_col_indices.numel() != nnz:
+                raise ValueError("CSR arrays have inconsistent sizes")
+        b = _Bound()
+        plan = self._get_plan() if sparse else None
+        need = self._workspace_bytes(M)
+        b.ws = _SharedWorkspace.get(dev, need)
+        b.ws_gen = b.ws.gen
+        b.ws_ptr = b.ws.tensor.data_ptr() if need else None
+        b.ws_bytes = b.ws.tensor.numel() if need else 0
+        b.fused_bias = (self.bias is not None and self.bias.dtype == torch.float32 and self.bias.device == dev
+                        and self.bias.is_contiguous())
+        descs = (_lib.LayerDesc * 1)()
+        d = descs[0]
+        d.q_weight, d.q_scales_f16 = bw.data_ptr(), bs.data_ptr()
+        d.ortho_values_f16 = self.ortho_values.data_ptr() if nnz else None
+        d.ortho_col_indices = self.ortho_col_indices.data_ptr() if nnz else None
+        d.ortho_row_ptr = self.ortho_row_ptr.data_ptr() if nnz else None
+        d.nnz = nnz
+        d.plan = plan.handle if plan is not None else None
+        d.bias_f32 = self.bias.data_ptr() if b.fused_bias else None
+        d.N, d.ldy, d.reserved = N, 0, 0
+        b.descs = descs
+        b.key = (self.alpha > 0, self._versions())
+        if len(self._bound) > 32:
+            self._bound.clear()
+        self._bound[M] = b
+        return b
 
     # -- forward ---------------------------------------------------------------------------------
     def forward(self, x: torch.Tensor) -> torch.Tensor:
@@ -153,15 +238,32 @@ class OrthoLinear(nn.Module):
         x_flat = x.reshape(-1, self.in_features)
         if x_flat.dtype != torch.float16:
             x_flat = x_flat.to(torch.float16)
-        x_flat = x_flat.contiguous()
+        if not x_flat.is_contiguous():
+            x_flat = x_flat.contiguous()
         M = x_flat.shape[0]
-        output = torch.empty(M, self.out_features, device=x.device, dtype=torch.float16)
+        dev = x.device
+        output = torch.empty(M, self.out_features, device=dev, dtype=torch.float16)
+        fused_bias = False
         if M:
-            _C.forward(self.base_weight, self.base_scales, self.ortho_values, self.ortho_col_indices,
-                       self.ortho_row_ptr, x_flat, output, self.alpha,
-                       plan=self._get_plan() if self.alpha > 0 else None,
-                       workspace=self._get_workspace(M))
-        if self.bias is not None:
+            alpha = float(self.alpha)
+            b = self._bound.get(M)
+            if b is None or b.key != (alpha > 0, self._versions()) or b.ws_gen != b.ws.gen:
+                b = self._bind(M, dev)
+            d = b.descs[0]
+            d.y_f16 = output.data_ptr()
+            d.alpha = alpha
+            fused_bias = b.fused_bias
+            lib = _lib.lib()
+            if torch.cuda.current_device() == dev.index:
+                st = lib.ortho_b200_forward_multi(b.descs, 1, x_flat.data_ptr(), M, self.in_features, b.ws_ptr, b.ws_bytes,
+                                                  torch.cuda.current_stream(dev).cuda_stream)
+            else:
+                with torch.cuda.device(dev):
+                    st = lib.ortho_b200_forward_multi(b.descs, 1, x_flat.data_ptr(), M, self.in_features, b.ws_ptr,
+                                                      b.ws_bytes, torch.cuda.current_stream(dev).cuda_stream)
+            if st:
+                _lib.check(st, "ortho_b200_forward_multi")
+        if self.bias is not None and not fused_bias:
             output += self.bias
         if output.dtype != x.dtype:
             output = output.to(x.dtype)

@@ -356,3 +356,86 @@ def test_sieve_derived_layer_alpha_sweep(oracle_mod, variant):
             d1 = (outs[1.0].float() - outs[0.0].float())
             assert d1.abs().max() > 1e-3
             assert torch.allclose(outs[0.5].float() - outs[0.0].float(), 0.5 * d1, atol=1.5e-2, rtol=0)
+
+
+@pytest.mark.parametrize("M,K,N", [(1, 512, 208), (7, 1024, 96), (16, 256, 144), (20, 384, 80), (40, 512, 272), (300, 256, 520)])
+def test_bias_is_added_inside_the_kernels(oracle_mod, M, K, N):
+    """Every kernel family adds the FP32 bias in its FP32 epilogue (one FP16 rounding): against the oracle's
+    FP32 output plus the bias (the reference adds it after the kernel, torch_bind/ortho_linear.py:164-166)."""
+    layer = wl.make_layer(K, N, 0.02, seed=200 + M)
+    x = wl.make_input(M, K, seed=200 + M)
+    g = torch.Generator().manual_seed(M)
+    bias = torch.randn(N, generator=g)
+    m = layer.to(DEV).to_module()
+    mb = OrthoLinear(K, N, bias=True).to(DEV)
+    mb.load_state_dict({**m.state_dict(), "bias": bias})
+    mb.set_alpha(0.75)
+    y = mb(x.to(DEV)).float().cpu().numpy()
+    assert _lib.lib().ortho_b200_query_kernel_status() == 0
+    ref = layer_oracle(oracle_mod, layer, x, 0.75) + bias.numpy()[None, :]
+    assert_close(y, ref, f"bias M={M}")
+    # a bias that is not FP32 still works (added after the kernel, as the reference does)
+    mb.bias.data = mb.bias.data.to(torch.float16)
+    y16 = mb(x.to(DEV)).float().cpu().numpy()
+    assert np.abs(y16 - ref).max() <= 5e-2
+
+
+@pytest.mark.parametrize("M,K,Ns", [(1, 4096, (512, 128, 128)), (4, 1024, (208, 96)), (16, 512, (144, 272, 80, 48)),
+                                    (8, 2048, (1000,)), (40, 512, (144, 96))])
+def test_layers_that_share_the_activations_in_one_call(oracle_mod, M, K, Ns):
+    """Separate projections over the same input (Q / K / V, gate / up) through ortho_b200_forward_multi: up to 16
+    tokens the tiles of all layers are walked by one launch.  Each member against the oracle with its own alpha
+    and bias, and bit-identical to its own single-layer forward."""
+    layers = [wl.make_layer(K, N, 0.02 if i != 1 else 0.0, seed=300 + i + M).to(DEV) for i, N in enumerate(Ns)]
+    alphas = [1.0, 0.5, 0.0, 0.25][:len(Ns)]
+    g = torch.Generator().manual_seed(M)
+    biases = [torch.randn(N, generator=g).to(DEV) if i % 2 == 0 else None for i, N in enumerate(Ns)]
+    x = wl.make_input(M, K, seed=300 + M).to(DEV)
+    outs = [torch.empty(M, N, dtype=torch.float16, device=DEV) for N in Ns]
+    n0 = _lib.lib().ortho_b200_launch_count()
+    _C_ops.forward_multi([(L.base_weight, L.base_scales, L.vals, L.col, L.row_ptr) for L in layers], x, outs,
+                         alphas=alphas, biases=biases)
+    launches = _lib.lib().ortho_b200_launch_count() - n0
+    torch.cuda.synchronize()
+    assert _lib.lib().ortho_b200_query_kernel_status() == 0
+    if M <= 16 and K % 256 == 0 and len(Ns) > 1:
+        assert launches == 1
+    for L, a, b, y in zip(layers, alphas, biases, outs):
+        ref = layer_oracle(oracle_mod, L.to("cpu"), x.cpu(), a)
+        if b is not None:
+            ref = ref + b.cpu().numpy()[None, :]
+        assert_close(y.float().cpu().numpy(), ref, f"multi M={M} N={L.N} alpha={a}")
+        y1 = torch.empty_like(y)
+        _C_ops.forward_multi([(L.base_weight, L.base_scales, L.vals, L.col, L.row_ptr)], x, [y1], alphas=[a], biases=[b])
+        assert torch.equal(y1, y)
+
+
+def test_swapped_model_runs_and_the_kill_switch_works():
+    """nn.Linear layers swapped for OrthoLinear: alpha = 1 is close to the dense model (INT4 base + residual),
+    alpha = 0 equals the INT4-only model bit for bit whatever the ortho part holds."""
+    import torch.nn as nn
+    from libortho_b200 import set_alpha_all, swap_linear
+    from libortho_b200.convert import base_only_split, sieve_split
+    g = torch.Generator().manual_seed(17)
+    dense = nn.Sequential(nn.Linear(256, 512, bias=True), nn.GELU(), nn.Linear(512, 128, bias=False)).to(DEV)
+    with torch.no_grad():
+        for p_ in dense.parameters():
+            p_.copy_((torch.randn(p_.shape, generator=g) * 0.02).to(DEV))
+    x = wl.make_input(5, 256, seed=17).to(DEV)
+    y_dense = dense(x.float())
+    import copy
+    a, b = copy.deepcopy(dense), copy.deepcopy(dense)
+    hd = {"0": torch.ones(256), "2": torch.ones(512)}
+    swap_linear(a, sieve_split(hd, sparsity_target=0.05))
+    swap_linear(b, base_only_split)
+    ya = a(x)
+    assert ya.dtype == torch.float16 and (ya.float() - y_dense).abs().max() < 0.05
+    # the sieve's base lies on the same INT4 grid as the base-only split (the re-derived FP32 scale may differ in
+    # its last bit): with the switch off both models agree to FP16 rounding, whatever the ortho part holds
+    set_alpha_all(a, 0.0)
+    assert (a(x).float() - b(x).float()).abs().max() < 4e-3
+    y_off = a(x)
+    for mod in a.modules():
+        if isinstance(mod, OrthoLinear):
+            mod.ortho_values = mod.ortho_values[:0]
+    assert torch.equal(a(x), y_off)

@@ -111,3 +111,42 @@ def test_library_exports_every_declared_symbol():
     assert l.ortho_b200_forward(8, 16, None, None, None, 0, 16, 16, 1, 64, 64, 1.0, None, None, 0, None) == 3
     assert l.ortho_b200_forward(None, None, None, None, None, 0, None, None, 0, 64, 64, 1.0, None, None, 0, None) == 0
     assert l.ortho_b200_set_decode_config(3, 3, 3, 3) == 2 and l.ortho_b200_set_decode_config(0, 0, 0, 0) == 0
+
+
+def test_swap_linear_replaces_modules_and_keeps_bias():
+    """Module swap on a two-layer toy model (CPU: packing only, the forward needs a GPU)."""
+    import torch.nn as nn
+    from libortho_b200 import set_alpha_all, swap_linear
+    from libortho_b200.convert import sieve_split
+    g = torch.Generator().manual_seed(3)
+
+    class Toy(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.up = nn.Linear(64, 96, bias=True)
+            self.act = nn.GELU()
+            self.block = nn.Sequential(nn.Linear(96, 32, bias=False))
+            self.lora_A = nn.Linear(64, 4, bias=False)       # adapters are left alone, as in the reference
+    toy = Toy()
+    with torch.no_grad():
+        for p_ in toy.parameters():
+            p_.copy_(torch.randn(p_.shape, generator=g) * 0.05)
+    w_up, b_up = toy.up.weight.detach().clone(), toy.up.bias.detach().clone()
+    hdiag = {"up": torch.rand(64, generator=g) + 0.5, "block.0": torch.rand(96, generator=g) + 0.5}
+    swapped = swap_linear(toy, sieve_split(hdiag, sparsity_target=0.05), alpha=0.5)
+    assert sorted(swapped) == ["block.0", "up"]
+    assert isinstance(toy.up, OrthoLinear) and isinstance(toy.block[0], OrthoLinear) and isinstance(toy.lora_A, nn.Linear)
+    assert toy.up.alpha == 0.5 and toy.up.bias.dtype == torch.float32 and torch.equal(toy.up.bias.detach(), b_up)
+    assert toy.block[0].bias is None
+    # same buffers as packing the sieve's split by hand
+    wb, wo = sieve.hessian_sieve(w_up, hdiag["up"], sparsity_target=0.05)
+    ref = OrthoLinear(64, 96)
+    ref.load_from_weights(wb, wo)
+    for name in ("base_weight", "ortho_col_indices", "ortho_row_ptr"):
+        assert torch.equal(getattr(toy.up, name), getattr(ref, name))
+    assert toy.up.ortho_values.numel() > 0
+    assert set_alpha_all(toy, 0.0) == 2 and toy.block[0].alpha == 0.0
+    # replacing a buffer drops the cached call state
+    toy.up._bound[1] = object()
+    toy.up.base_scales = toy.up.base_scales.clone()
+    assert toy.up._bound == {}
