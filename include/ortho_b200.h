@@ -299,7 +299,9 @@ ORTHO_B200_API int ortho_b200_query_kernel_status(void);
  *   row_groups == -1: streaming TMA kernel (M <= 16) with k_split CTAs per cluster and `unroll`
  *                    ring slots per warp (either may be 0 for the built-in choice);
  *   row_groups == -3: forwards with more than k_split tokens (0..ORTHO_B200_DECODE_MAX_M) use the
- *                    tensor-core kernel (built-in: 24);
+ *                    tensor-core kernels (built-in: 24);
+ *   row_groups == -4: forwards with unroll < tokens <= k_split (<= 128) use the tokens-as-M tensor-core kernel
+ *                    before any other rule (unroll == k_split: never); 0, 0 restores the built-in rule;
  *   row_groups == 0 : restore the built-in choice of kernel and tiling (not the -3 threshold).
  * Returns ERR_SHAPE for an unsupported tuple. */
 ORTHO_B200_API int ortho_b200_set_decode_config(int row_groups, int k_groups, int unroll, int k_split);

@@ -124,9 +124,8 @@ def forward(q_weight: torch.Tensor, q_scales: torch.Tensor, ortho_values: torch.
             raise TypeError("ortho buffers must be float16 / int32 / int32")
         if ortho_row_ptr.numel() != N + 1 or ortho_col_indices.numel() != nnz:
             raise ValueError("CSR arrays have inconsistent sizes")
-    # the sparse pre-pass needs its scratch; the tensor-core regime (more than 24 tokens) also uses scratch for
-    # the split-K of its last wave when it is given some
-    need = workspace_bytes(M, K, N, plan) if ((nnz and alpha > 0) or M > 24) else 0
+    # scratch of the tensor-core regimes (sparse pre-pass, partial sums of split tiles); 0 for the streaming kernels
+    need = workspace_bytes(M, K, N, plan)
     ws_ptr, ws_bytes = None, 0
     if need:
         if workspace is None or workspace.numel() * workspace.element_size() < need:
@@ -306,7 +305,7 @@ def forward_gather(q_weight: torch.Tensor, q_scales: torch.Tensor, ortho_values:
         raise ValueError("shape mismatch between q_weight/q_scales/input")
     dev = input.device
     nnz = int(ortho_values.numel()) if ortho_values is not None else 0
-    need = workspace_bytes(M, K, N, plan) if (nnz and alpha > 0 and N) else 0
+    need = workspace_bytes(M, K, N, plan) if N else 0
     ws_ptr, ws_bytes = None, 0
     if need:
         if workspace is None or workspace.numel() * workspace.element_size() < need:

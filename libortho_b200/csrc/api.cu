@@ -118,8 +118,10 @@ int64_t min_workspace_bytes(int64_t M, int64_t K, int64_t N)
 
 extern "C" int64_t ortho_b200_workspace_bytes(int64_t M, int64_t K, int64_t N)
 {
-    if (decode_regime(M, N, K)) return 0;
-    return prefill_workspace_bytes(M, K, N);
+    const int64_t other = decode_regime(M, N, K) ? 0 : prefill_workspace_bytes(M, K, N);
+    if (!mid_token_range(M)) return other;
+    const int64_t mid = mid_workspace_bytes(M, K, N);
+    return mid > other ? mid : other;
 }
 
 namespace ob {
@@ -137,8 +139,16 @@ int forward_impl(const void *q_weight, const void *q_scales_f16,
                                  x_f16, y_f16, M, K, N, alpha, plan, workspace, workspace_bytes, stream, ldy, bias_f32);
     if (st != ORTHO_B200_OK || M == 0) return st;
     a.gv = gv; a.gather_fused = gather_fused;
-    if (decode_regime(M, N, K)) return launch_decode(a);
-    return launch_prefill(a);
+    return launch_routed(a);
+}
+
+int launch_routed(const FwdArgs &a)
+{
+    switch (route_of(a.M, a.N, a.K, a.workspace, a.workspace_bytes)) {
+        case kRouteMid: return launch_mid(a);
+        case kRouteDecode: return launch_decode(a);
+        default: return launch_prefill(a);
+    }
 }
 
 // validates one layer's arguments and fills the launchers' argument record
@@ -231,11 +241,11 @@ extern "C" int ortho_b200_forward_multi(const ortho_b200_layer_desc *layers, int
                                      d.ortho_row_ptr, d.nnz, x_f16, d.y_f16, M, K, d.N, d.alpha, d.plan,
                                      workspace, workspace_bytes, stream, d.ldy, d.bias_f32);
         if (st != ORTHO_B200_OK) return st;
-        all_stream = all_stream && decode_regime(M, d.N, K) && stream_kernel_selected(M, K);
+        all_stream = all_stream && route_of(M, d.N, K, workspace, workspace_bytes) == kRouteDecode && stream_kernel_selected(M, K);
     }
     if (all_stream && n_layers > 1) return launch_decode_multi(a, n_layers);
     for (int l = 0; l < n_layers; l++) {
-        const int st = decode_regime(M, a[l].N, K) ? launch_decode(a[l]) : launch_prefill(a[l]);
+        const int st = launch_routed(a[l]);
         if (st != ORTHO_B200_OK) return st;
     }
     return ORTHO_B200_OK;

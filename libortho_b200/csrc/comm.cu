@@ -235,7 +235,9 @@ extern "C" int ortho_b200_forward_gather(const void *q_weight, const void *q_sca
     bool fused = false;
     // deferred mode: the streaming decode kernel waits for the previous exchange itself; any other
     // kernel is preceded by the one-thread wait kernel
-    if (cm->deferred && cm->world > 1 && !(N_local > 0 && stream_kernel_selected(M, K))) {
+    const bool self_waits = N_local > 0 && stream_kernel_selected(M, K) &&
+                            route_of(M, N_local, K, workspace, workspace_bytes) == kRouteDecode;
+    if (cm->deferred && cm->world > 1 && !self_waits) {
         gather_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(gv, status);
         OB_CUDA(cudaGetLastError());
         count_launch();

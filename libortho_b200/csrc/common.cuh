@@ -42,6 +42,11 @@ struct Tuning {
     bool force_stream = false;          // streaming kernel with stream_s / stream_stages
     int stream_s = 0, stream_stages = 0;
     int prefill_above = 24;             // forwards with more tokens than this use the tensor-core kernels
+    // forwards with mid_lo < tokens <= mid_hi use the tokens-as-M tensor-core kernel when they bring its workspace:
+    // built in, after the streaming kernels have had their pick (up to 24 tokens, and narrow layers); through the
+    // hook, first (mid_first)
+    int mid_lo = 24, mid_hi = 128;
+    bool mid_first = false;
 };
 constexpr int kPrefillAboveBuiltin = 24;
 Tuning tuning_snapshot();              // decode.cu
@@ -191,6 +196,7 @@ int make_fwd_args(FwdArgs &a, const void *q_weight, const void *q_scales_f16, co
                   const void *x_f16, void *y_f16, int64_t M, int64_t K, int64_t N, float alpha,
                   const ortho_b200_plan *plan, void *workspace, int64_t workspace_bytes, void *stream,
                   int64_t ldy, const float *bias_f32);
+int launch_routed(const FwdArgs &a);                      // api.cu: picks the kernel family and launches
 int launch_decode_multi(const FwdArgs *layers, int nl);   // decode.cu: one streaming launch for layers that share x
 int launch_prefill(const FwdArgs &a);
 int64_t prefill_workspace_bytes(int64_t M, int64_t K, int64_t N);
@@ -199,4 +205,11 @@ int set_decode_config(int wr, int wk, int u, int s);
 bool stream_kernel_selected(int64_t M, int64_t K);   // the forward of (M, K) will run decode_stream_kernel
 // true = decode kernels: up to Tuning::prefill_above tokens, and narrow layers of up to 64 tokens
 bool decode_regime(int64_t M, int64_t N, int64_t K);
+// which kernel family a forward takes.  The tokens-as-M kernel needs its workspace whatever alpha is; a call
+// inside its token range that brings none runs the kernels of the neighbouring regimes instead.
+enum Route { kRouteDecode = 0, kRouteMid = 1, kRoutePrefill = 2 };
+bool mid_token_range(int64_t M);
+Route route_of(int64_t M, int64_t N, int64_t K, const void *workspace, int64_t workspace_bytes);
+int launch_mid(const FwdArgs &a);                                  // mid.cu
+int64_t mid_workspace_bytes(int64_t M, int64_t K, int64_t N);
 }  // namespace ob

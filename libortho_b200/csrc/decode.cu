@@ -288,6 +288,24 @@ static bool decode_regime_of(const Tuning &t, int64_t M, int64_t N, int64_t K)
     return (M <= 32 && N <= 4096) || N <= 1024;
 }
 bool decode_regime(int64_t M, int64_t N, int64_t K) { return decode_regime_of(tuning_snapshot(), M, N, K); }
+bool mid_token_range(int64_t M)
+{
+    const Tuning t = tuning_snapshot();
+    return M > t.mid_lo && M <= t.mid_hi && M <= 128;
+}
+// Measured on one B200 (us, 0.3 % ortho, alpha = 1): 32 tokens on 8192->8192 / 8192->10240 / 8192->57344 / 28672->8192
+// take 68 / 72 / 222 / 135 with the tokens-as-M kernel against 95 / 108 / 370 / 218 with the 128 x 256-token tile of
+// prefill.cu; at 16 tokens the streaming kernel is level on the largest layer (205) and ahead on K = 4096 layers
+// (33 against 68 on 4096->22016), hence the built-in range (24, 128].
+Route route_of(int64_t M, int64_t N, int64_t K, const void *workspace, int64_t workspace_bytes)
+{
+    const Tuning t = tuning_snapshot();
+    const bool mid_ok = M > t.mid_lo && M <= t.mid_hi && M <= 128 && workspace && ((uintptr_t)workspace & 255u) == 0 &&
+                        workspace_bytes >= mid_workspace_bytes(M, K, N);
+    if (mid_ok && t.mid_first) return kRouteMid;
+    if (decode_regime_of(t, M, N, K)) return kRouteDecode;
+    return mid_ok ? kRouteMid : kRoutePrefill;
+}
 
 int launch_decode_stream(const FwdArgs &a, int S, int stages);          // decode_stream.cu
 int launch_decode_stream_multi(const FwdArgs *layers, int nl, int S, int stages);
@@ -299,6 +317,13 @@ int set_decode_config(int wr, int wk, int u, int s)
     if (wr == -3) {       // forwards with more than s tokens (0 <= s <= 64) go to the tensor-core prefill kernel
         if (s < 0 || s > ORTHO_B200_DECODE_MAX_M) return ORTHO_B200_ERR_SHAPE;
         t.prefill_above = s;
+        return ORTHO_B200_OK;
+    }
+    if (wr == -4) {       // forwards with u < tokens <= s (s <= 128) use the tokens-as-M tensor-core kernel whatever the
+                          // other rules say (u == s: never); u == s == 0 restores the built-in rule
+        if (u < 0 || s < 0 || s > 128 || u > s) return ORTHO_B200_ERR_SHAPE;
+        if (u == 0 && s == 0) { t.mid_lo = 24; t.mid_hi = 128; t.mid_first = false; }
+        else { t.mid_lo = u; t.mid_hi = s; t.mid_first = true; }
         return ORTHO_B200_OK;
     }
     if (wr == -1) {

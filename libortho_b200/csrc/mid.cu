@@ -27,7 +27,7 @@
 // partials last, so the bounded flag wait does not normally wait at all.
 //
 // The sparse term is computed ahead into O[m][n] (token-major FP32, in the workspace) by ortho_tokens_kernel
-// from the once-transposed activations, one warp per 8 weight rows, and added in the FP32 epilogue.
+// from the once-transposed activations, one warp per weight row, and added in the FP32 epilogue.
 #include <cstring>
 
 #include "common.cuh"
@@ -45,10 +45,16 @@ constexpr int TMK = 128;                // token lanes (MMA M)
 constexpr int KB = 64;                  // k per pipeline stage
 constexpr int WKB = 4;                  // k blocks covered by one packed-weight load
 constexpr int W_BYTES = TN * 128;       // 32 KB
-constexpr int X_BYTES = TMK * KB * 2;   // 16 KB
+constexpr int X_BYTES = TMK * KB * 2;   // 16 KB: a full token stage (fewer tokens use smaller stages, see Params::xstage)
 constexpr int B_BYTES = TN * KB * 2;    // 32 KB
-constexpr int WST = 2, XST = 3, BST = 3;
-constexpr int CONV_WARPS = 8;
+constexpr int BST = 2;                  // converted-weight stages (the converters work one k block ahead of the MMAs)
+constexpr int WST_MAX = 4, XST_MAX = 12;
+// The packed weights come from HBM: at the rate the tensor pipe can consume them (8 KB per ~0.4 us and SM) and a
+// loaded latency of 2-3 us, two 32 KB stages in flight per SM are the least that keeps the pipe fed, so the
+// shared memory left by the two B stages goes to packed-weight stages first (Params::wst) and the token stages
+// (which come from L2 and are small for few tokens) take the rest.
+constexpr int kSmemData = 214 * 1024;   // packed-weight + token + converted-weight stages
+constexpr int CONV_WARPS = 16;          // two threads per weight row: each converts 32 of the 64 k of a stage
 constexpr int EPI_WARP0 = 2 + CONV_WARPS;
 constexpr int EPI_WARPS = 4;
 constexpr int NWARPS = EPI_WARP0 + EPI_WARPS;
@@ -61,7 +67,11 @@ struct Params {
     int tiles_n, kblocks;
     long long total;            // tiles_n * kblocks
     int mrows;                  // token rows kept per partial slot (M rounded up to 32)
-    float *slots; int *flags;   // slots[cta][mrows][256], flags[cta]
+    int xbox_bytes;             // bytes one token-tile load delivers (token rows of the TMA box x 128)
+    int xstage, xst;            // bytes between token stages (xbox_bytes rounded up to 1 KB) and how many there are
+    int wst;                    // packed-weight stages
+    float *slots; int *flags;   // slots[2 * cta + which][mrows][256] (which = 0: sums handed to another CTA, 1: this
+                                // CTA's own sums of a tile it finishes), flags[cta]
     const float *o; float alpha; int has_ortho;    // O[m][n], row pitch N
     int *status;
     int gather;
@@ -69,14 +79,14 @@ struct Params {
 };
 
 struct Smem {
-    uint64_t w_full[WST], w_empty[WST];
-    uint64_t x_full[XST], x_empty[XST];
+    uint64_t w_full[WST_MAX], w_empty[WST_MAX];
+    uint64_t x_full[XST_MAX], x_empty[XST_MAX];
     uint64_t b_full[BST], b_empty[BST];
     uint64_t d_full[2], d_empty[2];
     uint32_t tmem_base;
     float sc[TN], bs[TN];
 };
-constexpr size_t kSmemBytes = 1024 + (size_t)WST * W_BYTES + (size_t)XST * X_BYTES + (size_t)BST * B_BYTES + sizeof(Smem) + 256;
+constexpr size_t kSmemBytes = 1024 + (size_t)kSmemData + sizeof(Smem) + 256;
 
 struct Seg { int t, kb0, kb1; };
 }  // namespace md
@@ -88,17 +98,17 @@ mid_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char *base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     unsigned char *ws = base;
-    unsigned char *xs = ws + (size_t)WST * W_BYTES;
-    unsigned char *bsm = xs + (size_t)XST * X_BYTES;
-    Smem *sm = reinterpret_cast<Smem *>(bsm + (size_t)BST * B_BYTES);
+    unsigned char *xs = ws + (size_t)p.wst * W_BYTES;            // token stages; an MMA reads 128 token rows from a stage's
+    unsigned char *bsm = base + (size_t)kSmemData - (size_t)BST * B_BYTES;   // base, i.e. on into what follows it
+    Smem *sm = reinterpret_cast<Smem *>(base + (size_t)kSmemData);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int cta = blockIdx.x, G = gridDim.x;
     const long long r_begin = p.total * cta / G, r_end = p.total * (cta + 1) / G;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < WST; s++) { mbar_init(&sm->w_full[s], 1); mbar_init(&sm->w_empty[s], CONV_WARPS); }
-        for (int s = 0; s < XST; s++) { mbar_init(&sm->x_full[s], 1); mbar_init(&sm->x_empty[s], 1); }
+        for (int s = 0; s < WST_MAX; s++) { mbar_init(&sm->w_full[s], 1); mbar_init(&sm->w_empty[s], CONV_WARPS); }
+        for (int s = 0; s < XST_MAX; s++) { mbar_init(&sm->x_full[s], 1); mbar_init(&sm->x_empty[s], 1); }
         for (int s = 0; s < BST; s++) { mbar_init(&sm->b_full[s], CONV_WARPS); mbar_init(&sm->b_empty[s], 1); }
         for (int s = 0; s < 2; s++) { mbar_init(&sm->d_full[s], 1); mbar_init(&sm->d_empty[s], EPI_WARPS); }
         fence_mbar_init();
@@ -137,12 +147,12 @@ mid_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
                         wait(&sm->w_empty[wi], wph ^ 1u);
                         mbar_arrive_expect_tx(&sm->w_full[wi], W_BYTES);
                         tma_load_2d(ws + (size_t)wi * W_BYTES, &wmap, &sm->w_full[wi], (kb / WKB) * 128, sg.t * TN);
-                        if (++wi == WST) { wi = 0; wph ^= 1u; }
+                        if (++wi == p.wst) { wi = 0; wph ^= 1u; }
                     }
                     wait(&sm->x_empty[xi], xph ^ 1u);
-                    mbar_arrive_expect_tx(&sm->x_full[xi], X_BYTES);
-                    tma_load_2d(xs + (size_t)xi * X_BYTES, &xmap, &sm->x_full[xi], kb * KB, 0);
-                    if (++xi == XST) { xi = 0; xph ^= 1u; }
+                    mbar_arrive_expect_tx(&sm->x_full[xi], (uint32_t)p.xbox_bytes);
+                    tma_load_2d(xs + (size_t)xi * p.xstage, &xmap, &sm->x_full[xi], kb * KB, 0);
+                    if (++xi == p.xst) { xi = 0; xph ^= 1u; }
                 }
             }
         }
@@ -163,14 +173,14 @@ mid_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
                     wait(&sm->x_full[xi], xph);
                     wait(&sm->b_full[bi], bph);
                     tc_fence_after();
-                    const uint64_t ad = adesc0 + (uint64_t)(xi * (X_BYTES >> 4));
+                    const uint64_t ad = adesc0 + (uint64_t)(xi * (p.xstage >> 4));
                     const uint64_t bd = bdesc0 + (uint64_t)(bi * (B_BYTES >> 4));
 #pragma unroll
                     for (int kk = 0; kk < KB / 16; kk++)
                         umma_f16_ss(d_tmem, ad + (uint64_t)(2 * kk), bd + (uint64_t)(2 * kk), idesc, (kb != sg.kb0 || kk != 0) ? 1u : 0u);
                     umma_commit(&sm->x_empty[xi]);
                     umma_commit(&sm->b_empty[bi]);
-                    if (++xi == XST) { xi = 0; xph ^= 1u; }
+                    if (++xi == p.xst) { xi = 0; xph ^= 1u; }
                     if (++bi == BST) { bi = 0; bph ^= 1u; }
                 }
                 umma_commit(&sm->d_full[a]);
@@ -179,7 +189,9 @@ mid_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
         }
     } else if (warp < EPI_WARP0) {
         // ================= converters: packed INT4 (smem) -> FP16 B tile (smem, K-major, 128-byte swizzle) =================
-        const int row = (warp - 2) * 32 + lane;          // weight row inside the tile
+        const int cw = warp - 2;
+        const int row = (cw & 7) * 32 + lane;            // weight row inside the tile
+        const int half = cw >> 3;                        // which 32 k of the stage's 64 this thread converts
         const uint32_t swz = (uint32_t)(row & 7);
         int wi = 0, bi = 0; uint32_t wph = 0, bph = 0;
         long long pos = r_begin; Seg sg;
@@ -188,22 +200,21 @@ mid_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
                 const int sub = kb % WKB;
                 if (sub == 0 || kb == sg.kb0) wait(&sm->w_full[wi], wph);
                 const unsigned char *wrow = ws + (size_t)wi * W_BYTES + row * 128;
-                const uint4 w0 = *reinterpret_cast<const uint4 *>(wrow + ((((uint32_t)(2 * sub)) ^ swz) << 4));
-                const uint4 w1 = *reinterpret_cast<const uint4 *>(wrow + ((((uint32_t)(2 * sub + 1)) ^ swz) << 4));
+                const uint4 w0 = *reinterpret_cast<const uint4 *>(wrow + ((((uint32_t)(2 * sub + half)) ^ swz) << 4));
                 if (sub == WKB - 1 || kb == sg.kb1 - 1) {
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&sm->w_empty[wi]);
-                    if (++wi == WST) { wi = 0; wph ^= 1u; }
+                    if (++wi == p.wst) { wi = 0; wph ^= 1u; }
                 }
-                const uint32_t ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                const uint32_t ww[4] = {w0.x, w0.y, w0.z, w0.w};
+                uint32_t o[4][4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) int4x8_to_half2x4_natural(ww[j], o[j]);
                 wait(&sm->b_empty[bi], bph ^ 1u);
                 unsigned char *brow = bsm + (size_t)bi * B_BYTES + row * 128;
 #pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    uint32_t o[4];
-                    int4x8_to_half2x4_natural(ww[j], o);
-                    *reinterpret_cast<uint4 *>(brow + ((((uint32_t)j) ^ swz) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-                }
+                for (int j = 0; j < 4; j++)
+                    *reinterpret_cast<uint4 *>(brow + ((((uint32_t)(4 * half + j)) ^ swz) << 4)) = make_uint4(o[j][0], o[j][1], o[j][2], o[j][3]);
                 fence_proxy_async();                     // the tensor core reads shared memory through the async proxy
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sm->b_full[bi]);
@@ -217,16 +228,16 @@ mid_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
         const int et = (warp - EPI_WARP0) * 32 + lane;   // 0..127 among the epilogue threads
         const bool warp_on = q * 32 < p.M;               // this warp's lanes hold real tokens
         const bool vec_ok = (p.ldy % 8) == 0 && (reinterpret_cast<uintptr_t>(p.y) & 15u) == 0;
+        const int nranks = p.gather ? p.gv.world : 1;
         long long pos = r_begin; Seg sg; int it = 0;
         while (next_seg(pos, sg)) {
             const int a = it & 1;
             const int n0 = sg.t * TN;
             const bool owner = sg.kb0 == 0;
+            const bool whole = owner && sg.kb1 == p.kblocks;
             // contributors: the CTAs behind this one whose share starts inside the same row tile
-            int c_first = 0, c_last = -1;
-            if (owner && sg.kb1 < p.kblocks) {
-                c_first = cta + 1;
-                c_last = cta;
+            int c_first = cta + 1, c_last = cta;
+            if (owner && !whole) {
                 const long long tile_end = (long long)(sg.t + 1) * p.kblocks;
                 while (c_last + 1 < G && p.total * (c_last + 1) / G < tile_end) c_last++;
             }
@@ -237,26 +248,20 @@ mid_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
                     sm->bs[i] = (p.bias && n < p.N) ? p.bias[n] : 0.f;
                 }
             }
-            wait(&sm->d_full[a], (uint32_t)((it >> 1) & 1));
-            tc_fence_after();
-            if (owner && c_last >= c_first) {
-                if (et == 0 && !dead) {                  // bounded wait for the contributors' flags
-                    for (int c = c_first; c <= c_last; c++) {
-                        int seen = 0;
-                        for (unsigned spin = 0; spin < (1u << 22); spin++) {
-                            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(p.flags + c) : "memory");
-                            if (seen) break;
-                            __nanosleep(64);
-                        }
-                        if (!seen) { atomicExch(p.status, 1); break; }
-                    }
+            if (!dead) {                                 // a long wait (a whole piece of MMAs): poll with pauses
+                bool ok = false;
+                for (uint32_t i = 0; i < (1u << 22) && !ok; i++) {
+                    ok = mbar_try_wait(&sm->d_full[a], (uint32_t)((it >> 1) & 1));
+                    if (!ok) __nanosleep(256);
                 }
+                if (!ok) { dead = true; atomicExch(p.status, 1); }
             }
-            named_bar_sync(1, EPI_WARPS * 32);           // scales staged, flags seen
-            if (warp_on) {
-                const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * TN);
-                if (!owner) {
-                    float *dst = p.slots + ((size_t)cta * p.mrows + tok) * TN;
+            tc_fence_after();
+            const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * TN);
+            if (!whole) {
+                // a piece of a split tile: the raw FP32 sums go to this CTA's slot
+                if (warp_on) {
+                    float *dst = p.slots + ((size_t)(2 * cta + (owner ? 1 : 0)) * p.mrows + tok) * TN;
                     for (int c = 0; c < TN / 32; c++) {
                         uint32_t r[32];
                         tmem_ld_32x32b_x32(taddr + (uint32_t)(c * 32), r);
@@ -267,57 +272,123 @@ mid_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
                             d4[j4] = make_float4(__uint_as_float(r[4 * j4]), __uint_as_float(r[4 * j4 + 1]),
                                                  __uint_as_float(r[4 * j4 + 2]), __uint_as_float(r[4 * j4 + 3]));
                     }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sm->d_empty[a]);          // the accumulator is free again
+                __threadfence();
+                if (owner && et == 0 && !dead) {                       // bounded wait for the contributors' flags
+                    for (int c = c_first; c <= c_last; c++) {
+                        int seen = 0;
+                        for (unsigned spin = 0; spin < (1u << 22); spin++) {
+                            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(p.flags + c) : "memory");
+                            if (seen) break;
+                            __nanosleep(64);
+                        }
+                        if (!seen) { atomicExch(p.status, 1); break; }
+                    }
+                }
+                named_bar_sync(1, EPI_WARPS * 32);       // own sums written, scales staged, flags seen
+                if (!owner) {
+                    if (et == 0) asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p.flags + cta), "r"(1) : "memory");
                 } else {
-                    for (int c = 0; c < TN / 32; c++) {
-                        const int nc = n0 + c * 32;
-                        if (nc >= p.N) break;
-                        uint32_t r[32];
-                        tmem_ld_32x32b_x32(taddr + (uint32_t)(c * 32), r);
-                        tmem_ld_wait();
-                        float v[32];
+                    // the tile's pieces are added in CTA order (this CTA's first) by all epilogue threads: a unit is
+                    // one token x 4 consecutive weight rows, consecutive threads take consecutive units
+                    const int units = p.M * (TN / 4);
+                    for (int u = et; u < units; u += EPI_WARPS * 32) {
+                        const int m = u / (TN / 4), c4 = (u % (TN / 4)) * 4;
+                        const int n = n0 + c4;
+                        if (n >= p.N) continue;
+                        const float *mine = p.slots + ((size_t)(2 * cta + 1) * p.mrows + m) * TN + c4;
+                        const float *theirs = p.slots + ((size_t)(2 * cta) * p.mrows + m) * TN + c4;     // + (cc - cta) * cstride
+                        const size_t cstride = (size_t)2 * p.mrows * TN;
+                        float4 acc = __ldcg(reinterpret_cast<const float4 *>(mine));
+                        int cc = c_first;
+                        for (; cc + 3 <= c_last; cc += 4) {            // four loads in flight, added in CTA order
+                            float4 t4[4];
 #pragma unroll
-                        for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
-                        for (int cc = c_first; cc <= c_last; cc++) {
-                            const float4 *s4 = reinterpret_cast<const float4 *>(p.slots + ((size_t)cc * p.mrows + tok) * TN + c * 32);
+                            for (int i = 0; i < 4; i++) t4[i] = __ldcg(reinterpret_cast<const float4 *>(theirs + (size_t)(cc + i - cta) * cstride));
 #pragma unroll
-                            for (int j4 = 0; j4 < 8; j4++) {
-                                const float4 t4 = __ldcg(s4 + j4);
-                                v[4 * j4] += t4.x; v[4 * j4 + 1] += t4.y; v[4 * j4 + 2] += t4.z; v[4 * j4 + 3] += t4.w;
+                            for (int i = 0; i < 4; i++) { acc.x += t4[i].x; acc.y += t4[i].y; acc.z += t4[i].z; acc.w += t4[i].w; }
+                        }
+                        for (; cc <= c_last; cc++) {
+                            const float4 t4 = __ldcg(reinterpret_cast<const float4 *>(theirs + (size_t)(cc - cta) * cstride));
+                            acc.x += t4.x; acc.y += t4.y; acc.z += t4.z; acc.w += t4.w;
+                        }
+                        float v[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+                        for (int j = 0; j < 4; j++) v[j] = fmaf(v[j], sm->sc[c4 + j], sm->bs[c4 + j]);
+                        if (p.has_ortho) {
+#pragma unroll
+                            for (int j = 0; j < 4; j++)
+                                if (n + j < p.N) v[j] = fmaf(p.alpha, p.o[(size_t)m * p.N + n + j], v[j]);
+                        }
+                        const __half2 h01 = __floats2half2_rn(v[0], v[1]), h23 = __floats2half2_rn(v[2], v[3]);
+                        const size_t at = (size_t)m * (size_t)p.ldy + n;
+                        for (int rk = 0; rk < nranks; rk++) {
+                            __half *dst = (p.gather ? p.gv.y[rk] : p.y) + at;
+                            if (vec_ok && n + 4 <= p.N) {
+                                *reinterpret_cast<uint2 *>(dst) = make_uint2(*reinterpret_cast<const uint32_t *>(&h01),
+                                                                             *reinterpret_cast<const uint32_t *>(&h23));
+                            } else {
+                                const __half hs[4] = {__low2half(h01), __high2half(h01), __low2half(h23), __high2half(h23)};
+                                for (int j = 0; j < 4 && n + j < p.N; j++) dst[j] = hs[j];
                             }
                         }
-                        if (tok < p.M) {
+                    }
+                }
+                named_bar_sync(1, EPI_WARPS * 32);       // the staged scales are rewritten by the next piece
+                it++;
+                continue;
+            }
+            // the whole tile was accumulated here: straight from tensor memory to the output
+            named_bar_sync(1, EPI_WARPS * 32);           // scales staged
+            if (warp_on) {
+                for (int c = 0; c < TN / 32; c++) {
+                    const int nc = n0 + c * 32;
+                    if (nc >= p.N) break;
+                    uint32_t r[32];
+                    tmem_ld_32x32b_x32(taddr + (uint32_t)(c * 32), r);
+                    tmem_ld_wait();
+                    if (tok < p.M) {
+                        float v[32];
 #pragma unroll
-                            for (int j = 0; j < 32; j++) v[j] = fmaf(v[j], sm->sc[c * 32 + j], sm->bs[c * 32 + j]);
-                            if (p.has_ortho) {
-                                const float *orow = p.o + (size_t)tok * p.N + nc;
-                                if (nc + 32 <= p.N && (p.N % 4) == 0) {
+                        for (int j = 0; j < 32; j++) v[j] = fmaf(__uint_as_float(r[j]), sm->sc[c * 32 + j], sm->bs[c * 32 + j]);
+                        const bool full = nc + 32 <= p.N;
+                        if (p.has_ortho) {
+                            const float *orow = p.o + (size_t)tok * p.N + nc;
+                            if (full && (p.N % 4) == 0) {
 #pragma unroll
-                                    for (int j4 = 0; j4 < 8; j4++) {
-                                        const float4 o4 = *reinterpret_cast<const float4 *>(orow + 4 * j4);
-                                        v[4 * j4] = fmaf(p.alpha, o4.x, v[4 * j4]); v[4 * j4 + 1] = fmaf(p.alpha, o4.y, v[4 * j4 + 1]);
-                                        v[4 * j4 + 2] = fmaf(p.alpha, o4.z, v[4 * j4 + 2]); v[4 * j4 + 3] = fmaf(p.alpha, o4.w, v[4 * j4 + 3]);
-                                    }
-                                } else {
-                                    for (int j = 0; j < 32 && nc + j < p.N; j++) v[j] = fmaf(p.alpha, orow[j], v[j]);
+                                for (int j4 = 0; j4 < 8; j4++) {
+                                    const float4 o4 = *reinterpret_cast<const float4 *>(orow + 4 * j4);
+                                    v[4 * j4] = fmaf(p.alpha, o4.x, v[4 * j4]); v[4 * j4 + 1] = fmaf(p.alpha, o4.y, v[4 * j4 + 1]);
+                                    v[4 * j4 + 2] = fmaf(p.alpha, o4.z, v[4 * j4 + 2]); v[4 * j4 + 3] = fmaf(p.alpha, o4.w, v[4 * j4 + 3]);
                                 }
-                            }
-                            uint32_t h[16];
+                            } else {
 #pragma unroll
-                            for (int j = 0; j < 16; j++) {
-                                const __half2 hh = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
-                                h[j] = *reinterpret_cast<const uint32_t *>(&hh);
+                                for (int j = 0; j < 32; j++)
+                                    if (nc + j < p.N) v[j] = fmaf(p.alpha, orow[j], v[j]);
                             }
-                            const size_t at = (size_t)tok * (size_t)p.ldy + nc;
-                            const int nranks = p.gather ? p.gv.world : 1;
-                            for (int rk = 0; rk < nranks; rk++) {
-                                __half *dst = (p.gather ? p.gv.y[rk] : p.y) + at;
-                                if (vec_ok && nc + 32 <= p.N && (nc % 8) == 0) {
+                        }
+                        uint32_t h[16];
 #pragma unroll
-                                    for (int j4 = 0; j4 < 4; j4++)
-                                        reinterpret_cast<uint4 *>(dst)[j4] = make_uint4(h[4 * j4], h[4 * j4 + 1], h[4 * j4 + 2], h[4 * j4 + 3]);
-                                } else {
-                                    const __half *hs = reinterpret_cast<const __half *>(h);
-                                    for (int j = 0; j < 32 && nc + j < p.N; j++) dst[j] = hs[j];
+                        for (int j = 0; j < 16; j++) {
+                            const __half2 hh = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+                            h[j] = *reinterpret_cast<const uint32_t *>(&hh);
+                        }
+                        const size_t at = (size_t)tok * (size_t)p.ldy + nc;
+                        for (int rk = 0; rk < nranks; rk++) {
+                            __half *dst = (p.gather ? p.gv.y[rk] : p.y) + at;
+                            if (vec_ok && full && (nc % 8) == 0) {
+#pragma unroll
+                                for (int j4 = 0; j4 < 4; j4++)
+                                    reinterpret_cast<uint4 *>(dst)[j4] = make_uint4(h[4 * j4], h[4 * j4 + 1], h[4 * j4 + 2], h[4 * j4 + 3]);
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 16; j++) {
+                                    const __half2 hh = *reinterpret_cast<const __half2 *>(&h[j]);
+                                    if (nc + 2 * j < p.N) dst[2 * j] = __low2half(hh);
+                                    if (nc + 2 * j + 1 < p.N) dst[2 * j + 1] = __high2half(hh);
                                 }
                             }
                         }
@@ -327,13 +398,7 @@ mid_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm->d_empty[a]);
-            if (!owner) {
-                __threadfence();
-                named_bar_sync(1, EPI_WARPS * 32);
-                if (et == 0) asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p.flags + cta), "r"(1) : "memory");
-            } else {
-                named_bar_sync(1, EPI_WARPS * 32);       // the staged scales are rewritten by the next piece
-            }
+            named_bar_sync(1, EPI_WARPS * 32);           // the staged scales are rewritten by the next piece
             it++;
         }
     }
@@ -347,78 +412,88 @@ mid_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
 }
 
 // O[m][n] = sum over the entries of row n of v * x[m, c]   (FP32, token-major with row pitch N; alpha is applied
-// in the epilogue).  One warp per 8 consecutive weight rows; a lane holds TPL consecutive tokens (Mp = 32 * TPL)
-// and reads them from the transposed activations Xt[k][Mp] with one load per entry; entries are fetched 32 at a
-// time with one coalesced load and broadcast by shuffles.
+// in the epilogue).  One warp per weight row; a lane holds TPL consecutive tokens (Mp = 32 * TPL) and reads them
+// from the transposed activations Xt[k][Mp] with one load per entry; entries are fetched 32 at a time with one
+// coalesced load and broadcast by shuffles.
 template <int TPL>
 __global__ void __launch_bounds__(256)
 ortho_tokens_kernel(const OrthoView ov, const __half *__restrict__ xt, float *__restrict__ o, int M, int K, int N)
 {
     constexpr int Mp = 32 * TPL;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n_first = (blockIdx.x * 8 + warp) * 8;
-    for (int r = 0; r < 8; r++) {
-        const int n = n_first + r;
-        if (n >= N) return;
-        const int e0 = ov.row_ptr[n], e1 = ov.row_ptr[n + 1];
-        float acc[TPL];
+    const int n = blockIdx.x * 8 + warp;                 // one warp per weight row
+    if (n >= N) return;
+    const int e0 = ov.row_ptr[n], e1 = ov.row_ptr[n + 1];
+    float acc[TPL];
 #pragma unroll
-        for (int i = 0; i < TPL; i++) acc[i] = 0.f;
-        for (int eb = e0; eb < e1; eb += 32) {
-            int cl = 0; float vl = 0.f;
-            if (eb + lane < e1) {
-                if (ov.entries) {
-                    const uint32_t pk = ov.entries[eb + lane];
-                    cl = (int)(pk & 0xFFFFu);
-                    vl = __half2float(__ushort_as_half((unsigned short)(pk >> 16)));
-                } else {
-                    cl = ov.col[eb + lane];
-                    vl = __half2float(ov.val[eb + lane]);
-                    if ((unsigned)cl >= (unsigned)K) { cl = 0; vl = 0.f; }
-                }
+    for (int i = 0; i < TPL; i++) acc[i] = 0.f;
+    for (int eb = e0; eb < e1; eb += 32) {
+        int cl = 0; float vl = 0.f;
+        if (eb + lane < e1) {
+            if (ov.entries) {
+                const uint32_t pk = ov.entries[eb + lane];
+                cl = (int)(pk & 0xFFFFu);
+                vl = __half2float(__ushort_as_half((unsigned short)(pk >> 16)));
+            } else {
+                cl = ov.col[eb + lane];
+                vl = __half2float(ov.val[eb + lane]);
+                if ((unsigned)cl >= (unsigned)K) { cl = 0; vl = 0.f; }
             }
-            const int nb = min(32, e1 - eb);
-            for (int j0 = 0; j0 < nb; j0 += 4) {
-                float vv[4]; const __half *xp[4];
+        }
+        const int nb = min(32, e1 - eb);
+        for (int j0 = 0; j0 < nb; j0 += 8) {             // eight independent activation loads in flight
+            float vv[8]; const __half *xp[8];
 #pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const int c = __shfl_sync(0xffffffffu, cl, (j0 + j) & 31);
-                    vv[j] = __shfl_sync(0xffffffffu, vl, (j0 + j) & 31);      // slots past the row hold v = 0, c = 0
-                    xp[j] = xt + (size_t)c * Mp + lane * TPL;
+            for (int j = 0; j < 8; j++) {
+                const int c = __shfl_sync(0xffffffffu, cl, (j0 + j) & 31);
+                vv[j] = __shfl_sync(0xffffffffu, vl, (j0 + j) & 31);      // slots past the row hold v = 0, c = 0
+                xp[j] = xt + (size_t)c * Mp + lane * TPL;
+            }
+            if constexpr (TPL == 1) {
+                __half h[8];
+#pragma unroll
+                for (int j = 0; j < 8; j++) h[j] = *xp[j];
+#pragma unroll
+                for (int j = 0; j < 8; j++) acc[0] = fmaf(vv[j], __half2float(h[j]), acc[0]);
+            } else if constexpr (TPL == 2) {
+                __half2 h[8];
+#pragma unroll
+                for (int j = 0; j < 8; j++) h[j] = *reinterpret_cast<const __half2 *>(xp[j]);
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const float2 f = __half22float2(h[j]);
+                    acc[0] = fmaf(vv[j], f.x, acc[0]); acc[1] = fmaf(vv[j], f.y, acc[1]);
                 }
+            } else {
+                uint2 u[8];
 #pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    if constexpr (TPL == 1) {
-                        acc[0] = fmaf(vv[j], __half2float(*xp[j]), acc[0]);
-                    } else if constexpr (TPL == 2) {
-                        const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(xp[j]));
-                        acc[0] = fmaf(vv[j], f.x, acc[0]); acc[1] = fmaf(vv[j], f.y, acc[1]);
-                    } else {
-                        const uint2 u = *reinterpret_cast<const uint2 *>(xp[j]);
-                        const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&u.x));
-                        const float2 f1 = __half22float2(*reinterpret_cast<const __half2 *>(&u.y));
-                        acc[0] = fmaf(vv[j], f0.x, acc[0]); acc[1] = fmaf(vv[j], f0.y, acc[1]);
-                        acc[2] = fmaf(vv[j], f1.x, acc[2]); acc[3] = fmaf(vv[j], f1.y, acc[3]);
-                    }
+                for (int j = 0; j < 8; j++) u[j] = *reinterpret_cast<const uint2 *>(xp[j]);
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&u[j].x));
+                    const float2 f1 = __half22float2(*reinterpret_cast<const __half2 *>(&u[j].y));
+                    acc[0] = fmaf(vv[j], f0.x, acc[0]); acc[1] = fmaf(vv[j], f0.y, acc[1]);
+                    acc[2] = fmaf(vv[j], f1.x, acc[2]); acc[3] = fmaf(vv[j], f1.y, acc[3]);
                 }
             }
         }
+    }
 #pragma unroll
-        for (int i = 0; i < TPL; i++) {
-            const int m = lane * TPL + i;
-            if (m < M) o[(size_t)m * N + n] = acc[i];
-        }
+    for (int i = 0; i < TPL; i++) {
+        const int m = lane * TPL + i;
+        if (m < M) o[(size_t)m * N + n] = acc[i];
     }
 }
 
 // workspace: [ Xt : K * Mp halves ][ O : M * N floats ][ partial slots : SMs * mrows * 256 floats ][ flags ]
+constexpr int kMidMaxSms = 148;         // the partial-sum slots are sized for this many CTAs; the grid never exceeds it
 static int64_t mid_mp(int64_t M) { return M <= 32 ? 32 : M <= 64 ? 64 : 128; }
 static int64_t mid_xt_bytes(int64_t M, int64_t K) { return ((K * mid_mp(M) * 2 + 255) / 256) * 256; }
 static int64_t mid_o_bytes(int64_t M, int64_t N) { return ((M * N * 4 + 255) / 256) * 256; }
-static int64_t mid_slot_bytes(int64_t M, int sms) { return (int64_t)sms * ((M + 31) / 32 * 32) * md::TN * 4; }
+static int64_t mid_slot_bytes(int64_t M, int sms) { return (int64_t)2 * sms * ((M + 31) / 32 * 32) * md::TN * 4; }
 int64_t mid_workspace_bytes(int64_t M, int64_t K, int64_t N)
 {
-    return mid_xt_bytes(M, K) + mid_o_bytes(M, N) + mid_slot_bytes(M, 160) + 1024;
+    return mid_xt_bytes(M, K) + mid_o_bytes(M, N) + mid_slot_bytes(M, kMidMaxSms) + 1024;
 }
 
 int launch_mid(const FwdArgs &a)
@@ -430,12 +505,11 @@ int launch_mid(const FwdArgs &a)
     const int dev = current_device_index();
     if (dev < 0) return ORTHO_B200_ERR_CUDA;
     const int num_sms = device_sm_count(dev);
-    if (num_sms > 160) return ORTHO_B200_ERR_DEVICE;
     unsigned char *wsb = reinterpret_cast<unsigned char *>(a.workspace);
     __half *xt = reinterpret_cast<__half *>(wsb);
     float *o = reinterpret_cast<float *>(wsb + mid_xt_bytes(a.M, a.K));
     float *slots = reinterpret_cast<float *>(wsb + mid_xt_bytes(a.M, a.K) + mid_o_bytes(a.M, a.N));
-    int *flags = reinterpret_cast<int *>(wsb + mid_xt_bytes(a.M, a.K) + mid_o_bytes(a.M, a.N) + mid_slot_bytes(a.M, 160));
+    int *flags = reinterpret_cast<int *>(wsb + mid_xt_bytes(a.M, a.K) + mid_o_bytes(a.M, a.N) + mid_slot_bytes(a.M, kMidMaxSms));
 
     Params p;
     memset(&p, 0, sizeof(p));
@@ -443,6 +517,18 @@ int launch_mid(const FwdArgs &a)
     p.tiles_n = (int)ceil_div(a.N, TN); p.kblocks = (int)ceil_div(a.K, KB);
     p.total = (long long)p.tiles_n * p.kblocks;
     p.mrows = (int)((a.M + 31) / 32 * 32);
+    // Only the token rows that exist are fetched (rounded up to the 8-row period of the swizzle).  The MMA still
+    // reads 128 rows of the stage: what the rows beyond the box hold only reaches accumulator rows nobody reads.
+    const int xbox_rows = (int)((a.M + 7) / 8 * 8);
+    p.xbox_bytes = xbox_rows * 128;
+    p.xstage = (p.xbox_bytes + 1023) / 1024 * 1024;
+    {
+        const int room = kSmemData - BST * B_BYTES;           // for packed-weight and token stages
+        p.wst = WST_MAX;
+        while (p.wst > 2 && (room - p.wst * W_BYTES) / p.xstage < 3) p.wst--;
+        const int xroom = room - p.wst * W_BYTES;
+        p.xst = xroom / p.xstage < XST_MAX ? xroom / p.xstage : XST_MAX;
+    }
     p.slots = slots; p.flags = flags;
     p.alpha = a.alpha; p.has_ortho = 0; p.o = nullptr;
     p.status = kernel_status_word();
@@ -451,7 +537,7 @@ int launch_mid(const FwdArgs &a)
         const int Mp = (int)mid_mp(a.M);
         int st = launch_transpose_x(a.x, xt, (int)a.M, (int)a.K, Mp, a.stream);
         if (st != ORTHO_B200_OK) return st;
-        const unsigned blocks = (unsigned)ceil_div(a.N, 64);
+        const unsigned blocks = (unsigned)ceil_div(a.N, 8);
         if (Mp == 32) ortho_tokens_kernel<1><<<blocks, 256, 0, a.stream>>>(a.ortho, xt, o, (int)a.M, (int)a.K, (int)a.N);
         else if (Mp == 64) ortho_tokens_kernel<2><<<blocks, 256, 0, a.stream>>>(a.ortho, xt, o, (int)a.M, (int)a.K, (int)a.N);
         else ortho_tokens_kernel<4><<<blocks, 256, 0, a.stream>>>(a.ortho, xt, o, (int)a.M, (int)a.K, (int)a.N);
@@ -461,7 +547,7 @@ int launch_mid(const FwdArgs &a)
     }
     CUtensorMap xmap, wmap;
     if (!make_tensor_map_2d(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.x, (uint64_t)a.M, (uint64_t)a.K,
-                            (uint64_t)a.K * 2, TMK, KB, CU_TENSOR_MAP_SWIZZLE_128B))
+                            (uint64_t)a.K * 2, (uint32_t)xbox_rows, KB, CU_TENSOR_MAP_SWIZZLE_128B))
         return ORTHO_B200_ERR_CUDA;
     if (!make_tensor_map_2d(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.w, (uint64_t)a.N, (uint64_t)(a.K / 2),
                             (uint64_t)(a.K / 2), TN, 128, CU_TENSOR_MAP_SWIZZLE_128B))
@@ -477,7 +563,8 @@ int launch_mid(const FwdArgs &a)
         OB_CUDA(cudaFuncSetAttribute(mid_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
         attr_set[dev] = true;
     }
-    const long long grid = p.total < num_sms ? p.total : num_sms;
+    long long grid = p.total < num_sms ? p.total : num_sms;
+    if (grid > kMidMaxSms) grid = kMidMaxSms;
     OB_CUDA(cudaMemsetAsync(flags, 0, (size_t)grid * sizeof(int), a.stream));
     mid_kernel<<<(unsigned)grid, NWARPS * 32, kSmemBytes, a.stream>>>(xmap, wmap, p);
     count_launch();

