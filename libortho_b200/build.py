@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 LIB_PATH = os.path.join(HERE, "libortho_b200.so")
-SOURCES = ["api.cu", "plan.cu", "decode.cu", "decode_stream.cu", "mid.cu", "prefill.cu", "spmm.cu", "static_scratch.cu", "comm.cu", "pack.cu", "sieve.cu"]
+SOURCES = ["api.cu", "plan.cu", "decode.cu", "decode_stream.cu", "mid.cu", "prefill.cu", "transpose.cu", "longrows.cu", "static_scratch.cu", "comm.cu", "pack.cu", "sieve.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--use_fast_math",

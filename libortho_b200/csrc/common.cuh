@@ -60,19 +60,16 @@ struct Plan {
     int64_t max_row_nnz;
     int32_t *row_ptr;     // [N+1] device copy
     uint32_t *entries;    // [nnz]
-    // rows longer than kPlanHeavy entries are split into segments of at most kPlanSeg entries
-    // for the prefill SpMM: segment v covers entries [vbeg[v], vend[v]); long row h (h < n_long) is
-    // output row hrow[h] and owns segments [hptr[h], hptr[h+1]).  Built on the host at plan creation.
-    int64_t n_virtual, n_long;
-    int32_t *vbeg, *vend, *hrow, *hptr;
-    // "long" for this layer: more than 32 entries (what the SpMM preloads per row) while the mean row fits in
-    // 32, else more than twice the mean.  What the split buys is a shorter longest chain of dependent gathers per
-    // warp, so rows are only cut when they stand out (a layer whose rows all hold ~90 entries is balanced as
-    // it is, and cutting it would triple the sparse-term traffic)
+    // Rows that stand out in length ("long": more than `heavy` entries = max(kLongRowMin, 4 x the mean row)) would
+    // hold up the tensor-core kernel's in-flight sparse pass, so the plan lists them (hrow, ascending) and cuts each
+    // into segments of at most kLongSeg entries: segment v covers entries [vbeg[v], vend[v]), long row h owns
+    // segments [hptr[h], hptr[h+1]).  A pre-pass computes their sums with whole CTAs per segment.  Built on the host.
     int heavy;
+    int64_t n_long, n_seg;
+    int32_t *hrow, *hptr, *vbeg, *vend;
 };
-constexpr int kPlanHeavy = 32;     // lower bound of the per-layer threshold; also the segment length floor
-constexpr int kNoPlanHeavy = 128;  // without a plan: rows above this are processed by a whole CTA
+constexpr int kLongRowMin = 256;
+constexpr int kLongSeg = 512;
 constexpr uint32_t kPlanMagic = 0x0B200A17u;
 
 // view of the ortho component handed to kernels: either packed plan entries or raw CSR
@@ -82,6 +79,19 @@ struct OrthoView {
     const int32_t *col;        // raw CSR path
     const __half *val;
 };
+// one stored entry as (column, value); an entry outside [0, K) of a raw CSR view reads as an explicit zero
+__device__ __forceinline__ void ortho_entry(const OrthoView &ov, int e, int K, int &c, float &v)
+{
+    if (ov.entries) {
+        const uint32_t pk = ov.entries[e];
+        c = (int)(pk & 0xFFFFu);
+        v = __half2float(__ushort_as_half((unsigned short)(pk >> 16)));
+    } else {
+        c = ov.col[e];
+        v = __half2float(ov.val[e]);
+        if ((unsigned)c >= (unsigned)K) { c = 0; v = 0.f; }
+    }
+}
 
 // ---- INT4 -> FP16 in registers ------------------------------------------------------------------
 // One 32-bit word holds 8 consecutive elements e0..e7 (e_i in bits [4i, 4i+4), low nibble = even
@@ -156,6 +166,31 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4],
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// Reduce V per-lane values over the 32 lanes with a halving butterfly: V/2 + V/4 + ... + 1
+// exchanges, then plain xor steps.  Returns the total of value index (lane >> (5 - log2 V)), valid
+// in every lane of that index group.  The order of additions is fixed.
+template <int V>
+__device__ __forceinline__ float butterfly_reduce(float (&v)[V], int lane)
+{
+    int off = 16;
+#pragma unroll
+    for (int half = V / 2; half >= 1; half >>= 1) {
+        const bool up = (lane & off) != 0;
+#pragma unroll
+        for (int j = 0; j < half; j++) {
+            const float send = up ? v[j] : v[j + half];
+            const float keep = up ? v[j + half] : v[j];
+            v[j] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+        }
+        off >>= 1;
+    }
+    float r = v[0];
+#pragma unroll
+    for (int o2 = 16; o2 >= 1; o2 >>= 1)
+        if (o2 <= off) r += __shfl_xor_sync(0xffffffffu, r, o2);
+    return r;
+}
+
 // streaming 128-bit load of read-once weight bytes: bypass L1 allocation
 __device__ __forceinline__ uint4 ldg_stream(const void *p) {
     uint4 v;
@@ -199,6 +234,8 @@ int make_fwd_args(FwdArgs &a, const void *q_weight, const void *q_scales_f16, co
 int launch_routed(const FwdArgs &a);                      // api.cu: picks the kernel family and launches
 int launch_decode_multi(const FwdArgs *layers, int nl);   // decode.cu: one streaming launch for layers that share x
 int launch_prefill(const FwdArgs &a);
+int64_t long_rows_workspace_bytes(const Plan *pl, int64_t M);            // longrows.cu
+int launch_long_rows(const FwdArgs &a, const __half *xt, int Mp, void *ws, const float **ol_out);
 int64_t prefill_workspace_bytes(int64_t M, int64_t K, int64_t N);
 int64_t min_workspace_bytes(int64_t M, int64_t K, int64_t N);
 int set_decode_config(int wr, int wk, int u, int s);

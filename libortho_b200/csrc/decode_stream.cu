@@ -73,32 +73,6 @@ __device__ __forceinline__ uint32_t prmt_b32(uint32_t a, uint32_t b, uint32_t se
     return d;
 }
 
-// Reduce V per-lane values over the 32 lanes with a halving butterfly: V/2 + V/4 + ... + 1
-// exchanges, then plain xor steps.  Returns the total of value index (lane >> (5 - log2 V)), valid
-// in every lane of that index group.  The order of additions is fixed.
-template <int V>
-__device__ __forceinline__ float butterfly_reduce(float (&v)[V], int lane)
-{
-    int off = 16;
-#pragma unroll
-    for (int half = V / 2; half >= 1; half >>= 1) {
-        const bool up = (lane & off) != 0;
-#pragma unroll
-        for (int j = 0; j < half; j++) {
-            const float send = up ? v[j] : v[j + half];
-            const float keep = up ? v[j + half] : v[j];
-            v[j] = keep + __shfl_xor_sync(0xffffffffu, send, off);
-        }
-        off >>= 1;
-    }
-    float r = v[0];
-#pragma unroll
-    for (int o2 = 16; o2 >= 1; o2 >>= 1)
-        if (o2 <= off) r += __shfl_xor_sync(0xffffffffu, r, o2);
-    return r;
-}
-
-
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

@@ -4,8 +4,8 @@
 // The reference kernels read CSR as three separate streams per row (row_ptr, then col_indices
 // and float values; src/dual_gemm.cu:106-130).  The re-layout keeps the CSR row-major order
 // (tools/sieve.py:131-136) but fuses column and value into one 32-bit word per entry
-// ({f16 value bits | 16-bit column}) and keeps its own copy of the row pointers; rows that stand
-// out in length are cut into segments (built on the host) for the prefill-regime sparse pass.
+// ({f16 value bits | 16-bit column}; an entry outside [0, K) becomes an explicit zero) and keeps its own
+// copy of the row pointers, so that every kernel reads one word per entry instead of two.
 #include <new>
 #include <vector>
 
@@ -111,8 +111,8 @@ extern "C" int ortho_b200_plan_create(ortho_b200_plan **plan_out, const int32_t 
     if (!pl) return ORTHO_B200_ERR_ALLOC;
     pl->magic = kPlanMagic; pl->K = K; pl->N = N; pl->nnz = nnz; pl->max_row_nnz = 0;
     pl->row_ptr = nullptr; pl->entries = nullptr;
-    pl->n_virtual = 0; pl->n_long = 0; pl->vbeg = nullptr; pl->vend = nullptr; pl->hrow = nullptr; pl->hptr = nullptr;
-    pl->heavy = kPlanHeavy;
+    pl->heavy = kLongRowMin; pl->n_long = 0; pl->n_seg = 0;
+    pl->hrow = nullptr; pl->hptr = nullptr; pl->vbeg = nullptr; pl->vend = nullptr;
     cudaError_t e = cudaGetDevice(&pl->device);
     if (e != cudaSuccess) { note_cuda_error(e); delete pl; return ORTHO_B200_ERR_CUDA; }
     if (nnz > 0) {
@@ -141,25 +141,21 @@ extern "C" int ortho_b200_plan_create(ortho_b200_plan **plan_out, const int32_t 
             return ORTHO_B200_ERR_CUDA;
         }
         pl->max_row_nnz = h_max;
-        {
-            // 32 entries are what the SpMM keeps preloaded per row (its fast path), so that is the cut while
-            // the mean row still fits it; denser layers are balanced as they are and only cut outliers
-            const int64_t mean = (nnz + N - 1) / N;
-            pl->heavy = (int)(mean <= kPlanHeavy ? kPlanHeavy : (2 * mean > 4096 ? 4096 : 2 * mean));
-        }
-        const int32_t kHeavyRow = pl->heavy, kSegLen = pl->heavy;
-        if (h_max > kHeavyRow) {
-            // split the long rows into segments on the host (one pass over the row pointers)
+        const int64_t mean = (nnz + N - 1) / N;
+        pl->heavy = (int)(4 * mean > kLongRowMin ? (4 * mean > 65536 ? 65536 : 4 * mean) : kLongRowMin);
+        if (h_max > pl->heavy) {
+            // list the long rows and cut them into segments on the host (one pass over the row pointers)
             std::vector<int32_t> rp((size_t)N + 1), vb, ve, hr, hp;
             e = cudaMemcpy(rp.data(), row_ptr, sizeof(int32_t) * (N + 1), cudaMemcpyDeviceToHost);
             if (e == cudaSuccess) {
                 for (int64_t n = 0; n < N; n++) {
                     const int32_t b = rp[n], en = rp[n + 1];
-                    if (en - b <= kHeavyRow) continue;
+                    if (en - b <= pl->heavy) continue;
                     hr.push_back((int32_t)n);
                     hp.push_back((int32_t)vb.size());
-                    for (int32_t s0 = b; s0 < en; s0 += kSegLen) {
-                        vb.push_back(s0); ve.push_back(s0 + kSegLen < en ? s0 + kSegLen : en);
+                    for (int32_t s0 = b; s0 < en; s0 += kLongSeg) {
+                        vb.push_back(s0);
+                        ve.push_back(s0 + kLongSeg < en ? s0 + kLongSeg : en);
                     }
                 }
                 hp.push_back((int32_t)vb.size());
@@ -172,7 +168,7 @@ extern "C" int ortho_b200_plan_create(ortho_b200_plan **plan_out, const int32_t 
                 if (e == cudaSuccess) e = cudaMemcpy(pl->vend, ve.data(), sizeof(int32_t) * nv, cudaMemcpyHostToDevice);
                 if (e == cudaSuccess) e = cudaMemcpy(pl->hrow, hr.data(), sizeof(int32_t) * nl, cudaMemcpyHostToDevice);
                 if (e == cudaSuccess) e = cudaMemcpy(pl->hptr, hp.data(), sizeof(int32_t) * (nl + 1), cudaMemcpyHostToDevice);
-                pl->n_virtual = (int64_t)nv;
+                pl->n_seg = (int64_t)nv;
                 pl->n_long = (int64_t)nl;
             }
             if (e != cudaSuccess) {
@@ -193,10 +189,10 @@ extern "C" int ortho_b200_plan_destroy(ortho_b200_plan *plan)
     if (pl->magic != kPlanMagic) return ORTHO_B200_ERR_PLAN;
     if (pl->row_ptr) cudaFree(pl->row_ptr);
     if (pl->entries) cudaFree(pl->entries);
-    if (pl->vbeg) cudaFree(pl->vbeg);
-    if (pl->vend) cudaFree(pl->vend);
     if (pl->hrow) cudaFree(pl->hrow);
     if (pl->hptr) cudaFree(pl->hptr);
+    if (pl->vbeg) cudaFree(pl->vbeg);
+    if (pl->vend) cudaFree(pl->vend);
     pl->magic = 0;
     delete pl;
     return ORTHO_B200_OK;
@@ -219,10 +215,9 @@ extern "C" int64_t ortho_b200_plan_workspace_bytes(const ortho_b200_plan *plan, 
     const Plan *pl = reinterpret_cast<const Plan *>(plan);
     if (!pl || pl->magic != kPlanMagic) return -1;
     if (pl->nnz == 0) return 0;
-    const int64_t plain = ortho_b200_workspace_bytes(M, pl->K, pl->N);     // includes the tokens-as-M kernel's needs
-    if (decode_regime(M, pl->N, pl->K)) return plain;
-    const int64_t pre = prefill_workspace_bytes(M, pl->K, pl->N + pl->n_virtual);
-    return pre > plain ? pre : plain;
+    const int64_t plain = ortho_b200_workspace_bytes(M, pl->K, pl->N);
+    // the tensor-core prefill kernel takes the sums of the plan's long rows from a pre-pass
+    return plain + (decode_regime(M, pl->N, pl->K) ? 0 : long_rows_workspace_bytes(pl, M));
 }
 
 extern "C" int ortho_b200_plan_decode_dump(const ortho_b200_plan *plan, int32_t *rows_out, int32_t *cols_out,

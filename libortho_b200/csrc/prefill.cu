@@ -5,24 +5,33 @@
 // base term is a real FP16 contraction with FP32 accumulation in tensor memory:
 //
 //     D[n, m] = sum_k  w_int[n, k] * x[m, k]          (tcgen05.mma, kind::f16)
-//     y[m, n] = scale[n] * D[n, m]  (+ alpha * ortho[m, n])
+//     y[m, n] = scale[n] * D[n, m] + bias[n] + alpha * O[n, m]
 //
 // The weight tile is the M operand of the MMA and lives in TENSOR MEMORY: TMA brings the packed
-// INT4 bytes (128 bytes = 256 k per row and load) into shared memory, converter warps (one thread per
+// INT4 bytes (128 bytes = 256 k per row and load) into shared memory, four converter warps (one thread per
 // output row) unpack them in registers to exact small-integer halves and write them with
-// tcgen05.st, so the converted weights never touch shared memory.  The token tile (128 tokens x
+// tcgen05.st, so the converted weights never touch shared memory.  The token tile (256 tokens x
 // 64 k, FP16, 128-byte swizzle) is the N operand and goes from global to shared memory by TMA and
-// from there straight into the MMA.  A tile is 256 output rows x 128 tokens: two accumulators of
-// 128 rows share every token stage, which halves the shared-memory fill per flop (the token tile is
-// by far the larger operand) and doubles the time one ring slot covers.  One elected thread issues
-// the MMAs.  The per-row scale is applied in the FP32 epilogue (it factors out of the K sum,
-// src/ortho.c:356,363); outputs are transposed through shared memory and stored coalesced.
+// from there straight into the MMA.  A tile is 128 output rows x 256 tokens (one 256-column FP32
+// accumulator); one elected thread issues the MMAs.  The per-row scale is applied in the FP32 epilogue (it
+// factors out of the K sum, src/ortho.c:356,363); outputs are transposed through shared memory and stored
+// coalesced.
 //
-// TMEM columns: [0,256) two accumulators, [256,512) ring of 4 converted weight stages.
+// The sparse ortho term is computed INSIDE this kernel by the epilogue warps while the tile's MMAs run
+// (the reference intends the same fusion, src/dual_gemm_tensor_core.cu:324-332, but scans the whole coordinate
+// list per output element): a warp walks one output row at a time with the tile's 256 tokens across its lanes
+// and gathers 16 bytes per entry and lane from the once-transposed activations Xt[k][m], eight entries in flight.
+// The sums of 32 rows are collected as FP16 in the (then idle) output staging tiles and moved, thread = row, into
+// the 128 tensor-memory columns that the accumulator and the weight ring leave free; the FP32 epilogue adds
+// alpha * O.  Rows that a plan marks as long get their sums from the pre-pass of longrows.cu instead of being
+// walked here.  Apart from the transposed activations there is no global scratch for the sparse term.
+//
+// TMEM columns: [0,256) accumulator, [256,384) ring of 4 converted weight stages, [384,512) sparse term.
 // Warp roles (CTA = 1 SM, persistent over tiles):
 //   warp 0       TMA producer           warp 1       MMA issuer, TMEM allocator
-//   warps 2-9    INT4 -> FP16 -> TMEM (one thread per output row of the tile)
-//   warps 10-17  epilogue (TMEM -> scale -> FP16 -> global), one set of 4 warps per accumulator
+//   warps 2-5    INT4 -> FP16 -> TMEM (one thread per output row of the tile)
+//   warps 6-13   sparse term, then epilogue (TMEM -> scale -> FP16 -> global): two sets of four warps that take
+//                alternate 32-token chunks
 #include <cstring>
 
 #include "common.cuh"
@@ -56,6 +65,10 @@ constexpr int NWARPS = EPI_WARP0 + EPI_WARPS;
 constexpr int TMEM_COLS = 512;
 constexpr int A_COL0 = NH * TM;          // accumulators occupy [0, NH*TM); converted weights follow
 constexpr int A_STAGE_COLS = NH * (KB / 2);
+constexpr int O_COL0 = A_COL0 + ASTAGES * A_STAGE_COLS;   // sparse term: 256 tokens as FP16 pairs = 128 columns
+static_assert(O_COL0 + TM / 2 <= TMEM_COLS, "tensor memory layout");
+constexpr int OB_PITCH = TM + 8;         // halves per row of the sparse term's 32-row batch buffer (pad against bank conflicts)
+static_assert(32 * OB_PITCH * 2 <= NH * ESETS * YS_BYTES, "the batch buffer lives in the staging tiles");
 
 struct Params {
     const __half *scales; __half *y;
@@ -64,9 +77,10 @@ struct Params {
     long long ldy;          // elements between token rows of y
     int tiles_n, tiles_m, kblocks;
     int *status;
-    // sparse term computed ahead by spmm_ortho_kernel: O[n][m] FP32 with row pitch Mp (rows without
-    // entries are never written and never read)
-    const int32_t *row_ptr; const float *o; int Mp; float alpha; int has_ortho;
+    // sparse term: CSR view (plan entries or raw arrays) and the transposed activations Xt[k][Mp] (zero for m >= M)
+    OrthoView ov; const __half *xt; int Mp; float alpha; int has_ortho;
+    // long rows of the plan: their sums OL[h][Mp] (FP32) come from the pre-pass of longrows.cu
+    const float *ol; const int32_t *hrow; int n_long, heavy;
     // split-K of the last, partial wave: tiles [full_tiles, full_tiles + n_split) are each worked on by two
     // CTAs (k-blocks [0, kh) and [kh, kblocks)); the second one leaves its raw FP32 accumulators in
     // part[j][128][TM] and raises flags[j], the first one adds them in its epilogue
@@ -270,21 +284,85 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
             const int n = nbase + q * 32 + lane;
             const float sc = (n < p.N) ? __half2float(p.scales[n]) : 0.f;
             const float bs = (p.bias && n < p.N) ? p.bias[n] : 0.f;
-            const float *orow = nullptr;               // this row's sparse term, if it has any entries
-            if (p.has_ortho && n < p.N && p.row_ptr[n + 1] > p.row_ptr[n]) orow = p.o + (size_t)n * p.Mp + mt * TM;
-            // the sparse term of a chunk is fetched one chunk ahead (the first one before the
-            // accumulator is even complete), so its latency never sits in the exposed epilogue
-            float4 ov[8];
-            auto load_o = [&](int c) {
-                const float4 *o4 = reinterpret_cast<const float4 *>(orow + c * 32);
+            // ---- sparse term of this tile, computed while its MMAs run: O[row][token] -> FP16 -> tensor memory ----
+            // A warp walks one row at a time with the 256 tokens of the tile across its lanes (8 per lane, one 16-byte
+            // gather per entry and lane, eight entries in flight).  The eight warps fill a 32-row batch (one
+            // tensor-memory lane quarter) in the staging tiles, then the two warps of that quarter, which alone may
+            // touch those lanes, move it into tensor memory with thread = row.
+            const bool with_o = p.has_ortho != 0;
+            if (with_o) {
+                __half *obuf = reinterpret_cast<__half *>(ys_base);          // [32][OB_PITCH]
+                const int ew = warp - EPI_WARP0;
+                const __half *xtile = p.xt + (size_t)mt * TM + lane * 8;       // + col * Mp
+                for (int qq = 0; qq < 4; qq++) {
+                    for (int i = 0; i < 4; i++) {
+                        const int r = ew * 4 + i;                              // row inside the quarter
+                        const int nrow = nbase + qq * 32 + r;
+                        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                        int e0 = 0, e1 = 0;
+                        if (nrow < p.N) { e0 = p.ov.row_ptr[nrow]; e1 = p.ov.row_ptr[nrow + 1]; }
+                        int li = -1;
+                        if (p.n_long > 0 && e1 - e0 > p.heavy) {               // a long row of the plan: its sums were computed ahead
+                            int lo = 0, hi = p.n_long - 1;
+                            while (lo < hi) {
+                                const int mid = (lo + hi) >> 1;
+                                if (p.hrow[mid] < nrow) lo = mid + 1; else hi = mid;
+                            }
+                            if (p.hrow[lo] == nrow) li = lo;
+                        }
+                        if (li >= 0) {
+                            const float4 *src = reinterpret_cast<const float4 *>(p.ol + (size_t)li * p.Mp + (size_t)mt * TM + lane * 8);
+                            const float4 a0 = src[0], a1 = src[1];
+                            acc[0] = a0.x; acc[1] = a0.y; acc[2] = a0.z; acc[3] = a0.w;
+                            acc[4] = a1.x; acc[5] = a1.y; acc[6] = a1.z; acc[7] = a1.w;
+                        } else {
+                            for (int eb = e0; eb < e1; eb += 32) {
+                                int cl = 0; float vl = 0.f;
+                                if (eb + lane < e1) ortho_entry(p.ov, eb + lane, p.K, cl, vl);
+                                const int nb = min(32, e1 - eb);
+                                for (int j0 = 0; j0 < nb; j0 += 8) {
+                                    uint4 xv[8]; float vv[8];
 #pragma unroll
-                for (int j4 = 0; j4 < 8; j4++) ov[j4] = o4[j4];
-            };
-            if (orow) {
-                load_o(eset);
-                // the other chunks of this row's sparse term: ask L2 for them while the MMAs still run
-                for (int c = eset + ESETS; c < TM / 32; c += ESETS)
-                    asm volatile("prefetch.global.L2 [%0];" ::"l"(orow + c * 32));
+                                    for (int j = 0; j < 8; j++) {
+                                        const int cc = __shfl_sync(0xffffffffu, cl, (j0 + j) & 31);
+                                        vv[j] = __shfl_sync(0xffffffffu, vl, (j0 + j) & 31);      // slots past the row hold v = 0, c = 0
+                                        xv[j] = __ldg(reinterpret_cast<const uint4 *>(xtile + (size_t)cc * p.Mp));
+                                    }
+#pragma unroll
+                                    for (int j = 0; j < 8; j++) {
+                                        const __half2 *h = reinterpret_cast<const __half2 *>(&xv[j]);
+#pragma unroll
+                                        for (int q2 = 0; q2 < 4; q2++) {
+                                            const float2 f = __half22float2(h[q2]);
+                                            acc[2 * q2] = fmaf(vv[j], f.x, acc[2 * q2]);
+                                            acc[2 * q2 + 1] = fmaf(vv[j], f.y, acc[2 * q2 + 1]);
+                                        }
+                                    }
+                                }
+                            }
+                        }
+                        const __half2 h0 = __floats2half2_rn(acc[0], acc[1]), h1 = __floats2half2_rn(acc[2], acc[3]);
+                        const __half2 h2 = __floats2half2_rn(acc[4], acc[5]), h3 = __floats2half2_rn(acc[6], acc[7]);
+                        *reinterpret_cast<uint4 *>(obuf + r * OB_PITCH + lane * 8) =
+                            make_uint4(*reinterpret_cast<const uint32_t *>(&h0), *reinterpret_cast<const uint32_t *>(&h1),
+                                       *reinterpret_cast<const uint32_t *>(&h2), *reinterpret_cast<const uint32_t *>(&h3));
+                    }
+                    named_bar_sync(3, EPI_WARPS * 32);           // the batch is complete
+                    if (q == qq) {
+                        for (int c = eset; c < TM / 32; c += ESETS) {
+                            const uint4 *src = reinterpret_cast<const uint4 *>(obuf + lane * OB_PITCH + c * 32);
+                            uint32_t hp[16];
+#pragma unroll
+                            for (int j4 = 0; j4 < 4; j4++) {
+                                const uint4 u = src[j4];
+                                hp[4 * j4] = u.x; hp[4 * j4 + 1] = u.y; hp[4 * j4 + 2] = u.z; hp[4 * j4 + 3] = u.w;
+                            }
+                            tmem_st_32x32b_x16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(O_COL0 + c * 16), hp);
+                        }
+                    }
+                    named_bar_sync(3, EPI_WARPS * 32);           // the batch buffer is free again
+                }
+                tmem_st_wait();
             }
             wait(&sm->d_full, (uint32_t)(it & 1));
             tc_fence_after();
@@ -324,15 +402,16 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                     }
                     if (c + ESETS < TM / 32) load_p(c + ESETS);
                 }
-                if (orow) {                            // y = scale * D + alpha * O, one FP16 rounding
+                if (with_o) {                          // y = scale * D + bias + alpha * O
+                    uint32_t ho[16];
+                    tmem_ld_32x32b_x16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(O_COL0 + c * 16), ho);
+                    tmem_ld_wait();
 #pragma unroll
-                    for (int j4 = 0; j4 < 8; j4++) {
-                        ys[(4 * j4 + 0) * YS_PITCH + q * 32 + lane] = __float2half_rn(fmaf(p.alpha, ov[j4].x, fmaf(__uint_as_float(r[4 * j4 + 0]), sc, bs)));
-                        ys[(4 * j4 + 1) * YS_PITCH + q * 32 + lane] = __float2half_rn(fmaf(p.alpha, ov[j4].y, fmaf(__uint_as_float(r[4 * j4 + 1]), sc, bs)));
-                        ys[(4 * j4 + 2) * YS_PITCH + q * 32 + lane] = __float2half_rn(fmaf(p.alpha, ov[j4].z, fmaf(__uint_as_float(r[4 * j4 + 2]), sc, bs)));
-                        ys[(4 * j4 + 3) * YS_PITCH + q * 32 + lane] = __float2half_rn(fmaf(p.alpha, ov[j4].w, fmaf(__uint_as_float(r[4 * j4 + 3]), sc, bs)));
+                    for (int j = 0; j < 16; j++) {
+                        const float2 o2 = __half22float2(*reinterpret_cast<const __half2 *>(&ho[j]));
+                        ys[(2 * j) * YS_PITCH + q * 32 + lane] = __float2half_rn(fmaf(p.alpha, o2.x, fmaf(__uint_as_float(r[2 * j]), sc, bs)));
+                        ys[(2 * j + 1) * YS_PITCH + q * 32 + lane] = __float2half_rn(fmaf(p.alpha, o2.y, fmaf(__uint_as_float(r[2 * j + 1]), sc, bs)));
                     }
-                    if (c + ESETS < TM / 32) load_o(c + ESETS);
                 } else {
 #pragma unroll
                     for (int j = 0; j < 32; j++) ys[j * YS_PITCH + q * 32 + lane] = __float2half_rn(fmaf(__uint_as_float(r[j]), sc, bs));
@@ -379,30 +458,45 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
 }
 
-int64_t spmm_workspace_bytes(int64_t M, int64_t K, int64_t N);            // spmm.cu
-int launch_spmm(const FwdArgs &a, const float **o_out, int *mp_out);
+int launch_transpose_x(const __half *x, __half *xt, int M, int K, int Mp, cudaStream_t stream);   // transpose.cu
 
-// what the sparse pre-pass needs (the forward refuses less when the ortho term is active) ...
-int64_t prefill_min_workspace_bytes(int64_t M, int64_t K, int64_t N) { return spmm_workspace_bytes(M, K, N); }
+// workspace layout: [ Xt : K * Mp halves, Mp = M rounded up to 256 ][ split-K partial tiles + flags ]
+static int64_t prefill_mp(int64_t M) { return ceil_div(M, pf::TM) * pf::TM; }
+static int64_t prefill_xt_bytes(int64_t M, int64_t K) { return ((K * prefill_mp(M) * 2 + 255) / 256) * 256; }
+// what the sparse term needs (the forward refuses less when the ortho term is active) ...
+int64_t prefill_min_workspace_bytes(int64_t M, int64_t K, int64_t N) { (void)N; return prefill_xt_bytes(M, K); }
 // ... and what ortho_b200_workspace_bytes() reports: room behind it for the split-K partial tiles, which the
 // forward uses when it is there (also for base-only calls) and does without otherwise
 int64_t prefill_workspace_bytes(int64_t M, int64_t K, int64_t N)
 {
-    return ((spmm_workspace_bytes(M, K, N) + 255) / 256) * 256 + (int64_t)pf::kSplitBytes;
+    (void)N;
+    return prefill_xt_bytes(M, K) + (int64_t)pf::kSplitBytes;
 }
 
 int launch_prefill(const FwdArgs &a)
 {
     using namespace pf;
     Params p;
-    p.row_ptr = nullptr; p.o = nullptr; p.Mp = 0; p.alpha = a.alpha; p.has_ortho = 0;
+    memset(&p, 0, sizeof(p));
+    p.alpha = a.alpha; p.has_ortho = 0; p.K = (int)a.K;
     if (a.has_ortho) {
-        // sparse term first (transpose + SpMM into the workspace), added in the tensor-core epilogue
-        if (ceil_div(a.M, 64) > 65535) return ORTHO_B200_ERR_SHAPE;
-        int st = launch_spmm(a, &p.o, &p.Mp);
+        // the activations are transposed once per forward (Xt[k][m]) so that one sparse entry touches a contiguous run
+        // of tokens; the sparse term itself is computed inside the tensor-core kernel
+        if (!a.workspace || a.workspace_bytes < prefill_xt_bytes(a.M, a.K)) return ORTHO_B200_ERR_WORKSPACE;
+        if (((uintptr_t)a.workspace & 255u) != 0) return ORTHO_B200_ERR_ALIGN;
+        const int Mp = (int)prefill_mp(a.M);
+        __half *xt = reinterpret_cast<__half *>(a.workspace);
+        const int st = launch_transpose_x(a.x, xt, (int)a.M, (int)a.K, Mp, a.stream);
         if (st != ORTHO_B200_OK) return st;
-        p.row_ptr = a.ortho.row_ptr;
+        p.ov = a.ortho; p.xt = xt; p.Mp = Mp;
         p.has_ortho = 1;
+        if (a.plan && a.ortho.entries && a.plan->n_long > 0) {
+            const int64_t lr = long_rows_workspace_bytes(a.plan, a.M);
+            if (a.workspace_bytes < prefill_xt_bytes(a.M, a.K) + lr) return ORTHO_B200_ERR_WORKSPACE;
+            const int st2 = launch_long_rows(a, xt, Mp, reinterpret_cast<unsigned char *>(a.workspace) + prefill_xt_bytes(a.M, a.K), &p.ol);
+            if (st2 != ORTHO_B200_OK) return st2;
+            p.hrow = a.plan->hrow; p.n_long = (int)a.plan->n_long; p.heavy = a.plan->heavy;
+        }
     }
     CUtensorMap xmap, wmap;
     if (!make_tensor_map_2d(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.x, (uint64_t)a.M, (uint64_t)a.K,
@@ -416,7 +510,6 @@ int launch_prefill(const FwdArgs &a)
     p.status = kernel_status_word();
     if (!p.status) return ORTHO_B200_ERR_CUDA;
     p.gather = 0;
-    memset(&p.gv, 0, sizeof(p.gv));
     if (a.gv && a.gv->world > 1) {
         p.gv = *a.gv;
         p.gather = 1;
@@ -436,8 +529,7 @@ int launch_prefill(const FwdArgs &a)
         const int T = p.tiles_n * p.tiles_m;
         const int G = T < num_sms ? T : num_sms;
         const int L = T % G == 0 ? (T < num_sms ? T : 0) : T % G;       // tiles of the last wave
-        const int64_t nv = (a.has_ortho && a.plan && a.ortho.entries) ? a.plan->n_virtual : 0;
-        const int64_t off = a.has_ortho ? ((spmm_workspace_bytes(a.M, a.K, a.N + nv) + 255) / 256) * 256 : 0;
+        const int64_t off = a.has_ortho ? prefill_xt_bytes(a.M, a.K) + (p.n_long > 0 ? long_rows_workspace_bytes(a.plan, a.M) : 0) : 0;
         p.full_tiles = T; p.n_split = 0; p.kh = 0; p.part = nullptr; p.flags = nullptr;
         const int kh = (p.kblocks / 2 / WKB) * WKB;
         if (L > 0 && 2 * L <= num_sms && L <= kMaxSplit && kh >= WKB && a.workspace &&
