@@ -419,11 +419,14 @@ def run_ours(args):
     h2d = sum(hx[K].numel() * 2 for (K, N) in shapes)
     d2h = sum(hy[kn].numel() * 2 for kn in shapes)
 
+    xdev = {K: torch.empty_like(xs[(K, 1)]) for (K, N) in shapes}
+
     def e2e_step(c):
         for kn in shapes:
-            xd = hx[kn[0]].to(dev, non_blocking=True)
+            xd = xdev[kn[0]]
+            xd.copy_(hx[kn[0]], non_blocking=True)        # this step's input, from pinned host memory
             y = mods[c][kn](xd)
-            hy[kn].copy_(y, non_blocking=True)
+            hy[kn].copy_(y, non_blocking=True)              # and its result back to the host
         torch.cuda.current_stream().synchronize()
 
     for i in range(max(3, n_copies)):       # touches every weight copy once: plans are built on first use
@@ -814,6 +817,33 @@ def run_sharded_report(args):
         os._exit(0)
 
 
+def run_one(args):
+    """``--one KxNxM``: a few forwards of one layer through the C ABI, nothing else (what the ncu summaries under
+    ``profiles/`` capture).  ``--density``, ``--alpha``, ``--zipf`` pick the ortho part."""
+    import torch
+    from libortho_b200 import _C_ops, _lib
+    import workloads as wl
+    K, N, M = [int(v) for v in args.one.lower().split("x")]
+    dev = torch.device("cuda", 0)
+    mk = wl.make_zipf_layer if args.zipf else wl.make_layer
+    L = mk(K, N, args.density, seed=0, device=dev)
+    plan = _C_ops.Plan(L.row_ptr, L.col, L.vals, K, N)
+    x = wl.make_input(M, K, seed=M, device=dev)
+    y = torch.empty(M, N, dtype=torch.float16, device=dev)
+    ws = torch.empty(max(256, _C_ops.workspace_bytes(M, K, N, plan)), dtype=torch.uint8, device=dev)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.repeat + 1)]
+    ev[0].record()
+    for i in range(args.repeat):
+        _C_ops.forward(L.base_weight, L.base_scales, L.vals, L.col, L.row_ptr, x, y, args.alpha, plan=plan, workspace=ws)
+        ev[i + 1].record()
+    torch.cuda.synchronize()
+    us = [ev[i].elapsed_time(ev[i + 1]) * 1e3 for i in range(args.repeat)]
+    print(json.dumps({"one": args.one, "alpha": args.alpha, "density": args.density, "zipf": bool(args.zipf), "nnz": L.nnz,
+                      "us_per_forward": [round(u, 1) for u in us], "algorithmic_bytes": L.algorithmic_bytes(M, args.alpha),
+                      "algorithmic_flops": L.algorithmic_flops(M, args.alpha),
+                      "kernel_status": int(_lib.lib().ortho_b200_query_kernel_status())}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -827,12 +857,19 @@ def main():
                     help="multi-GPU output exchange: peer stores from the kernels, or an NCCL all-gather")
     ap.add_argument("--no-deferred", action="store_true",
                     help="peer exchange: every forward waits for its own exchange instead of the next one waiting for it")
+    ap.add_argument("--one", default=None, metavar="KxNxM", help="run a few forwards of one layer and exit (for profiling)")
+    ap.add_argument("--density", type=float, default=0.003)
+    ap.add_argument("--alpha", type=float, default=1.0)
+    ap.add_argument("--zipf", action="store_true", help="--one: Zipf(1.2) row loads instead of uniform positions")
+    ap.add_argument("--repeat", type=int, default=4)
     ap.add_argument("--report", default=None, metavar="PATH",
                     help="instead of the benchmark line: time every configuration on one GPU and write a markdown table")
     ap.add_argument("--sharded-report", default=None, metavar="PATH",
                     help="under torch.distributed.run: time the 70B-style layers sharded over the job's ranks, write a table")
     args = ap.parse_args()
-    if args.sharded_report:
+    if args.one:
+        run_one(args)
+    elif args.sharded_report:
         run_sharded_report(args)
     elif args.report:
         run_report(args)

@@ -104,12 +104,19 @@ ORTHO_B200_API int ortho_b200_dequant_dump(const void *q_weight, const void *q_s
  * torch_bind/ortho_linear.py:142-151); same argument order and meaning, plus explicit sizes,
  * the optional plan, a caller-owned workspace and the stream.
  *
- *   M <= 24  : memory-bound streaming kernels (ORTHO_B200_DECODE_MAX_M is the most they accept);
- *              also M <= 32 with N <= 4096 and M <= 64 with N <= 1024 while N * K <= 4096 * 8192 (too few
- *              128-row tiles to fill the GPU).
- *   larger M : tcgen05 / TMEM tensor-core kernel.
- * Either regime needs ortho_b200_workspace_bytes(M, K, N) bytes of caller-owned workspace when the
- * ortho term is active (alpha > 0 and nnz > 0), none otherwise.
+ *   M <= 24   : memory-bound streaming kernels (ORTHO_B200_DECODE_MAX_M is the most they accept);
+ *               also M <= 32 with N <= 4096 and M <= 64 with N <= 1024 while N * K <= 4096 * 8192 (too few
+ *               row tiles to fill the GPU with a tensor-core kernel).  No global scratch.
+ *   25 .. 128 : tcgen05 kernel with the token block as the MMA's M operand (256 weight rows per instruction),
+ *               taken when the call brings ortho_b200_workspace_bytes(M, K, N) bytes of workspace, whatever alpha
+ *               is; without it the call runs the kernel of the neighbouring regime.
+ *   larger M  : tcgen05 / TMEM prefill kernel (weight tile as the M operand).  With an active ortho term
+ *               (alpha > 0 and nnz > 0) it needs the workspace (transposed activations; with a plan, the sums of
+ *               its long rows) and returns ERR_WORKSPACE without; otherwise the workspace is optional (split-K
+ *               of the last wave).
+ * Size the workspace with ortho_b200_workspace_bytes / ortho_b200_plan_workspace_bytes and pass it, 256-byte
+ * aligned, whenever that is not 0.  The first forward of a kernel variant on a device sets function attributes:
+ * issue it outside any stream capture.
  * plan may be NULL: the kernels then read the CSR arrays directly.  With a plan the CSR
  * pointers may be NULL.  alpha <= 0 or nnz == 0 skips the sparse stream entirely, so the output
  * is bit-identical to the base-only result (src/ortho.c:343 and the reference null test,
@@ -119,8 +126,8 @@ ORTHO_B200_API int ortho_b200_dequant_dump(const void *q_weight, const void *q_s
 #define ORTHO_B200_DECODE_MAX_M 64
 
 ORTHO_B200_API int64_t ortho_b200_workspace_bytes(int64_t M, int64_t K, int64_t N);
-/* Workspace for forwards that pass this plan (its long rows are split into extra output slots, so it
- * needs slightly more than the plan-less bound); 0 in the decode regime or for an empty plan. */
+/* Workspace for forwards that pass this plan (the prefill regime keeps the pre-pass sums of the plan's long rows
+ * there, so it may need more than the plan-less bound); 0 for the streaming kernels or for an empty plan. */
 ORTHO_B200_API int64_t ortho_b200_plan_workspace_bytes(const ortho_b200_plan *plan, int64_t M);
 
 ORTHO_B200_API int ortho_b200_forward(const void *q_weight, const void *q_scales_f16,
@@ -173,21 +180,22 @@ ORTHO_B200_API int ortho_b200_forward_multi(const ortho_b200_layer_desc *layers,
  * Who needs it: code that runs where cudaMalloc must not be called -- a host application that owns
  * the allocator and hands a plugin only tensors, a serving loop whose memory was fixed at start-up,
  * or a section that is about to be recorded into a CUDA graph.  ortho_b200_forward asks such a
- * caller for a workspace when M > ORTHO_B200_DECODE_MAX_M and the sparse term is active, and a
- * plan has to be allocated too.  This entry point takes neither: it reads the CSR arrays directly
- * and keeps the scratch (transposed activations + FP32 sparse term) in a fixed array of
+ * caller for a workspace in the tensor-core regimes, and a plan has to be allocated too.  This entry
+ * point takes neither: it reads the CSR arrays directly and keeps the scratch in a fixed array of
  * ORTHO_B200_STATIC_SCRATCH_BYTES that is part of the library image.  Every GPU that loads the
- * library holds that array until the process exits.
+ * library holds that array until the process exits.  It picks the kernel exactly as ortho_b200_forward
+ * does when given a workspace of that size, so both entries produce the same bits.
  *
  * Limits and rules:
- *  - if ortho_b200_workspace_bytes(M, K, N) exceeds ORTHO_B200_STATIC_SCRATCH_BYTES the call returns
- *    ORTHO_B200_ERR_SCRATCH_LIMIT and launches nothing (alpha <= 0 or nnz == 0 need no scratch and are
- *    never rejected for size);
+ *  - the one case it refuses (ORTHO_B200_ERR_SCRATCH_LIMIT, nothing launched) is a prefill-regime call
+ *    with an active ortho term whose transposed activations, K * roundup(M, 256) * 2 bytes, exceed
+ *    ORTHO_B200_STATIC_SCRATCH_BYTES; alpha <= 0, nnz == 0 and the streaming regime need no scratch;
  *  - the first call on a device looks up the array's device address (cudaGetSymbolAddress, no
  *    allocation); make that first call before any stream capture begins;
  *  - all calls share the one array and it keeps the previous call's contents.  Nothing in it needs
- *    clearing (each call writes every byte it later reads), but calls that overlap on the GPU --
- *    other streams, other host threads -- race on it: issue them one after another on one stream;
+ *    clearing by the caller (each call writes what it later reads; the flag words of split tiles are
+ *    cleared on the stream by the call itself), but calls that overlap on the GPU -- other streams,
+ *    other host threads -- race on it: issue them one after another on one stream;
  *  - no cudaMalloc / cudaFree or any other allocating call is made.
  * Arguments as for ortho_b200_forward, without plan and workspace.
  * ------------------------------------------------------------------------------------------- */

@@ -25,6 +25,15 @@ from . import _C_ops as _C
 from . import _lib
 from .sieve import pack_ortho_sparse
 
+# raw handle of the current stream without building a torch.cuda.Stream object per call
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
+def _current_stream_handle(dev: torch.device) -> int:
+    if _raw_stream is not None:
+        return _raw_stream(dev.index)
+    return torch.cuda.current_stream(dev).cuda_stream
+
 _ORTHO_BUFFERS = ("ortho_values", "ortho_col_indices", "ortho_row_ptr")
 _WATCHED = frozenset(("base_weight", "base_scales", "bias") + _ORTHO_BUFFERS)
 
@@ -253,14 +262,13 @@ class OrthoLinear(nn.Module):
             d.y_f16 = output.data_ptr()
             d.alpha = alpha
             fused_bias = b.fused_bias
-            lib = _lib.lib()
+            fwd = _lib.lib().ortho_b200_forward_multi
             if torch.cuda.current_device() == dev.index:
-                st = lib.ortho_b200_forward_multi(b.descs, 1, x_flat.data_ptr(), M, self.in_features, b.ws_ptr, b.ws_bytes,
-                                                  torch.cuda.current_stream(dev).cuda_stream)
+                st = fwd(b.descs, 1, x_flat.data_ptr(), M, self.in_features, b.ws_ptr, b.ws_bytes, _current_stream_handle(dev))
             else:
                 with torch.cuda.device(dev):
-                    st = lib.ortho_b200_forward_multi(b.descs, 1, x_flat.data_ptr(), M, self.in_features, b.ws_ptr,
-                                                      b.ws_bytes, torch.cuda.current_stream(dev).cuda_stream)
+                    st = fwd(b.descs, 1, x_flat.data_ptr(), M, self.in_features, b.ws_ptr, b.ws_bytes,
+                             _current_stream_handle(dev))
             if st:
                 _lib.check(st, "ortho_b200_forward_multi")
         if self.bias is not None and not fused_bias:

@@ -1,6 +1,7 @@
 """Worker of the two-GPU peer-gather test (launched by torch.distributed.run, one rank per GPU)."""
 import os
 import sys
+import time
 
 import torch
 import torch.distributed as dist
@@ -45,8 +46,12 @@ def main():
             ya = sh(xa)                           # region 0
             yb = sh(xb)                           # region 1; its kernel waits for ya's exchange
             sh._comm.wait()                       # yb's exchange
+            # every reader of a region must be ordered before this rank's next forward on the comm (which lets the
+            # peers store into it again): take copies now, compare afterwards
+            ya, yb = ya.clone(), yb.clone()
             ra, rb = full(xa), full(xb)
             torch.cuda.synchronize()
+            dist.barrier()
             assert _lib.lib().ortho_b200_query_kernel_status() == 0, "a deferred gather wait timed out"
             for y, ref in ((ya, ra), (yb, rb)):
                 d = (y.float() - ref.float()).abs().max().item()
@@ -54,6 +59,50 @@ def main():
                 assert d <= 2e-2 and rel <= 1e-3, f"rank {rank}: deferred K={K} N={N} M={M} it={it}: max_abs={d} rel={rel}"
         sh._comm.set_deferred(False)
         dist.barrier()
+    # A peer that does not show up: rank 1 withholds one forward, so the wait of rank 0's kernel for rank 1's flag
+    # must run out after the comm's timeout and leave a status for the host, with the context still usable.
+    # Nothing faults or hangs: the kernel polls a flag nobody sets, against a clock.  Rank 1 then issues the withheld
+    # call (rank 0's flag of that epoch is already there), the epochs are level again and the next exchange works.
+    K, N, M = 1024, 1056, 4
+    layer = wl.make_layer(K, N, 0.01, seed=77).to(dev)
+    full = OrthoLinear(K, N, device=dev)
+    full.base_weight, full.base_scales = layer.base_weight, layer.base_scales
+    full.ortho_row_ptr, full.ortho_col_indices, full.ortho_values = layer.row_ptr, layer.col, layer.vals
+    sh = ShardedOrthoLinear.from_full(full)
+    sh.enable_peer_gather(M)
+    x = wl.make_input(M, K, seed=401).to(dev)
+    y = sh(x)
+    torch.cuda.synchronize()
+    assert _lib.lib().ortho_b200_query_kernel_status() == 0
+    dist.barrier()
+    sh._comm.set_timeout_ms(50)
+    if rank == 0:
+        t0 = time.perf_counter()
+        sh(x)
+        torch.cuda.synchronize()
+        waited = time.perf_counter() - t0
+        st = _lib.lib().ortho_b200_query_kernel_status()
+        assert st == 8, f"rank 0: expected the bounded wait to run out (status 8), got {st}"
+        assert 0.03 < waited < 5.0, waited
+        try:
+            _lib.check(st, "forward_gather")
+            raise AssertionError("a kernel status must surface as an exception")
+        except _lib.OrthoB200Error as e:
+            assert "bounded wait" in str(e)
+        assert _lib.lib().ortho_b200_query_kernel_status() == 0      # reading the status clears it
+    dist.barrier()
+    if rank == 1:
+        sh(x)                                      # the withheld call: rank 0's flag of this epoch is already set
+        torch.cuda.synchronize()
+        assert _lib.lib().ortho_b200_query_kernel_status() == 0
+    dist.barrier()
+    sh._comm.set_timeout_ms(2000)
+    x2 = wl.make_input(M, K, seed=402).to(dev)
+    y2, ref2 = sh(x2), full(x2)
+    torch.cuda.synchronize()
+    assert _lib.lib().ortho_b200_query_kernel_status() == 0, "the exchange after the timed-out one must work"
+    assert (y2.float() - ref2.float()).abs().max().item() <= 2e-2
+    dist.barrier()
     torch.cuda.synchronize()
     open(os.path.join(sys.argv[1], f"ok{rank}"), "w").write("ok")
     dist.barrier()

@@ -150,3 +150,13 @@ def test_swap_linear_replaces_modules_and_keeps_bias():
     toy.up._bound[1] = object()
     toy.up.base_scales = toy.up.base_scales.clone()
     assert toy.up._bound == {}
+
+
+def test_kernel_status_surfaces_as_runtime_error():
+    """Host side of the failure path: a non-zero status (here: a bounded device-side wait that ran out) becomes a
+    RuntimeError that names the cause; no GPU is involved."""
+    with pytest.raises(RuntimeError, match="bounded wait"):
+        _lib.check(8, "ortho_b200_forward_gather")
+    with pytest.raises(_lib.OrthoB200Error, match="workspace"):
+        _lib.check(5, "ortho_b200_forward")
+    _lib.check(0, "ok")
