@@ -78,3 +78,20 @@ def test_two_ranks_exchange_through_peer_memory(tmp_path):
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     for rank in (0, 1):
         assert (tmp_path / f"ok{rank}").exists(), r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_second_device_in_the_same_process(oracle_mod):
+    """Function attributes, SM counts and occupancy caches are kept per device: a process that has run every kernel
+    family on cuda:0 runs them on cuda:1 as well (streaming, generic decode, tokens-as-M, prefill)."""
+    for dev in ("cuda:0", "cuda:1"):
+        for (M, K, N) in [(1, 4096, 512), (20, 1024, 208), (40, 1024, 4352), (300, 1024, 520)]:
+            layer = wl.make_layer(K, N, 0.01, seed=500 + M)
+            x = wl.make_input(M, K, seed=500 + M)
+            m = layer.to(dev).to_module()
+            y = m(x.to(dev))
+            torch.cuda.synchronize(dev)
+            with torch.cuda.device(dev):
+                from libortho_b200 import _lib
+                assert _lib.lib().ortho_b200_query_kernel_status() == 0
+            assert_close(y.float().cpu().numpy(), layer_oracle(oracle_mod, layer, x, 1.0), f"{dev} M={M}")
