@@ -129,30 +129,6 @@ __device__ __forceinline__ void int4x8_to_half2x4(uint32_t w, uint32_t (&h)[4]) 
     h[3] = *reinterpret_cast<uint32_t *>(&r3);
 }
 
-// The streaming decode kernel's variant: the same pair order, but the high-nibble pairs (e1,e5) and (e3,e7) --
-// the odd elements -- keep an offset of +72: OR-ing the exponent pattern 0x5400 (= 64.0) under a nibble in bits
-// 4-7 yields 64 + (s + 8) exactly, with no arithmetic at all (7 instead of 9 instructions per 8 weights in a
-// kernel that is bound by instruction issue).  The contraction then carries 72 * sum over the odd k of x[k], which
-// does not depend on the output row: the kernel computes that sum once per token when it stages the activations
-// and takes it off the partial sums (kOddOffset).  Everything stays exact small-integer FP16; the FP32
-// accumulation sees magnitudes a few times larger than the result, far inside its precision.
-constexpr float kOddOffset = 72.f;
-__device__ __forceinline__ void int4x8_to_half2x4_odd72(uint32_t w, uint32_t (&h)[4]) {
-    const uint32_t kLoMask = 0x000F000Fu, kHiMask = 0x00F000F0u;
-    const uint32_t kLoMagic = 0x64086408u;   // 1024 | sign flip of a low nibble
-    const uint32_t kHiMagic = 0x54805480u;   // 64   | sign flip of a high nibble
-    const __half2 kSubLo = __half2half2(__ushort_as_half((unsigned short)0x6408));   // 1032
-    const uint32_t w8 = w >> 8;
-    uint32_t a0 = lop3_and_xor(w, kLoMask, kLoMagic);
-    uint32_t a2 = lop3_and_xor(w8, kLoMask, kLoMagic);
-    const __half2 r0 = __hsub2(*reinterpret_cast<__half2 *>(&a0), kSubLo);
-    const __half2 r2 = __hsub2(*reinterpret_cast<__half2 *>(&a2), kSubLo);
-    h[0] = *reinterpret_cast<const uint32_t *>(&r0);
-    h[1] = lop3_and_xor(w, kHiMask, kHiMagic);        // (e1 + 72, e5 + 72)
-    h[2] = *reinterpret_cast<const uint32_t *>(&r2);
-    h[3] = lop3_and_xor(w8, kHiMask, kHiMagic);       // (e3 + 72, e7 + 72)
-}
-
 // natural element order variant: pairs (e0,e1) (e2,e3) (e4,e5) (e6,e7).  A byte holds the pair
 // (low nibble = even element).  prmt replicates byte i into both 16-bit halves under the 0x64
 // exponent byte, the mask keeps bits 0-3 in the low half and bits 4-7 (now bits 20-23) in the high

@@ -130,8 +130,6 @@ decode_stream_kernel(const __grid_constant__ StreamMaps maps, const StreamParams
     float *red = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(bars) + (((kWarps * p.stages + 1) * 8 + 127) & ~127));
     float *osm = red + p.red_bufs * kWarps * 16 * MV;                             // [2][16*MV]
     unsigned char *xs = base + (size_t)NG * region;                               // M * pitch
-    float *corr = reinterpret_cast<float *>(xs + (size_t)M * p.pitch);            // [16] per token: 72 * sum over the odd k of
-                                                                                  // this CTA's K range of x[m][k]
 
     // ---- this warp's share of the K range, in boxes of 256 weights -----------------------------
     const int cb0 = (p.nboxes * rank) / S, cb1 = (p.nboxes * (rank + 1)) / S;
@@ -233,26 +231,6 @@ decode_stream_kernel(const __grid_constant__ StreamMaps maps, const StreamParams
     }
     __syncthreads();
     griddep_launch();
-    // the offset the unpack leaves on the odd elements: one warp per token sums them from the staged slab (in a
-    // staged 16-byte chunk (x0,x4,x1,x5,x2,x6,x3,x7) the odd elements are the second and the fourth word)
-    {
-        const int chunks_per_row = (cb1 - cb0) * (kBoxK / 8);
-        for (int m = (int)(threadIdx.x >> 5); m < M; m += NG * kWarps) {
-            float sum = 0.f;
-            const unsigned char *row = xs + (size_t)m * p.pitch;
-            for (int q = lane; q < chunks_per_row; q += 32) {
-                const uint4 v = *reinterpret_cast<const uint4 *>(row + (size_t)q * 16);
-                const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&v.y));
-                const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&v.w));
-                sum += (a.x + a.y) + (b.x + b.y);
-            }
-#pragma unroll
-            for (int o2 = 16; o2 >= 1; o2 >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o2);
-            if (lane == 0) corr[m] = kOddOffset * sum;
-        }
-    }
-    __syncthreads();
-
     // A box is laid out [row][column block][128 B]; the 128-byte swizzle XORs the 16-byte chunk index
     // with bits 7..9 of the shared-memory address, i.e. with (row * kKbx + block) & 7.  mma row g is
     // mapped to box row rho(g) = g with bits 0 and 1 swapped, so that the two rows met in one
@@ -370,8 +348,8 @@ decode_stream_kernel(const __grid_constant__ StreamMaps maps, const StreamParams
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
                     uint32_t ha[4], hb[4];
-                    int4x8_to_half2x4_odd72(wwa[j], ha);     // odd elements carry +72, taken off below through corr[]
-                    int4x8_to_half2x4_odd72(wwb[j], hb);
+                    int4x8_to_half2x4(wwa[j], ha);
+                    int4x8_to_half2x4(wwb[j], hb);
                     const uint32_t A0[4] = {ha[0], hb[0], ha[1], hb[1]};
                     const uint32_t A1[4] = {ha[2], hb[2], ha[3], hb[3]};
 #pragma unroll
@@ -433,10 +411,8 @@ decode_stream_kernel(const __grid_constant__ StreamMaps maps, const StreamParams
                 for (int q = 0; q < 2; q++) {
                     const int col = 8 * mt + 2 * t + q;
                     if (col < MV) {
-                        // warp 0 takes this CTA's whole offset off its own partial sums (the same for every row)
-                        const float off = (warp == 0 && col < M) ? corr[col] : 0.f;
-                        mine[brow0 * MV + col] = (acc[0][mt][q] + acc[1][mt][q]) - off;
-                        mine[brow1 * MV + col] = (acc[0][mt][2 + q] + acc[1][mt][2 + q]) - off;
+                        mine[brow0 * MV + col] = acc[0][mt][q] + acc[1][mt][q];
+                        mine[brow1 * MV + col] = acc[0][mt][2 + q] + acc[1][mt][2 + q];
                     }
                 }
             }
@@ -478,8 +454,7 @@ static size_t stream_smem_bytes(int MV, int kbx, int64_t M, int boxes_per_cta, i
 {
     const size_t region = ((size_t)kWarps * stages * (16 * kbx * 128) + (((kWarps * stages + 1) * 8 + 127) & ~127) +
                            (size_t)red_bufs * kWarps * 16 * MV * 4 + (size_t)2 * 16 * MV * 4 + 1023) & ~(size_t)1023;
-    // alignment slack, the per-token offset sums (corr[16]), the warp groups' regions, the activation slab
-    return 1024 + 64 + (size_t)ng * region + (size_t)M * (boxes_per_cta * 512 * kbx + 64);
+    return 1024 + (size_t)ng * region + (size_t)M * (boxes_per_cta * 512 * kbx + 64);
 }
 
 // layers[0..nl): layers that share x, M, K and the stream (nl == 1 for the ordinary forward)

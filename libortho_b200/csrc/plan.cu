@@ -57,8 +57,8 @@ __global__ void plan_decode_dump_kernel(const uint32_t *__restrict__ entries, co
 }
 
 // every thread unpacks one 32-bit word (8 elements) with the forward kernels' own converters:
-// elements 0..7 come back from the pair-order converter; the natural-order converter of the tensor-core
-// kernels and the offset variant of the streaming kernel must agree with it, otherwise a poison value is written.
+// elements 0..7 come back from the pair-order converter, and the natural-order converter of the tensor-core
+// kernels must agree with it, otherwise a poison value is written.
 __global__ void dequant_dump_kernel(const uint32_t *__restrict__ w32, const __half *__restrict__ scales,
                                     int64_t N, int64_t K, int8_t *__restrict__ w_int, float *__restrict__ w_deq)
 {
@@ -67,10 +67,9 @@ __global__ void dequant_dump_kernel(const uint32_t *__restrict__ w32, const __ha
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t n = i / words_per_row;
         const uint32_t w = w32[i];
-        uint32_t hp[4], hn[4], ho[4];
+        uint32_t hp[4], hn[4];
         int4x8_to_half2x4(w, hp);
         int4x8_to_half2x4_natural(w, hn);
-        int4x8_to_half2x4_odd72(w, ho);
         float e[8];
 #pragma unroll
         for (int q = 0; q < 4; q++) {
@@ -83,12 +82,6 @@ __global__ void dequant_dump_kernel(const uint32_t *__restrict__ w32, const __ha
         for (int q = 0; q < 4; q++) {
             const __half2 pr = *reinterpret_cast<const __half2 *>(&hn[q]);
             agree = agree && (__low2float(pr) == e[2 * q]) && (__high2float(pr) == e[2 * q + 1]);
-        }
-#pragma unroll
-        for (int q = 0; q < 4; q++) {            // the offset variant: pairs (e_q, e_{q+4}), odd elements carry +72
-            const __half2 pr = *reinterpret_cast<const __half2 *>(&ho[q]);
-            const float off = (q & 1) ? kOddOffset : 0.f;
-            agree = agree && (__low2float(pr) - off == e[q]) && (__high2float(pr) - off == e[q + 4]);
         }
         const float s = __half2float(scales[n]);
 #pragma unroll
