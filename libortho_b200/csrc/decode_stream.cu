@@ -567,6 +567,15 @@ int launch_decode_stream_multi(const FwdArgs *layers, int nl, int cfg_s, int cfg
         // smallest cluster that does
         S = 1;
         while (S < 8 && stream_smem_bytes(MV, kbx, a.M, (int)ceil_div(nboxes, S), 2) > 200 * 1024) S *= 2;
+        // few row tiles (a narrow layer, or one GPU's shard of a layer): a warp group per tile would leave most of
+        // the GPU idle for a whole K sweep, so K is split over a larger cluster while that still gives every warp a
+        // box per tile and no more groups than can be resident (about two per SM)
+        {
+            int tiles = 0;
+            for (int l = 0; l < nl; l++) tiles += (int)ceil_div(layers[l].N, 16);
+            const int cap = 2 * device_sm_count(current_device_index());
+            while (S < 8 && tiles * S * 2 <= cap && nboxes / (S * 2) >= kWarps) S *= 2;
+        }
         // a large activation slab (8 or more tokens, or a long K) leaves room for one CTA per SM only;
         // two warp groups then share one slab when that needs no further split of K (a cluster costs a DSMEM
         // exchange per tile and makes every CTA walk the tile's sparse entries) and leaves each

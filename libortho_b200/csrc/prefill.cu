@@ -32,6 +32,8 @@
 //   warps 2-5    INT4 -> FP16 -> TMEM (one thread per output row of the tile)
 //   warps 6-13   sparse term, then epilogue (TMEM -> scale -> FP16 -> global): two sets of four warps that take
 //                alternate 32-token chunks
+//   warps 14-17  N-sharded layer only: copy each finished output tile from the local buffer to the peers' buffers
+//                (plain loads and stores over NVLink) while the next tile is being computed
 #include <cstring>
 
 #include "common.cuh"
@@ -61,7 +63,9 @@ constexpr int CONV_WARPS = 4 * NH;       // one converter thread per output row 
 constexpr int EPI_WARP0 = 2 + CONV_WARPS;
 constexpr int ESETS = 2;                 // epilogue warp sets per accumulator: set e drains the 32-token chunks c = e, e + 2, ...
 constexpr int EPI_WARPS = 4 * NH * ESETS;
-constexpr int NWARPS = EPI_WARP0 + EPI_WARPS;
+constexpr int PUSH_WARP0 = EPI_WARP0 + EPI_WARPS;
+constexpr int PUSH_WARPS = 4;            // N-sharded layer: copy every finished output tile to the peers while the next tile runs
+constexpr int NWARPS = PUSH_WARP0 + PUSH_WARPS;
 constexpr int TMEM_COLS = 512;
 constexpr int A_COL0 = NH * TM;          // accumulators occupy [0, NH*TM); converted weights follow
 constexpr int A_STAGE_COLS = NH * (KB / 2);
@@ -110,6 +114,7 @@ struct Smem {
     uint64_t w_full[WSTAGES], w_empty[WSTAGES];
     uint64_t a_full[ASTAGES], a_empty[ASTAGES];
     uint64_t d_full, d_empty;
+    uint64_t y_done;            // the epilogue warps have stored a tile to the local output (gathering forward)
     uint32_t tmem_base;
 };
 
@@ -136,6 +141,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         for (int s = 0; s < ASTAGES; s++) { mbar_init(&sm->a_full[s], CONV_WARPS); mbar_init(&sm->a_empty[s], 1); }
         mbar_init(&sm->d_full, 1);
         mbar_init(&sm->d_empty, EPI_WARPS);
+        mbar_init(&sm->y_done, EPI_WARPS);
         fence_mbar_init();
         prefetch_tensormap(&xmap);
         prefetch_tensormap(&wmap);
@@ -243,7 +249,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                 if (++as == ASTAGES) { as = 0; aph ^= 1u; }
             }
         }
-    } else {
+    } else if (warp < PUSH_WARP0) {
         // ================= epilogue: TMEM -> scale -> FP16 -> shared (transpose) -> global =================
         const int q = warp & 3;
         const int h = 0;                               // accumulator handled by this warp set (NH == 1)
@@ -252,6 +258,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         __half *ys = reinterpret_cast<__half *>(ys_base + eset * YS_BYTES);
         static_assert(NH == 1, "the epilogue warp sets are laid out for one accumulator");
         const bool vec_ok = (p.N % 8) == 0 && (p.ldy % 8) == 0 && (reinterpret_cast<uintptr_t>(p.y) & 15u) == 0;
+        // N-sharded layer: with 16-byte alignment the epilogue stores to the local buffer only (p.y) and the push warps
+        // copy the finished tile to the peers while the next tile is being computed; otherwise the epilogue stores to
+        // every rank itself
+        const bool push_split = p.gather && vec_ok;
         int it = 0;
         for (int u = blockIdx.x; u < nunits; u += gridDim.x, it++) {
             const Unit un = unit_of(p, u);
@@ -424,7 +434,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                     if (m < p.M && n0 < p.N) {
                         const __half *src = ys + tok * YS_PITCH + part * 8;
                         __half *dst = p.y + (size_t)m * (size_t)p.ldy + n0;
-                        if (!p.gather) {
+                        if (!p.gather || push_split) {
                             if (vec_ok) {
                                 *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(src);
                             } else {
@@ -447,6 +457,36 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm->d_empty);
+            if (push_split) {                          // this warp's share of the tile is in the local buffer
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sm->y_done);
+            }
+        }
+    } else if (warp >= PUSH_WARP0) {
+        // ================= push warps (gathering forward): local output tile -> every peer, over NVLink =================
+        // plain 16-byte loads (through L2) and stores; the tile of unit u travels while unit u + 1 is being computed
+        const bool vec_ok = (p.N % 8) == 0 && (p.ldy % 8) == 0 && (reinterpret_cast<uintptr_t>(p.y) & 15u) == 0;
+        if (p.gather && vec_ok) {
+            const int pt = (warp - PUSH_WARP0) * 32 + lane;       // 0..127
+            int done = 0;
+            for (int u = blockIdx.x; u < nunits; u += gridDim.x) {
+                const Unit un = unit_of(p, u);
+                if (un.role == 2) continue;                        // the second K half of a split tile writes no output
+                const int nt = un.t % p.tiles_n, mt = un.t / p.tiles_n;
+                wait(&sm->y_done, (uint32_t)(done & 1));
+                done++;
+                const int n0 = nt * TN + (pt & 15) * 8;
+                if (n0 >= p.N) continue;
+                for (int r0 = 0; r0 < TM; r0 += PUSH_WARPS * 2) {
+                    const int m = mt * TM + r0 + (pt >> 4);
+                    if (m >= p.M) break;
+                    const size_t at = (size_t)m * (size_t)p.ldy + n0;
+                    const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(p.y + at));
+                    for (int r = 0; r < p.gv.world; r++)
+                        if (r != p.gv.rank) *reinterpret_cast<uint4 *>(p.gv.y[r] + at) = v;
+                }
+            }
         }
     }
 

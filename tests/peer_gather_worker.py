@@ -19,7 +19,7 @@ def main():
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
     dev = torch.device("cuda", torch.cuda.current_device())
     dist.init_process_group("nccl", device_id=dev)
-    cases = [(4096, 2048, 1), (1024, 1056, 16), (512, 528, 40), (256, 1024, 200), (2048, 96, 4)]
+    cases = [(4096, 2048, 1), (1024, 1056, 16), (512, 528, 40), (256, 1024, 200), (2048, 96, 4), (512, 1056, 300)]
     for K, N, M in cases:
         layer = wl.make_layer(K, N, 0.01, seed=K + N + M).to(dev)
         full = OrthoLinear(K, N, device=dev)
