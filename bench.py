@@ -14,7 +14,8 @@ distinct copies of the layers as it takes for a GPU's share to exceed the L2 sev
 ``value``    decode GB/s = algorithmic bytes of the step (whole layers) / device time (max over ranks),
              inputs resident in HBM, the step replayed as a CUDA graph, timed with CUDA events.
 ``e2e``      the same metric through ``OrthoLinear.forward`` / ``ShardedOrthoLinear.forward`` with host
-             buffers: per forward X comes from pinned host memory and Y goes back, inside the timed region.
+             buffers: every step copies its inputs from pinned host memory, runs the four forwards, copies the four
+             outputs back and synchronises the stream, all inside the timed region.
 ``roofline`` HBM roofline of the decode kernel from the same timed region (per GPU).
 ``cpu_baseline`` the reference's own CPU forward timed on this host (N=1 only).
 ``regimes``  (extra, every N) the same four layers at M=32 (GB/s) and M=4096 (TFLOP/s) with the exchange
@@ -43,9 +44,9 @@ WORKLOAD = ("70B-style decode: (8192->10240, 8192->8192, 8192->57344, 28672->819
 L2_BYTES = 126 << 20
 
 # DRAM bytes moved per algorithmic byte by the streaming decode kernel, from an ncu capture of one launch
-# (dram__bytes_read.sum + dram__bytes_write.sum = 47.15 MB for the 47.98 MB 4096->22016 M=1 launch); the
+# (dram__bytes_read.sum + dram__bytes_write.sum = 245.2 MB for the 243.8 MB 8192->57344 M=1 launch); the
 # kernel reads every weight byte once, so traffic grows in proportion to the algorithmic bytes
-NCU_TRAFFIC_RATIO = 47.15 / 47.98
+NCU_TRAFFIC_RATIO = 245.2 / 243.8
 
 
 def peaks():
@@ -416,17 +417,17 @@ def run_ours(args):
         mods.append(d)
     hx = {K: xs[(K, 1)].cpu().pin_memory() for (K, N) in shapes}
     hy = {kn: torch.empty(1, kn[1], dtype=torch.float16).pin_memory() for kn in shapes}
-    h2d = sum(hx[K].numel() * 2 for (K, N) in shapes)
+    h2d = sum(hx[K].numel() * 2 for K in hx)
     d2h = sum(hy[kn].numel() * 2 for kn in shapes)
 
     xdev = {K: torch.empty_like(xs[(K, 1)]) for (K, N) in shapes}
 
     def e2e_step(c):
-        for kn in shapes:
-            xd = xdev[kn[0]]
-            xd.copy_(hx[kn[0]], non_blocking=True)        # this step's input, from pinned host memory
-            y = mods[c][kn](xd)
-            hy[kn].copy_(y, non_blocking=True)              # and its result back to the host
+        for K in xdev:                                      # this step's inputs, from pinned host memory
+            xdev[K].copy_(hx[K], non_blocking=True)
+        out = [(kn, mods[c][kn](xdev[kn[0]])) for kn in shapes]
+        for kn, y in out:                                   # and its results back to the host
+            hy[kn].copy_(y, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     for i in range(max(3, n_copies)):       # touches every weight copy once: plans are built on first use
@@ -499,12 +500,12 @@ def run_ours(args):
             "clocks": clocks,
             "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "api": ("ShardedOrthoLinear.forward" if world > 1 else "OrthoLinear.forward") +
-                                               ", pinned host X in, Y out, per forward"},
+                                               ", per step: pinned host X in, four forwards, Y out, one stream sync"},
             "gpu_launches": int(launches_per_step * args.steps + e2e_launches),
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": pk["hbm_gbs"], "unit": "GB/s",
                          "frac": per_gpu / pk["hbm_gbs"],
                          "traffic": NCU_TRAFFIC_RATIO * step_bytes / len(shapes) / world,
-                         "traffic_source": "ncu capture of one launch of this kernel (DRAM bytes / algorithmic bytes = 0.983), scaled by algorithmic bytes",
+                         "traffic_source": "ncu capture of one launch of this kernel (DRAM bytes / algorithmic bytes = 1.006), scaled by algorithmic bytes",
                          "peak_source": pk["source"], "kernel": "ob::decode_stream_kernel",
                          "launches_per_step": launches_per_step,
                          "algorithmic_bytes_per_launch": step_bytes / len(shapes) / world},
@@ -818,8 +819,8 @@ def run_sharded_report(args):
 
 
 def run_one(args):
-    """``--one KxNxM``: a few forwards of one layer through the C ABI, nothing else (what the ncu summaries under
-    ``profiles/`` capture).  ``--density``, ``--alpha``, ``--zipf`` pick the ortho part."""
+    """``--one KxNxM``: a few forwards of one layer through the C ABI and nothing else, for profiler captures of a
+    single kernel.  ``--density``, ``--alpha``, ``--zipf`` pick the ortho part."""
     import torch
     from libortho_b200 import _C_ops, _lib
     import workloads as wl
