@@ -12,7 +12,7 @@ its output slice into every rank's peer-mapped buffer (``--exchange nccl``: an N
 distinct copies of the layers as it takes for a GPU's share to exceed the L2 several times.
 
 ``value``    decode GB/s = algorithmic bytes of the step (whole layers) / device time (max over ranks),
-             inputs resident in HBM, the step replayed as a CUDA graph, timed with CUDA events.
+             inputs resident in HBM, the steps replayed as CUDA graphs (up to --steps-per-graph steps each), timed with CUDA events.
 ``e2e``      the same metric through ``OrthoLinear.forward`` / ``ShardedOrthoLinear.forward`` with host
              buffers: every step copies its inputs from pinned host memory, runs the four forwards, copies the four
              outputs back and synchronises the stream, all inside the timed region.
@@ -306,11 +306,14 @@ def run_ours(args):
             return ys[(M, "g")][kn]
         return y
 
-    def run_step(c):
-        for kn in shapes:
-            forward(c, kn, 1)
+    def run_steps(first, count):
+        """`count` consecutive steps (step i works on weight copy i % n_copies).  With the deferred peer exchange every
+        forward waits for its predecessor's flags, so only the last forward of the sequence needs an explicit wait."""
+        for i in range(first, first + count):
+            for kn in shapes:
+                forward(i % n_copies, kn, 1)
         if exchange == "peer":
-            comm.wait()          # deferred mode: every forward waited for its predecessor's exchange; this is the last one's
+            comm.wait()
 
     for M in wl.CFG3_M:
         out_buffers(M)
@@ -319,19 +322,24 @@ def run_ours(args):
     if exchange == "peer":
         comm.set_deferred(not args.no_deferred)
 
-    # ---- headline: one CUDA graph per weight copy, K timed steps -------------------------------------------
-    graphs = []
-    launches_per_step = 0
+    # ---- headline: the K timed steps are captured as CUDA graphs of up to `chunk` steps each --------------------
+    chunk = max(1, min(args.steps, args.steps_per_graph))
+    n_chunks, rem = divmod(args.steps, chunk)
+
+    def capture(first, count):
+        g = torch.cuda.CUDAGraph()
+        l0 = lib.ortho_b200_launch_count()
+        with torch.cuda.graph(g, stream=stream):
+            run_steps(first, count)
+        return g, lib.ortho_b200_launch_count() - l0
+
     with torch.cuda.stream(stream):
-        run_step(0)
+        run_steps(0, 1)                  # first call of every kernel variant happens outside a capture
         stream.synchronize()
-        for c in range(n_copies):
-            g = torch.cuda.CUDAGraph()
-            l0 = lib.ortho_b200_launch_count()
-            with torch.cuda.graph(g, stream=stream):
-                run_step(c)
-            launches_per_step = lib.ortho_b200_launch_count() - l0
-            graphs.append(g)
+        g_chunk, l_chunk = capture(0, chunk)
+        g_rem, l_rem = capture(n_chunks * chunk, rem) if rem else (None, 0)
+    timed_launches = n_chunks * l_chunk + l_rem
+    launches_per_step = timed_launches / args.steps
 
     def barrier():
         if world > 1:
@@ -340,14 +348,16 @@ def run_ours(args):
 
     warm = max(3, args.warmup)
     with torch.cuda.stream(stream):
-        for i in range(warm):
-            graphs[i % n_copies].replay()
+        for i in range(-(-warm // chunk)):
+            g_chunk.replay()
         barrier()
         sampler = ClockSampler(local) if rank == 0 else None
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record(stream)
-        for i in range(args.steps):
-            graphs[i % n_copies].replay()
+        for i in range(n_chunks):
+            g_chunk.replay()
+        if g_rem is not None:
+            g_rem.replay()
         ev1.record(stream)
         barrier()
         ms = ev0.elapsed_time(ev1)
@@ -362,7 +372,7 @@ def run_ours(args):
         dist.all_reduce(status, op=dist.ReduceOp.MAX)
     if int(status.item()) != 0:
         failures.append("a kernel gave up on a bounded wait inside the timed loop")
-    del graphs
+    del g_chunk, g_rem
     if exchange == "peer":
         comm.set_deferred(False)
 
@@ -415,19 +425,34 @@ def run_ours(args):
                 m = sh
             d[kn] = m
         mods.append(d)
-    hx = {K: xs[(K, 1)].cpu().pin_memory() for (K, N) in shapes}
-    hy = {kn: torch.empty(1, kn[1], dtype=torch.float16).pin_memory() for kn in shapes}
-    h2d = sum(hx[K].numel() * 2 for K in hx)
-    d2h = sum(hy[kn].numel() * 2 for kn in shapes)
-
-    xdev = {K: torch.empty_like(xs[(K, 1)]) for (K, N) in shapes}
+    # one pinned host buffer and one device buffer hold the step's inputs (one copy in); with one GPU the modules
+    # write into slices of one device buffer (forward(x, out=...)), so the results leave with one copy as well
+    Ks = sorted({K for (K, N) in shapes})
+    hx_all = torch.cat([xs[(K, 1)].reshape(-1).cpu() for K in Ks]).pin_memory()
+    xdev_all = torch.empty_like(hx_all, device=dev)
+    xdev, o = {}, 0
+    for K in Ks:
+        xdev[K] = xdev_all[o:o + K].view(1, K)
+        o += K
+    hy_all = torch.empty(sum(N for (_, N) in shapes), dtype=torch.float16).pin_memory()
+    ydev_all = torch.empty_like(hy_all, device=dev)
+    hy, ydev, o = {}, {}, 0
+    for kn in shapes:
+        hy[kn], ydev[kn] = hy_all[o:o + kn[1]], ydev_all[o:o + kn[1]]
+        o += kn[1]
+    h2d = hx_all.numel() * 2
+    d2h = hy_all.numel() * 2
 
     def e2e_step(c):
-        for K in xdev:                                      # this step's inputs, from pinned host memory
-            xdev[K].copy_(hx[K], non_blocking=True)
-        out = [(kn, mods[c][kn](xdev[kn[0]])) for kn in shapes]
-        for kn, y in out:                                   # and its results back to the host
-            hy[kn].copy_(y, non_blocking=True)
+        xdev_all.copy_(hx_all, non_blocking=True)           # this step's inputs, from pinned host memory
+        if world == 1:
+            for kn in shapes:
+                mods[c][kn](xdev[kn[0]], out=ydev[kn])
+            hy_all.copy_(ydev_all, non_blocking=True)       # and its results back to the host
+        else:
+            out = [(kn, mods[c][kn](xdev[kn[0]])) for kn in shapes]
+            for kn, y in out:
+                hy[kn].copy_(y.view(-1), non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     for i in range(max(3, n_copies)):       # touches every weight copy once: plans are built on first use
@@ -496,12 +521,12 @@ def run_ours(args):
                                          ("" if args.no_deferred else "; each forward waits for its predecessor's flags, the step ends with a wait"),
                                  "nccl": "NCCL all_gather_into_tensor after the kernel", "none": None}[exchange],
                     "l2": f"rotation over {n_copies} distinct copies of the layers ({per_gpu_set * n_copies >> 20} MB per GPU) > 126 MB L2",
-                    "timing": "CUDA graph replay per step, CUDA events on the launch stream, max over ranks"},
+                    "timing": f"the {args.steps} steps replayed as CUDA graphs of {chunk} steps, CUDA events on the launch stream, max over ranks"},
             "clocks": clocks,
             "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "api": ("ShardedOrthoLinear.forward" if world > 1 else "OrthoLinear.forward") +
-                                               ", per step: pinned host X in, four forwards, Y out, one stream sync"},
-            "gpu_launches": int(launches_per_step * args.steps + e2e_launches),
+                                               ", per step: one pinned host buffer with X in, four forwards, Y out to pinned host memory, one stream sync"},
+            "gpu_launches": int(timed_launches + e2e_launches),
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": pk["hbm_gbs"], "unit": "GB/s",
                          "frac": per_gpu / pk["hbm_gbs"],
                          "traffic": NCU_TRAFFIC_RATIO * step_bytes / len(shapes) / world,
@@ -849,6 +874,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps-per-graph", type=int, default=64,
+                    help="the timed steps are captured as CUDA graphs of at most this many steps each")
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-regimes", action="store_true", help="skip the M=32 / M=4096 sweep over the same layers")

@@ -66,7 +66,7 @@ ORTHO_B200_API int ortho_b200_last_cuda_error(void);
  * Has no counterpart in the reference (its kernels read CSR directly,
  * src/dual_gemm.cu:106-130); it takes the place of the per-call orth_layer_t the binding builds
  * on its stack (torch_bind/bindings.cpp:19-36).  The plan owns only its own device copies
- * (packed {col16|f16 value} entries in row order, row pointers, segment tables of long rows);
+ * (packed {col16|f16 value} entries in row order, row pointers, the list of long rows and their dense FP16 copy);
  * it never retains the caller's pointers.  Creation allocates device memory, launches the
  * re-layout kernels on `stream` and synchronises that stream once.  A plan is immutable after
  * creation and may be shared by concurrent forwards.  nnz == 0 yields a valid empty plan.
@@ -81,6 +81,10 @@ ORTHO_B200_API int ortho_b200_plan_destroy(ortho_b200_plan *plan);
 ORTHO_B200_API int64_t ortho_b200_plan_nnz(const ortho_b200_plan *plan);
 /* largest number of stored entries in one output row (host value cached at creation) */
 ORTHO_B200_API int64_t ortho_b200_plan_max_row_nnz(const ortho_b200_plan *plan);
+/* 1 when every row lists its columns in strictly ascending order inside [0, in_features) (what
+ * tools/sieve.py:131-136 produces), 0 otherwise, -1 for an invalid handle.  Only such plans let the tensor-core
+ * kernels fold the sparse entries into their weight tiles; any other plan takes the gather path. */
+ORTHO_B200_API int ortho_b200_plan_rows_ordered(const ortho_b200_plan *plan);
 
 /* Decodes the re-laid-out entries back to (row, col, f16 value) triplets, entry i of the plan
  * to slot i of the outputs (each sized nnz).  Exists so that a test can prove the sparse index
@@ -310,7 +314,12 @@ ORTHO_B200_API int ortho_b200_query_kernel_status(void);
  *                    tensor-core kernels (built-in: 24);
  *   row_groups == -4: forwards with unroll < tokens <= k_split (<= 128) use the tokens-as-M tensor-core kernel
  *                    before any other rule (unroll == k_split: never); 0, 0 restores the built-in rule;
- *   row_groups == 0 : restore the built-in choice of kernel and tiling (not the -3 threshold).
+ *   row_groups == -5: plans created after the call treat rows of more than max(k_split, 4 x the mean row)
+ *                    entries as long rows (8..65536; 0 restores the built-in 64);
+ *   row_groups == -6: k_split = 0 makes the tensor-core kernels compute the sparse term as gathers from the
+ *                    transposed activations even when the plan's rows are in column order; 1 restores the
+ *                    built-in behaviour (entries folded into the weight tile);
+ *   row_groups == 0 : restore the built-in choice of kernel and tiling (not the -3 ... -6 settings).
  * Returns ERR_SHAPE for an unsupported tuple. */
 ORTHO_B200_API int ortho_b200_set_decode_config(int row_groups, int k_groups, int unroll, int k_split);
 

@@ -51,6 +51,12 @@ class Plan:
     def max_row_nnz(self) -> int:
         return int(_lib.lib().ortho_b200_plan_max_row_nnz(self._h))
 
+    @property
+    def rows_ordered(self) -> bool:
+        """Every row lists its columns in ascending order (then the tensor-core kernels fold the entries into their
+        weight tiles instead of gathering them)."""
+        return int(_lib.lib().ortho_b200_plan_rows_ordered(self._h)) == 1
+
     def decode_dump(self):
         """(rows, cols, values) of every stored entry, decoded on the GPU from the plan."""
         rows = torch.empty(self.nnz, dtype=torch.int32, device=self.device)

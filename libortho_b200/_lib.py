@@ -53,6 +53,8 @@ def _declare(l):
     l.ortho_b200_plan_nnz.argtypes = [vp]
     l.ortho_b200_plan_max_row_nnz.restype = i64
     l.ortho_b200_plan_max_row_nnz.argtypes = [vp]
+    l.ortho_b200_plan_rows_ordered.restype = ctypes.c_int
+    l.ortho_b200_plan_rows_ordered.argtypes = [vp]
     l.ortho_b200_plan_decode_dump.restype = c.c_int
     l.ortho_b200_plan_decode_dump.argtypes = [vp, i32p, i32p, vp, vp]
     l.ortho_b200_dequant_dump.restype = c.c_int
@@ -111,7 +113,7 @@ def _declare(l):
 EXPORTS = [
     "ortho_b200_strerror", "ortho_b200_version", "ortho_b200_last_cuda_error",
     "ortho_b200_plan_create", "ortho_b200_plan_destroy", "ortho_b200_plan_nnz",
-    "ortho_b200_plan_max_row_nnz", "ortho_b200_plan_decode_dump", "ortho_b200_dequant_dump",
+    "ortho_b200_plan_max_row_nnz", "ortho_b200_plan_rows_ordered", "ortho_b200_plan_decode_dump", "ortho_b200_dequant_dump",
     "ortho_b200_workspace_bytes", "ortho_b200_plan_workspace_bytes", "ortho_b200_forward", "ortho_b200_set_decode_config",
     "ortho_b200_launch_count", "ortho_b200_query_kernel_status", "ortho_b200_forward_static_scratch",
     "ortho_b200_comm_create", "ortho_b200_comm_export", "ortho_b200_comm_connect", "ortho_b200_comm_local",

@@ -47,6 +47,8 @@ struct Tuning {
     // hook, first (mid_first)
     int mid_lo = 24, mid_hi = 128;
     bool mid_first = false;
+    bool patch_weights = true;          // tensor-core kernels fold the sparse entries into the weight tile (plan with ordered rows)
+    int long_row_min = 64;              // = kLongRowMin: a plan's long-row threshold is max(this, 4 x the mean row)
 };
 constexpr int kPrefillAboveBuiltin = 24;
 Tuning tuning_snapshot();              // decode.cu
@@ -60,16 +62,21 @@ struct Plan {
     int64_t max_row_nnz;
     int32_t *row_ptr;     // [N+1] device copy
     uint32_t *entries;    // [nnz]
+    float *row_max;       // [N] largest |value| of the row (infinite if the row holds a NaN)
+    bool ordered;         // every row lists its columns in strictly ascending order, all inside [0, K)
     // Rows that stand out in length ("long": more than `heavy` entries = max(kLongRowMin, 4 x the mean row)) would
-    // hold up the tensor-core kernel's in-flight sparse pass, so the plan lists them (hrow, ascending) and cuts each
-    // into segments of at most kLongSeg entries: segment v covers entries [vbeg[v], vend[v]), long row h owns
-    // segments [hptr[h], hptr[h+1]).  A pre-pass computes their sums with whole CTAs per segment.  Built on the host.
+    // hold up the tensor-core kernel's in-flight sparse pass, so the plan lists them (hrow, ascending) and keeps
+    // them once more as a zero-filled dense FP16 matrix hdense[n_pad][K] (n_pad = n_long rounded up to 128): a
+    // pre-pass computes their sums as a small tensor-core GEMM (longrows.cu).  `heavy` is doubled until that
+    // matrix fits kLongDenseMaxBytes; a CSR row that repeats a column cannot be held densely, and a plan that
+    // meets one keeps no long rows.
     int heavy;
-    int64_t n_long, n_seg;
-    int32_t *hrow, *hptr, *vbeg, *vend;
+    int64_t n_long, n_pad;
+    int32_t *hrow;
+    __half *hdense;
 };
-constexpr int kLongRowMin = 256;
-constexpr int kLongSeg = 512;
+constexpr int kLongRowMin = 64;
+constexpr int64_t kLongDenseMaxBytes = 256ll << 20;
 constexpr uint32_t kPlanMagic = 0x0B200A17u;
 
 // view of the ortho component handed to kernels: either packed plan entries or raw CSR
@@ -235,7 +242,8 @@ int launch_routed(const FwdArgs &a);                      // api.cu: picks the k
 int launch_decode_multi(const FwdArgs *layers, int nl);   // decode.cu: one streaming launch for layers that share x
 int launch_prefill(const FwdArgs &a);
 int64_t long_rows_workspace_bytes(const Plan *pl, int64_t M);            // longrows.cu
-int launch_long_rows(const FwdArgs &a, const __half *xt, int Mp, void *ws, const float **ol_out);
+int launch_long_rows(const FwdArgs &a, int Mp, void *ws, const float **ol_out);
+int plan_build_long_rows(Plan *pl, cudaStream_t st, bool *dup_out);      // longrows.cu; returns a cudaError_t
 int64_t prefill_workspace_bytes(int64_t M, int64_t K, int64_t N);
 int64_t min_workspace_bytes(int64_t M, int64_t K, int64_t N);
 int set_decode_config(int wr, int wk, int u, int s);

@@ -326,6 +326,16 @@ int set_decode_config(int wr, int wk, int u, int s)
         else { t.mid_lo = u; t.mid_hi = s; t.mid_first = true; }
         return ORTHO_B200_OK;
     }
+    if (wr == -6) {       // s = 0: the tensor-core kernels compute the sparse term as gathers even with an ordered plan
+        if (s != 0 && s != 1) return ORTHO_B200_ERR_SHAPE;
+        t.patch_weights = s == 1;
+        return ORTHO_B200_OK;
+    }
+    if (wr == -5) {       // plans created from now on treat rows of more than max(s, 4 x the mean row) entries as long
+        if (s != 0 && (s < 8 || s > 65536)) return ORTHO_B200_ERR_SHAPE;
+        t.long_row_min = s ? s : kLongRowMin;
+        return ORTHO_B200_OK;
+    }
     if (wr == -1) {
         if ((s != 0 && s != 1 && s != 2 && s != 4 && s != 8) || u < 0 || u > 12 || u == 1) return ORTHO_B200_ERR_SHAPE;
         t.wr = t.wk = t.u = t.s = 0;

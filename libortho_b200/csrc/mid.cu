@@ -27,7 +27,7 @@
 // partials last, so the bounded flag wait does not normally wait at all.
 //
 // The sparse term is computed ahead into O[m][n] (token-major FP32, in the workspace) by ortho_tokens_kernel
-// from the once-transposed activations, one warp per weight row, and added in the FP32 epilogue.
+// from the once-transposed activations (a warp per 8 weight rows, lanes = tokens) and added in the FP32 epilogue.
 #include <cstring>
 
 #include "common.cuh"
@@ -412,76 +412,94 @@ mid_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
 }
 
 // O[m][n] = sum over the entries of row n of v * x[m, c]   (FP32, token-major with row pitch N; alpha is applied
-// in the epilogue).  One warp per weight row; a lane holds TPL consecutive tokens (Mp = 32 * TPL) and reads them
-// from the transposed activations Xt[k][Mp] with one load per entry; entries are fetched 32 at a time with one
-// coalesced load and broadcast by shuffles.
+// in the epilogue).  A warp takes 8 consecutive weight rows; a lane holds TPL consecutive tokens (Mp = 32 * TPL) and
+// reads them from the transposed activations Xt[k][Mp] with one load per entry, up to 32 / TPL entries in flight;
+// entries are fetched 32 at a time with one coalesced load and broadcast by shuffles.
 template <int TPL>
 __global__ void __launch_bounds__(256)
 ortho_tokens_kernel(const OrthoView ov, const __half *__restrict__ xt, float *__restrict__ o, int M, int K, int N)
 {
     constexpr int Mp = 32 * TPL;
+    constexpr int U = 32 / TPL;                          // activation loads in flight per lane
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n = blockIdx.x * 8 + warp;                 // one warp per weight row
-    if (n >= N) return;
-    const int e0 = ov.row_ptr[n], e1 = ov.row_ptr[n + 1];
-    float acc[TPL];
+    const int n_first = (blockIdx.x * 8 + warp) * 8;     // a warp takes 8 consecutive weight rows, one after the other
+    if (n_first >= N) return;
+    float res[8][TPL];
 #pragma unroll
-    for (int i = 0; i < TPL; i++) acc[i] = 0.f;
-    for (int eb = e0; eb < e1; eb += 32) {
-        int cl = 0; float vl = 0.f;
-        if (eb + lane < e1) {
-            if (ov.entries) {
-                const uint32_t pk = ov.entries[eb + lane];
-                cl = (int)(pk & 0xFFFFu);
-                vl = __half2float(__ushort_as_half((unsigned short)(pk >> 16)));
-            } else {
-                cl = ov.col[eb + lane];
-                vl = __half2float(ov.val[eb + lane]);
-                if ((unsigned)cl >= (unsigned)K) { cl = 0; vl = 0.f; }
+    for (int r = 0; r < 8; r++) {
+#pragma unroll
+        for (int i = 0; i < TPL; i++) res[r][i] = 0.f;
+        const int n = n_first + r;
+        if (n >= N) continue;
+        const int e0 = ov.row_ptr[n], e1 = ov.row_ptr[n + 1];
+        float acc[TPL];
+#pragma unroll
+        for (int i = 0; i < TPL; i++) acc[i] = 0.f;
+        for (int eb = e0; eb < e1; eb += 32) {
+            int cl = 0; float vl = 0.f;
+            if (eb + lane < e1) ortho_entry(ov, eb + lane, K, cl, vl);
+            const int nb = min(32, e1 - eb);
+            for (int j0 = 0; j0 < nb; j0 += U) {
+                float vv[U];
+                if constexpr (TPL == 1) {
+                    __half h[U];
+#pragma unroll
+                    for (int j = 0; j < U; j++) {
+                        const int c = __shfl_sync(0xffffffffu, cl, (j0 + j) & 31);
+                        vv[j] = __shfl_sync(0xffffffffu, vl, (j0 + j) & 31);      // slots past the row hold v = 0, c = 0
+                        h[j] = xt[(size_t)c * Mp + lane];
+                    }
+#pragma unroll
+                    for (int j = 0; j < U; j++) acc[0] = fmaf(vv[j], __half2float(h[j]), acc[0]);
+                } else if constexpr (TPL == 2) {
+                    __half2 h[U];
+#pragma unroll
+                    for (int j = 0; j < U; j++) {
+                        const int c = __shfl_sync(0xffffffffu, cl, (j0 + j) & 31);
+                        vv[j] = __shfl_sync(0xffffffffu, vl, (j0 + j) & 31);
+                        h[j] = *reinterpret_cast<const __half2 *>(xt + (size_t)c * Mp + lane * 2);
+                    }
+#pragma unroll
+                    for (int j = 0; j < U; j++) {
+                        const float2 f = __half22float2(h[j]);
+                        acc[0] = fmaf(vv[j], f.x, acc[0]); acc[1] = fmaf(vv[j], f.y, acc[1]);
+                    }
+                } else {
+                    uint2 u[U];
+#pragma unroll
+                    for (int j = 0; j < U; j++) {
+                        const int c = __shfl_sync(0xffffffffu, cl, (j0 + j) & 31);
+                        vv[j] = __shfl_sync(0xffffffffu, vl, (j0 + j) & 31);
+                        u[j] = *reinterpret_cast<const uint2 *>(xt + (size_t)c * Mp + lane * 4);
+                    }
+#pragma unroll
+                    for (int j = 0; j < U; j++) {
+                        const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&u[j].x));
+                        const float2 f1 = __half22float2(*reinterpret_cast<const __half2 *>(&u[j].y));
+                        acc[0] = fmaf(vv[j], f0.x, acc[0]); acc[1] = fmaf(vv[j], f0.y, acc[1]);
+                        acc[2] = fmaf(vv[j], f1.x, acc[2]); acc[3] = fmaf(vv[j], f1.y, acc[3]);
+                    }
+                }
             }
         }
-        const int nb = min(32, e1 - eb);
-        for (int j0 = 0; j0 < nb; j0 += 8) {             // eight independent activation loads in flight
-            float vv[8]; const __half *xp[8];
 #pragma unroll
-            for (int j = 0; j < 8; j++) {
-                const int c = __shfl_sync(0xffffffffu, cl, (j0 + j) & 31);
-                vv[j] = __shfl_sync(0xffffffffu, vl, (j0 + j) & 31);      // slots past the row hold v = 0, c = 0
-                xp[j] = xt + (size_t)c * Mp + lane * TPL;
-            }
-            if constexpr (TPL == 1) {
-                __half h[8];
-#pragma unroll
-                for (int j = 0; j < 8; j++) h[j] = *xp[j];
-#pragma unroll
-                for (int j = 0; j < 8; j++) acc[0] = fmaf(vv[j], __half2float(h[j]), acc[0]);
-            } else if constexpr (TPL == 2) {
-                __half2 h[8];
-#pragma unroll
-                for (int j = 0; j < 8; j++) h[j] = *reinterpret_cast<const __half2 *>(xp[j]);
-#pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    const float2 f = __half22float2(h[j]);
-                    acc[0] = fmaf(vv[j], f.x, acc[0]); acc[1] = fmaf(vv[j], f.y, acc[1]);
-                }
-            } else {
-                uint2 u[8];
-#pragma unroll
-                for (int j = 0; j < 8; j++) u[j] = *reinterpret_cast<const uint2 *>(xp[j]);
-#pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&u[j].x));
-                    const float2 f1 = __half22float2(*reinterpret_cast<const __half2 *>(&u[j].y));
-                    acc[0] = fmaf(vv[j], f0.x, acc[0]); acc[1] = fmaf(vv[j], f0.y, acc[1]);
-                    acc[2] = fmaf(vv[j], f1.x, acc[2]); acc[3] = fmaf(vv[j], f1.y, acc[3]);
-                }
-            }
-        }
+        for (int i = 0; i < TPL; i++) res[r][i] = acc[i];
     }
+    // a lane writes the 8 rows' sums of each of its tokens as one 32-byte run
+    const bool vec = (N % 4) == 0 && n_first + 8 <= N;
 #pragma unroll
     for (int i = 0; i < TPL; i++) {
         const int m = lane * TPL + i;
-        if (m < M) o[(size_t)m * N + n] = acc[i];
+        if (m >= M) continue;
+        float *dst = o + (size_t)m * N + n_first;
+        if (vec) {
+            reinterpret_cast<float4 *>(dst)[0] = make_float4(res[0][i], res[1][i], res[2][i], res[3][i]);
+            reinterpret_cast<float4 *>(dst)[1] = make_float4(res[4][i], res[5][i], res[6][i], res[7][i]);
+        } else {
+#pragma unroll
+            for (int r = 0; r < 8; r++)
+                if (n_first + r < N) dst[r] = res[r][i];
+        }
     }
 }
 
@@ -537,7 +555,7 @@ int launch_mid(const FwdArgs &a)
         const int Mp = (int)mid_mp(a.M);
         int st = launch_transpose_x(a.x, xt, (int)a.M, (int)a.K, Mp, a.stream);
         if (st != ORTHO_B200_OK) return st;
-        const unsigned blocks = (unsigned)ceil_div(a.N, 8);
+        const unsigned blocks = (unsigned)ceil_div(a.N, 64);
         if (Mp == 32) ortho_tokens_kernel<1><<<blocks, 256, 0, a.stream>>>(a.ortho, xt, o, (int)a.M, (int)a.K, (int)a.N);
         else if (Mp == 64) ortho_tokens_kernel<2><<<blocks, 256, 0, a.stream>>>(a.ortho, xt, o, (int)a.M, (int)a.K, (int)a.N);
         else ortho_tokens_kernel<4><<<blocks, 256, 0, a.stream>>>(a.ortho, xt, o, (int)a.M, (int)a.K, (int)a.N);

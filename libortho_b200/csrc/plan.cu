@@ -13,11 +13,13 @@
 
 namespace ob {
 
-// one warp per output row: pack the row's entries, track the longest row
+// one warp per output row: pack the row's entries, track the longest row, the largest magnitude of every row
+// (NaN counts as infinite) and whether every row lists its columns in strictly ascending order inside [0, K)
+// (info[0] = longest row, info[1] != 0: some row does not)
 __global__ void relayout_rows_kernel(const int32_t *__restrict__ row_ptr, const int32_t *__restrict__ col,
                                      const __half *__restrict__ val, int N, int K,
                                      uint32_t *__restrict__ entries, int32_t *__restrict__ row_ptr_copy,
-                                     int *__restrict__ max_row_nnz)
+                                     float *__restrict__ row_max, int *__restrict__ info)
 {
     const int warps_per_block = blockDim.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -26,15 +28,27 @@ __global__ void relayout_rows_kernel(const int32_t *__restrict__ row_ptr, const 
         if (lane == 0) row_ptr_copy[n] = e0;
         if (n == N) continue;
         const int e1 = row_ptr[n + 1];
+        float vmax = 0.f;
+        bool unordered = false;
         for (int e = e0 + lane; e < e1; e += 32) {
             int c = col[e];
             unsigned short vb = __half_as_ushort(val[e]);
+            if (e > e0 && col[e - 1] >= c) unordered = true;
             // an entry outside [0,K) is skipped by the reference (src/ortho.c:394); store it as an
             // explicit zero so that it contributes nothing
-            if ((unsigned)c >= (unsigned)K) { c = 0; vb = 0; }
+            if ((unsigned)c >= (unsigned)K) { c = 0; vb = 0; unordered = true; }
+            const float av = fabsf(__half2float(__ushort_as_half(vb)));
+            vmax = (av != av) ? __int_as_float(0x7f800000) : fmaxf(vmax, av);
             entries[e] = ((uint32_t)vb << 16) | (uint32_t)c;
         }
-        if (lane == 0) atomicMax(max_row_nnz, e1 - e0);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
+        unordered = __any_sync(0xffffffffu, unordered);
+        if (lane == 0) {
+            row_max[n] = vmax;
+            atomicMax(&info[0], e1 - e0);
+            if (unordered) atomicExch(&info[1], 1);
+        }
     }
 }
 
@@ -110,9 +124,9 @@ extern "C" int ortho_b200_plan_create(ortho_b200_plan **plan_out, const int32_t 
     Plan *pl = new (std::nothrow) Plan();
     if (!pl) return ORTHO_B200_ERR_ALLOC;
     pl->magic = kPlanMagic; pl->K = K; pl->N = N; pl->nnz = nnz; pl->max_row_nnz = 0;
-    pl->row_ptr = nullptr; pl->entries = nullptr;
-    pl->heavy = kLongRowMin; pl->n_long = 0; pl->n_seg = 0;
-    pl->hrow = nullptr; pl->hptr = nullptr; pl->vbeg = nullptr; pl->vend = nullptr;
+    pl->row_ptr = nullptr; pl->entries = nullptr; pl->row_max = nullptr; pl->ordered = false;
+    pl->heavy = kLongRowMin; pl->n_long = 0; pl->n_pad = 0;
+    pl->hrow = nullptr; pl->hdense = nullptr;
     cudaError_t e = cudaGetDevice(&pl->device);
     if (e != cudaSuccess) { note_cuda_error(e); delete pl; return ORTHO_B200_ERR_CUDA; }
     if (nnz > 0) {
@@ -120,19 +134,20 @@ extern "C" int ortho_b200_plan_create(ortho_b200_plan **plan_out, const int32_t 
         int *d_max = nullptr;
         e = cudaMalloc(&pl->row_ptr, sizeof(int32_t) * (N + 1));
         if (e == cudaSuccess) e = cudaMalloc(&pl->entries, sizeof(uint32_t) * nnz);
-        if (e == cudaSuccess) e = cudaMalloc(&d_max, sizeof(int));
-        if (e == cudaSuccess) e = cudaMemsetAsync(d_max, 0, sizeof(int), st);
+        if (e == cudaSuccess) e = cudaMalloc(&pl->row_max, sizeof(float) * N);
+        if (e == cudaSuccess) e = cudaMalloc(&d_max, 2 * sizeof(int));
+        if (e == cudaSuccess) e = cudaMemsetAsync(d_max, 0, 2 * sizeof(int), st);
         if (e == cudaSuccess) {
             const int threads = 256, wpb = threads / 32;
             int64_t blocks = ceil_div(N + 1, wpb);
             if (blocks > 148 * 16) blocks = 148 * 16;
             relayout_rows_kernel<<<(unsigned)blocks, threads, 0, st>>>(
-                row_ptr, col_indices, (const __half *)values_f16, (int)N, (int)K, pl->entries, pl->row_ptr, d_max);
+                row_ptr, col_indices, (const __half *)values_f16, (int)N, (int)K, pl->entries, pl->row_ptr, pl->row_max, d_max);
             count_launch();
             e = cudaGetLastError();
         }
-        int h_max = 0;
-        if (e == cudaSuccess) e = cudaMemcpyAsync(&h_max, d_max, sizeof(int), cudaMemcpyDeviceToHost, st);
+        int h_info[2] = {0, 0};
+        if (e == cudaSuccess) e = cudaMemcpyAsync(h_info, d_max, 2 * sizeof(int), cudaMemcpyDeviceToHost, st);
         if (e == cudaSuccess) e = cudaStreamSynchronize(st);
         if (d_max) cudaFree(d_max);
         if (e != cudaSuccess) {
@@ -140,36 +155,41 @@ extern "C" int ortho_b200_plan_create(ortho_b200_plan **plan_out, const int32_t 
             ortho_b200_plan_destroy(reinterpret_cast<ortho_b200_plan *>(pl));
             return ORTHO_B200_ERR_CUDA;
         }
+        const int h_max = h_info[0];
         pl->max_row_nnz = h_max;
+        pl->ordered = h_info[1] == 0;
         const int64_t mean = (nnz + N - 1) / N;
-        pl->heavy = (int)(4 * mean > kLongRowMin ? (4 * mean > 65536 ? 65536 : 4 * mean) : kLongRowMin);
+        const int lmin = tuning_snapshot().long_row_min;
+        pl->heavy = (int)(4 * mean > lmin ? (4 * mean > 65536 ? 65536 : 4 * mean) : lmin);
         if (h_max > pl->heavy) {
-            // list the long rows and cut them into segments on the host (one pass over the row pointers)
-            std::vector<int32_t> rp((size_t)N + 1), vb, ve, hr, hp;
+            // list the long rows on the host (one pass over the row pointers); the threshold doubles until their
+            // dense copy fits its budget
+            std::vector<int32_t> rp((size_t)N + 1), hr;
             e = cudaMemcpy(rp.data(), row_ptr, sizeof(int32_t) * (N + 1), cudaMemcpyDeviceToHost);
             if (e == cudaSuccess) {
-                for (int64_t n = 0; n < N; n++) {
-                    const int32_t b = rp[n], en = rp[n + 1];
-                    if (en - b <= pl->heavy) continue;
-                    hr.push_back((int32_t)n);
-                    hp.push_back((int32_t)vb.size());
-                    for (int32_t s0 = b; s0 < en; s0 += kLongSeg) {
-                        vb.push_back(s0);
-                        ve.push_back(s0 + kLongSeg < en ? s0 + kLongSeg : en);
+                for (;;) {
+                    hr.clear();
+                    for (int64_t n = 0; n < N; n++)
+                        if (rp[n + 1] - rp[n] > pl->heavy) hr.push_back((int32_t)n);
+                    const int64_t n_pad = ((int64_t)hr.size() + 127) / 128 * 128;
+                    if (n_pad * K * 2 <= kLongDenseMaxBytes || pl->heavy >= 65536) break;
+                    pl->heavy *= 2;
+                }
+                const size_t nl = hr.size();
+                if (nl > 0 && (int64_t)((nl + 127) / 128 * 128) * K * 2 <= kLongDenseMaxBytes) {
+                    e = cudaMalloc(&pl->hrow, sizeof(int32_t) * nl);
+                    if (e == cudaSuccess) e = cudaMemcpy(pl->hrow, hr.data(), sizeof(int32_t) * nl, cudaMemcpyHostToDevice);
+                    if (e == cudaSuccess) {
+                        pl->n_long = (int64_t)nl;
+                        bool dup = false;
+                        e = (cudaError_t)plan_build_long_rows(pl, st, &dup);
+                        if (e == cudaSuccess && dup) {         // a repeated column: every row stays with the in-kernel pass
+                            cudaFree(pl->hdense); pl->hdense = nullptr;
+                            cudaFree(pl->hrow); pl->hrow = nullptr;
+                            pl->n_long = 0; pl->n_pad = 0;
+                        }
                     }
                 }
-                hp.push_back((int32_t)vb.size());
-                const size_t nv = vb.size(), nl = hr.size();
-                e = cudaMalloc(&pl->vbeg, sizeof(int32_t) * nv);
-                if (e == cudaSuccess) e = cudaMalloc(&pl->vend, sizeof(int32_t) * nv);
-                if (e == cudaSuccess) e = cudaMalloc(&pl->hrow, sizeof(int32_t) * nl);
-                if (e == cudaSuccess) e = cudaMalloc(&pl->hptr, sizeof(int32_t) * (nl + 1));
-                if (e == cudaSuccess) e = cudaMemcpy(pl->vbeg, vb.data(), sizeof(int32_t) * nv, cudaMemcpyHostToDevice);
-                if (e == cudaSuccess) e = cudaMemcpy(pl->vend, ve.data(), sizeof(int32_t) * nv, cudaMemcpyHostToDevice);
-                if (e == cudaSuccess) e = cudaMemcpy(pl->hrow, hr.data(), sizeof(int32_t) * nl, cudaMemcpyHostToDevice);
-                if (e == cudaSuccess) e = cudaMemcpy(pl->hptr, hp.data(), sizeof(int32_t) * (nl + 1), cudaMemcpyHostToDevice);
-                pl->n_seg = (int64_t)nv;
-                pl->n_long = (int64_t)nl;
             }
             if (e != cudaSuccess) {
                 note_cuda_error(e);
@@ -189,10 +209,9 @@ extern "C" int ortho_b200_plan_destroy(ortho_b200_plan *plan)
     if (pl->magic != kPlanMagic) return ORTHO_B200_ERR_PLAN;
     if (pl->row_ptr) cudaFree(pl->row_ptr);
     if (pl->entries) cudaFree(pl->entries);
+    if (pl->row_max) cudaFree(pl->row_max);
     if (pl->hrow) cudaFree(pl->hrow);
-    if (pl->hptr) cudaFree(pl->hptr);
-    if (pl->vbeg) cudaFree(pl->vbeg);
-    if (pl->vend) cudaFree(pl->vend);
+    if (pl->hdense) cudaFree(pl->hdense);
     pl->magic = 0;
     delete pl;
     return ORTHO_B200_OK;
@@ -208,6 +227,13 @@ extern "C" int64_t ortho_b200_plan_max_row_nnz(const ortho_b200_plan *plan)
 {
     const Plan *pl = reinterpret_cast<const Plan *>(plan);
     return (pl && pl->magic == kPlanMagic) ? pl->max_row_nnz : -1;
+}
+
+extern "C" int ortho_b200_plan_rows_ordered(const ortho_b200_plan *plan)
+{
+    const Plan *pl = reinterpret_cast<const Plan *>(plan);
+    if (!pl || pl->magic != kPlanMagic) return -1;
+    return (pl->nnz == 0 || pl->ordered) ? 1 : 0;
 }
 
 extern "C" int64_t ortho_b200_plan_workspace_bytes(const ortho_b200_plan *plan, int64_t M)

@@ -8,8 +8,8 @@
 //     y[m, n] = scale[n] * D[n, m] + bias[n] + alpha * O[n, m]
 //
 // The weight tile is the M operand of the MMA and lives in TENSOR MEMORY: TMA brings the packed
-// INT4 bytes (128 bytes = 256 k per row and load) into shared memory, four converter warps (one thread per
-// output row) unpack them in registers to exact small-integer halves and write them with
+// INT4 bytes (128 bytes = 256 k per row and load) into shared memory, eight converter warps (two threads per
+// output row, 32 k of a block each) unpack them in registers to exact small-integer halves and write them with
 // tcgen05.st, so the converted weights never touch shared memory.  The token tile (256 tokens x
 // 64 k, FP16, 128-byte swizzle) is the N operand and goes from global to shared memory by TMA and
 // from there straight into the MMA.  A tile is 128 output rows x 256 tokens (one 256-column FP32
@@ -17,22 +17,29 @@
 // factors out of the K sum, src/ortho.c:356,363); outputs are transposed through shared memory and stored
 // coalesced.
 //
-// The sparse ortho term is computed INSIDE this kernel by the epilogue warps while the tile's MMAs run
-// (the reference intends the same fusion, src/dual_gemm_tensor_core.cu:324-332, but scans the whole coordinate
-// list per output element): a warp walks one output row at a time with the tile's 256 tokens across its lanes
-// and gathers 16 bytes per entry and lane from the once-transposed activations Xt[k][m], eight entries in flight.
-// The sums of 32 rows are collected as FP16 in the (then idle) output staging tiles and moved, thread = row, into
-// the 128 tensor-memory columns that the accumulator and the weight ring leave free; the FP32 epilogue adds
-// alpha * O.  Rows that a plan marks as long get their sums from the pre-pass of longrows.cu instead of being
-// walked here.  Apart from the transposed activations there is no global scratch for the sparse term.
+// The sparse ortho term (the reference intends its fusion into this kernel, src/dual_gemm_tensor_core.cu:324-332,
+// but scans the whole coordinate list per output element) takes one of two forms:
+//  * With a plan whose rows list their columns in ascending order it is FOLDED INTO THE WEIGHT TILE: as the
+//    converters walk along K, each thread walks the entries of its row with them and adds v * alpha / scale[n]
+//    (FP16) to the integer weight it has just unpacked, so the MMAs compute base and sparse term in one go
+//    (scale[n] * (w + v alpha / scale[n]) = scale[n] w + alpha v).  No transposed activations, no gathers, no
+//    extra traffic.  Rows whose corrections FP16 cannot hold (zero or tiny scale, huge values) are gathered by
+//    the epilogue warps straight from X, rows a plan marks as long get their sums from the tensor-core pre-pass
+//    of longrows.cu; a tile without such rows does nothing else.
+//  * Otherwise (raw CSR, unordered plan) the epilogue warps compute it while the tile's MMAs run: a warp walks one
+//    output row at a time with the tile's 256 tokens across its lanes and gathers 16 bytes per entry and lane
+//    from the once-transposed activations Xt[k][m], eight entries in flight.
+// In both forms the sums the epilogue warps produce are collected, 32 rows at a time, as FP16 in the (then idle)
+// output staging tiles and moved, thread = row, into the 128 tensor-memory columns that the accumulator and the
+// weight ring leave free; the FP32 epilogue adds alpha * O.
 //
 // TMEM columns: [0,256) accumulator, [256,384) ring of 4 converted weight stages, [384,512) sparse term.
 // Warp roles (CTA = 1 SM, persistent over tiles):
 //   warp 0       TMA producer           warp 1       MMA issuer, TMEM allocator
-//   warps 2-5    INT4 -> FP16 -> TMEM (one thread per output row of the tile)
-//   warps 6-13   sparse term, then epilogue (TMEM -> scale -> FP16 -> global): two sets of four warps that take
-//                alternate 32-token chunks
-//   warps 14-17  N-sharded layer only: copy each finished output tile from the local buffer to the peers' buffers
+//   warps 2-9    INT4 -> FP16 (+ sparse entries) -> TMEM
+//   warps 10-17  sparse term where needed, then epilogue (TMEM -> scale -> FP16 -> global): two sets of four warps
+//                that take alternate 32-token chunks
+//   warps 18-19  N-sharded layer only: copy each finished output tile from the local buffer to the peers' buffers
 //                (plain loads and stores over NVLink) while the next tile is being computed
 #include <cstring>
 
@@ -51,20 +58,21 @@ constexpr int NH = 1;              // accumulators per tile that share one token
 constexpr int TN = TH * NH;        // output rows per tile
 constexpr int TM = 256;            // tokens per tile        (MMA N)
 constexpr int KB = 64;             // k per pipeline stage
-constexpr int STAGES = 5;
+constexpr int STAGES = 4;
 constexpr int ASTAGES = 4;
-constexpr int X_BYTES = TM * KB * 2;     // 16 KB
+constexpr int X_BYTES = TM * KB * 2;     // 32 KB
 constexpr int WKB = 4;                   // k-blocks covered by one packed-weight load (128 bytes per row)
 constexpr int WSTAGES = 2;
 constexpr int W_BYTES = TN * 128;        // 32 KB: 256 rows x 128 B (256 k), 128-byte swizzle
 constexpr int YS_PITCH = TH + 8;         // halves per staged token row (pad against bank conflicts)
 constexpr int YS_BYTES = 32 * YS_PITCH * 2;
-constexpr int CONV_WARPS = 4 * NH;       // one converter thread per output row of the tile
+constexpr int CONV_WARPS = 8;            // two converter threads per output row of the tile (32 k of a block each)
+static_assert(NH == 1, "the converter and epilogue warp layouts are written for one accumulator");
 constexpr int EPI_WARP0 = 2 + CONV_WARPS;
 constexpr int ESETS = 2;                 // epilogue warp sets per accumulator: set e drains the 32-token chunks c = e, e + 2, ...
 constexpr int EPI_WARPS = 4 * NH * ESETS;
 constexpr int PUSH_WARP0 = EPI_WARP0 + EPI_WARPS;
-constexpr int PUSH_WARPS = 4;            // N-sharded layer: copy every finished output tile to the peers while the next tile runs
+constexpr int PUSH_WARPS = 2;            // N-sharded layer: copy every finished output tile to the peers while the next tile runs
 constexpr int NWARPS = PUSH_WARP0 + PUSH_WARPS;
 constexpr int TMEM_COLS = 512;
 constexpr int A_COL0 = NH * TM;          // accumulators occupy [0, NH*TM); converted weights follow
@@ -85,6 +93,10 @@ struct Params {
     OrthoView ov; const __half *xt; int Mp; float alpha; int has_ortho;
     // long rows of the plan: their sums OL[h][Mp] (FP32) come from the pre-pass of longrows.cu
     const float *ol; const int32_t *hrow; int n_long, heavy;
+    // patch != 0 (a plan whose rows list their columns in ascending order): the converters add the sparse entries
+    // to the weight tile itself (see the kernel's header); row_max[n] = largest |value| of row n, x = the
+    // activations in their own layout for the rows that cannot be patched
+    int patch; const float *row_max; const __half *x;
     // split-K of the last, partial wave: tiles [full_tiles, full_tiles + n_split) are each worked on by two
     // CTAs (k-blocks [0, kh) and [kh, kblocks)); the second one leaves its raw FP32 accumulators in
     // part[j][128][TM] and raises flags[j], the first one adds them in its epilogue
@@ -118,7 +130,20 @@ struct Smem {
     uint32_t tmem_base;
 };
 
-constexpr size_t kSmemBytes = 1024 + (size_t)STAGES * X_BYTES + (size_t)WSTAGES * W_BYTES + NH * ESETS * YS_BYTES + sizeof(Smem) + 256;
+constexpr int DL_BYTES = TN * KB * 2;     // 16 KB: one row of 64 FP16 weight corrections per converter thread
+constexpr size_t kSmemBytes = 1024 + (size_t)STAGES * X_BYTES + (size_t)WSTAGES * W_BYTES + NH * ESETS * YS_BYTES + DL_BYTES + sizeof(Smem) + 256;
+static_assert(kSmemBytes <= 232448, "shared memory per CTA");
+
+// Scale of a row's weight corrections: a sparse entry v of row n enters the weight tile as v * alpha / scale[n]
+// (the epilogue multiplies the whole row by scale[n]).  Returns 0 when that cannot be represented safely in
+// FP16 next to the integer weights (tiny or zero scale, huge values, NaN): such a row keeps the gather path.
+// Converters and epilogue warps evaluate this independently and must agree, hence one function.
+__device__ __forceinline__ float patch_rscale(float alpha, float scale, float row_max)
+{
+    const float r = __fdiv_rn(alpha, scale);
+    const float top = __fmul_rn(row_max, fabsf(r));
+    return (top <= 16384.f && fabsf(r) <= 3.0e38f && r != 0.f) ? r : 0.f;     // NaN and infinity fail the comparisons
+}
 }  // namespace pf
 
 __global__ void __launch_bounds__(pf::NWARPS * 32, 1)
@@ -130,7 +155,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     unsigned char *xs = base;                                       // STAGES x 16 KB, 1 KB aligned
     unsigned char *ws = xs + (size_t)STAGES * X_BYTES;              // WSTAGES x 32 KB, 1 KB aligned
     unsigned char *ys_base = ws + (size_t)WSTAGES * W_BYTES;        // NH staging tiles for the transposed store
-    Smem *sm = reinterpret_cast<Smem *>(ys_base + NH * ESETS * YS_BYTES);
+    unsigned char *dl_base = ys_base + NH * ESETS * YS_BYTES;       // weight corrections of the current k block
+    Smem *sm = reinterpret_cast<Smem *>(dl_base + DL_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nunits = p.full_tiles + 2 * p.n_split;       // work units of the grid (a split tile counts twice)
@@ -213,41 +239,122 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         }
     } else if (warp < EPI_WARP0) {
         // ================= converters: packed INT4 (smem) -> FP16 (TMEM, A operand) =================
+        // two threads per output row: thread (row, half) converts k [32 half, 32 half + 32) of every k block
         const int q = warp & 3;                        // TMEM lane quarter this warp may touch
-        const int h = (warp - 2) >> 2;                 // which accumulator's rows
-        const int row = h * TH + q * 32 + lane;        // output row inside the tile
+        const int half = (warp - 2) >> 2;              // which 32 k of the block's 64
+        const int row = q * 32 + lane;                 // output row inside the tile
         int wsi = 0, as = 0; uint32_t wph = 0, aph = 0;
         const uint32_t swz = (uint32_t)(row & 7);      // 128-byte swizzle: 16-byte chunk c sits at c ^ (row & 7)
+        // Patch mode: this thread walks the sparse entries of its row in column order along the k blocks (both
+        // threads of a row walk all of them and each keeps those of its own half), a window of four entries in
+        // registers.  An entry v becomes the FP16 correction v * alpha / scale[row], dropped into this thread's private
+        // 32 corrections in shared memory and added to the converted weights (no synchronisation: nobody else
+        // touches them).
+        __half *dlrow = reinterpret_cast<__half *>(dl_base) + half * (TN * 32) + row * 32;     // four 16-byte chunks, swizzled
+        const uint32_t dsw = (uint32_t)((row >> 1) & 3);
+        if (p.patch) {
+#pragma unroll
+            for (int j = 0; j < 4; j++) reinterpret_cast<uint4 *>(dlrow)[j] = make_uint4(0, 0, 0, 0);
+        }
+        int pend_as = -1;                                                // stage whose tcgen05.st is still on its way
         for (int u = blockIdx.x; u < nunits; u += gridDim.x) {
             const Unit un = unit_of(p, u);
+            int e_cur = 0, e_end = 0; float rsc = 0.f;
+            uint32_t w0 = 0, w1 = 0, w2 = 0, w3 = 0;
+            if (p.patch) {
+                const int n = (un.t % p.tiles_n) * TN + row;
+                if (n < p.N) {
+                    const int e0 = p.ov.row_ptr[n], e1 = p.ov.row_ptr[n + 1];
+                    if (e1 > e0 && !(p.n_long > 0 && e1 - e0 > p.heavy)) {
+                        rsc = patch_rscale(p.alpha, __half2float(p.scales[n]), p.row_max[n]);
+                        if (rsc != 0.f) { e_cur = e0; e_end = e1; }
+                    }
+                }
+                if (un.kb0 > 0 && e_cur < e_end) {          // second K half of a split tile: first entry at or past its start
+                    int lo = e_cur, hi = e_end;
+                    const uint32_t c0 = (uint32_t)(un.kb0 * KB);
+                    while (lo < hi) {
+                        const int mid = (lo + hi) >> 1;
+                        if ((p.ov.entries[mid] & 0xFFFFu) < c0) lo = mid + 1; else hi = mid;
+                    }
+                    e_cur = lo;
+                }
+                if (e_cur < e_end) w0 = p.ov.entries[e_cur];
+                if (e_cur + 1 < e_end) w1 = p.ov.entries[e_cur + 1];
+                if (e_cur + 2 < e_end) w2 = p.ov.entries[e_cur + 2];
+                if (e_cur + 3 < e_end) w3 = p.ov.entries[e_cur + 3];
+            }
             for (int kb = un.kb0; kb < un.kb1; kb++) {
                 const int sub = kb % WKB;                   // which 32-byte slice of the 128-byte weight row
                 if (sub == 0) wait(&sm->w_full[wsi], wph);
                 const unsigned char *wrow = ws + (size_t)wsi * W_BYTES + row * 128;
-                const uint4 w0 = *reinterpret_cast<const uint4 *>(wrow + ((((uint32_t)(2 * sub)) ^ swz) << 4));
-                const uint4 w1 = *reinterpret_cast<const uint4 *>(wrow + ((((uint32_t)(2 * sub + 1)) ^ swz) << 4));
+                const uint4 wa = *reinterpret_cast<const uint4 *>(wrow + ((((uint32_t)(2 * sub + half)) ^ swz) << 4));
                 if (sub == WKB - 1 || kb == un.kb1 - 1) {   // last slice of this weight stage: hand it back
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&sm->w_empty[wsi]);
                     if (++wsi == WSTAGES) { wsi = 0; wph ^= 1u; }
                 }
-                uint32_t hreg[32];
-                const uint32_t ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                uint32_t hreg[16];
+                const uint32_t ww[4] = {wa.x, wa.y, wa.z, wa.w};
 #pragma unroll
-                for (int j = 0; j < 8; j++) {
+                for (int j = 0; j < 4; j++) {
                     uint32_t o[4];
                     int4x8_to_half2x4_natural(ww[j], o);
                     hreg[4 * j] = o[0]; hreg[4 * j + 1] = o[1]; hreg[4 * j + 2] = o[2]; hreg[4 * j + 3] = o[3];
                 }
+                if (p.patch) {
+                    // entries of this row inside the k block: w_int + v * alpha / scale, as FP16
+                    const int kend = (kb + 1) * KB;
+                    bool mine = false;
+                    while (e_cur < e_end && (int)(w0 & 0xFFFFu) < kend) {
+                        const int c = (int)(w0 & 0xFFFFu) - kb * KB;
+                        if ((c >> 5) == half) {
+                            const float d = __half2float(__ushort_as_half((unsigned short)(w0 >> 16))) * rsc;
+                            dlrow[(((((uint32_t)c >> 3) & 3u) ^ dsw) << 3) + (c & 7)] = __float2half_rn(d);
+                            mine = true;
+                        }
+                        e_cur++;
+                        w0 = w1; w1 = w2; w2 = w3;
+                        w3 = (e_cur + 3 < e_end) ? p.ov.entries[e_cur + 3] : 0u;
+                    }
+                    if (__any_sync(0xffffffffu, mine)) {
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            const uint4 dv = *reinterpret_cast<const uint4 *>(dlrow + ((((uint32_t)j) ^ dsw) << 3));
+                            const uint32_t dw[4] = {dv.x, dv.y, dv.z, dv.w};
+#pragma unroll
+                            for (int i = 0; i < 4; i++) {
+                                const __half2 sum = __hadd2(*reinterpret_cast<const __half2 *>(&hreg[4 * j + i]),
+                                                            *reinterpret_cast<const __half2 *>(&dw[i]));
+                                hreg[4 * j + i] = *reinterpret_cast<const uint32_t *>(&sum);
+                            }
+                        }
+                        if (mine) {
+#pragma unroll
+                            for (int j = 0; j < 4; j++) reinterpret_cast<uint4 *>(dlrow)[j] = make_uint4(0, 0, 0, 0);
+                        }
+                    }
+                }
+                // the store of the previous k block has had this block's conversion to complete: publish it now,
+                // then start this block's store (its completion is awaited one block later)
+                if (pend_as >= 0) {
+                    tmem_st_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sm->a_full[pend_as]);
+                }
                 wait(&sm->a_empty[as], aph ^ 1u);
                 tc_fence_after();
-                tmem_st_32x32b_x32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(A_COL0 + as * A_STAGE_COLS + h * (KB / 2)), hreg);
-                tmem_st_wait();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&sm->a_full[as]);
+                tmem_st_32x32b_x16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(A_COL0 + as * A_STAGE_COLS + half * (KB / 4)), hreg);
+                pend_as = as;
                 if (++as == ASTAGES) { as = 0; aph ^= 1u; }
             }
+        }
+        if (pend_as >= 0) {
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm->a_full[pend_as]);
         }
     } else if (warp < PUSH_WARP0) {
         // ================= epilogue: TMEM -> scale -> FP16 -> shared (transpose) -> global =================
@@ -299,26 +406,75 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
             // gather per entry and lane, eight entries in flight).  The eight warps fill a 32-row batch (one
             // tensor-memory lane quarter) in the staging tiles, then the two warps of that quarter, which alone may
             // touch those lanes, move it into tensor memory with thread = row.
-            const bool with_o = p.has_ortho != 0;
+            bool with_o = p.has_ortho != 0;
+            const int ew = warp - EPI_WARP0;
+            // Patch mode: the converters fold the entries of ordinary rows into the weight tile, which leaves two kinds
+            // of rows to this pass: long rows of the plan (their sums exist already) and rows whose corrections FP16
+            // cannot hold (gathered here, straight from X).  Lane l < 16 classifies this warp's row l of the tile
+            // (batch l / 4, row l % 4 of the batch); a tile without such rows skips the pass altogether.
+            int my_e0 = 0, my_e1 = 0, my_li = -1, my_mode = 0;       // mode 1: long row, 2: gather from X
+            if (with_o && p.patch) {
+                if (lane < 16) {
+                    const int nrow = nbase + (lane >> 2) * 32 + ew * 4 + (lane & 3);
+                    if (nrow < p.N) { my_e0 = p.ov.row_ptr[nrow]; my_e1 = p.ov.row_ptr[nrow + 1]; }
+                    if (my_e1 > my_e0) {
+                        if (p.n_long > 0 && my_e1 - my_e0 > p.heavy) {
+                            int lo = 0, hi = p.n_long - 1;
+                            while (lo < hi) {
+                                const int mid = (lo + hi) >> 1;
+                                if (p.hrow[mid] < nrow) lo = mid + 1; else hi = mid;
+                            }
+                            my_li = lo; my_mode = 1;
+                        } else if (patch_rscale(p.alpha, __half2float(p.scales[nrow]), p.row_max[nrow]) == 0.f) {
+                            my_mode = 2;
+                        }
+                    }
+                }
+                uint32_t any_row;
+                asm volatile(
+                    "{\n\t.reg .pred pi, po;\n\t"
+                    "setp.ne.u32 pi, %1, 0;\n\t"
+                    "bar.red.or.pred po, 3, %2, pi;\n\t"
+                    "selp.u32 %0, 1, 0, po;\n\t}"
+                    : "=r"(any_row) : "r"((uint32_t)(my_mode != 0)), "r"(EPI_WARPS * 32) : "memory");
+                with_o = any_row != 0;
+            }
             if (with_o) {
                 __half *obuf = reinterpret_cast<__half *>(ys_base);          // [32][OB_PITCH]
-                const int ew = warp - EPI_WARP0;
                 const __half *xtile = p.xt + (size_t)mt * TM + lane * 8;       // + col * Mp
                 for (int qq = 0; qq < 4; qq++) {
                     for (int i = 0; i < 4; i++) {
                         const int r = ew * 4 + i;                              // row inside the quarter
                         const int nrow = nbase + qq * 32 + r;
                         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                        int e0 = 0, e1 = 0;
-                        if (nrow < p.N) { e0 = p.ov.row_ptr[nrow]; e1 = p.ov.row_ptr[nrow + 1]; }
-                        int li = -1;
-                        if (p.n_long > 0 && e1 - e0 > p.heavy) {               // a long row of the plan: its sums were computed ahead
-                            int lo = 0, hi = p.n_long - 1;
-                            while (lo < hi) {
-                                const int mid = (lo + hi) >> 1;
-                                if (p.hrow[mid] < nrow) lo = mid + 1; else hi = mid;
+                        int e0 = 0, e1 = 0, li = -1;
+                        if (p.patch) {
+                            const int mode = __shfl_sync(0xffffffffu, my_mode, qq * 4 + i);
+                            li = __shfl_sync(0xffffffffu, my_li, qq * 4 + i);
+                            if (mode == 2) {
+                                // a row outside the FP16 range of the weight tile: every entry against the lane's eight
+                                // tokens of X in its own layout (uncoalesced; such rows are rare)
+                                const int ea = __shfl_sync(0xffffffffu, my_e0, qq * 4 + i), eb2 = __shfl_sync(0xffffffffu, my_e1, qq * 4 + i);
+                                for (int e = ea; e < eb2; e++) {
+                                    int c; float v;
+                                    ortho_entry(p.ov, e, p.K, c, v);
+#pragma unroll
+                                    for (int t = 0; t < 8; t++) {
+                                        const int m = mt * TM + lane * 8 + t;
+                                        if (m < p.M) acc[t] = fmaf(v, __half2float(p.x[(size_t)m * p.K + c]), acc[t]);
+                                    }
+                                }
                             }
-                            if (p.hrow[lo] == nrow) li = lo;
+                        } else {
+                            if (nrow < p.N) { e0 = p.ov.row_ptr[nrow]; e1 = p.ov.row_ptr[nrow + 1]; }
+                            if (p.n_long > 0 && e1 - e0 > p.heavy) {           // a long row of the plan: its sums were computed ahead
+                                int lo = 0, hi = p.n_long - 1;
+                                while (lo < hi) {
+                                    const int mid = (lo + hi) >> 1;
+                                    if (p.hrow[mid] < nrow) lo = mid + 1; else hi = mid;
+                                }
+                                if (p.hrow[lo] == nrow) li = lo;
+                            }
                         }
                         if (li >= 0) {
                             const float4 *src = reinterpret_cast<const float4 *>(p.ol + (size_t)li * p.Mp + (size_t)mt * TM + lane * 8);
@@ -468,7 +624,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         // plain 16-byte loads (through L2) and stores; the tile of unit u travels while unit u + 1 is being computed
         const bool vec_ok = (p.N % 8) == 0 && (p.ldy % 8) == 0 && (reinterpret_cast<uintptr_t>(p.y) & 15u) == 0;
         if (p.gather && vec_ok) {
-            const int pt = (warp - PUSH_WARP0) * 32 + lane;       // 0..127
+            const int pt = (warp - PUSH_WARP0) * 32 + lane;       // 0..63: token row pt / 16 of a group, 16-byte piece pt % 16
             int done = 0;
             for (int u = blockIdx.x; u < nunits; u += gridDim.x) {
                 const Unit un = unit_of(p, u);
@@ -478,13 +634,22 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                 done++;
                 const int n0 = nt * TN + (pt & 15) * 8;
                 if (n0 >= p.N) continue;
-                for (int r0 = 0; r0 < TM; r0 += PUSH_WARPS * 2) {
-                    const int m = mt * TM + r0 + (pt >> 4);
-                    if (m >= p.M) break;
-                    const size_t at = (size_t)m * (size_t)p.ldy + n0;
-                    const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(p.y + at));
-                    for (int r = 0; r < p.gv.world; r++)
-                        if (r != p.gv.rank) *reinterpret_cast<uint4 *>(p.gv.y[r] + at) = v;
+                constexpr int PU = 4;                              // loads in flight per lane
+                for (int r0 = 0; r0 < TM; r0 += PUSH_WARPS * 2 * PU) {
+                    uint4 v[PU];
+#pragma unroll
+                    for (int i = 0; i < PU; i++) {
+                        const int m = mt * TM + r0 + i * PUSH_WARPS * 2 + (pt >> 4);
+                        if (m < p.M) v[i] = __ldcg(reinterpret_cast<const uint4 *>(p.y + (size_t)m * (size_t)p.ldy + n0));
+                    }
+#pragma unroll
+                    for (int i = 0; i < PU; i++) {
+                        const int m = mt * TM + r0 + i * PUSH_WARPS * 2 + (pt >> 4);
+                        if (m >= p.M) continue;
+                        const size_t at = (size_t)m * (size_t)p.ldy + n0;
+                        for (int r = 0; r < p.gv.world; r++)
+                            if (r != p.gv.rank) *reinterpret_cast<uint4 *>(p.gv.y[r] + at) = v[i];
+                    }
                 }
             }
         }
@@ -520,20 +685,28 @@ int launch_prefill(const FwdArgs &a)
     memset(&p, 0, sizeof(p));
     p.alpha = a.alpha; p.has_ortho = 0; p.K = (int)a.K;
     if (a.has_ortho) {
-        // the activations are transposed once per forward (Xt[k][m]) so that one sparse entry touches a contiguous run
-        // of tokens; the sparse term itself is computed inside the tensor-core kernel
-        if (!a.workspace || a.workspace_bytes < prefill_xt_bytes(a.M, a.K)) return ORTHO_B200_ERR_WORKSPACE;
-        if (((uintptr_t)a.workspace & 255u) != 0) return ORTHO_B200_ERR_ALIGN;
         const int Mp = (int)prefill_mp(a.M);
-        __half *xt = reinterpret_cast<__half *>(a.workspace);
-        const int st = launch_transpose_x(a.x, xt, (int)a.M, (int)a.K, Mp, a.stream);
-        if (st != ORTHO_B200_OK) return st;
-        p.ov = a.ortho; p.xt = xt; p.Mp = Mp;
-        p.has_ortho = 1;
+        p.ov = a.ortho; p.Mp = Mp; p.has_ortho = 1;
+        // With a plan whose rows are in column order the sparse entries are folded into the weight tile by the
+        // converters; otherwise the activations are transposed once per forward (Xt[k][m]) so that one sparse entry
+        // touches a contiguous run of tokens, and the epilogue warps gather the term.
+        p.patch = (a.plan && a.ortho.entries && a.plan->ordered && a.plan->row_max && tuning_snapshot().patch_weights) ? 1 : 0;
+        if (p.patch) {
+            p.row_max = a.plan->row_max; p.x = a.x;
+        } else {
+            if (!a.workspace || a.workspace_bytes < prefill_xt_bytes(a.M, a.K)) return ORTHO_B200_ERR_WORKSPACE;
+            if (((uintptr_t)a.workspace & 255u) != 0) return ORTHO_B200_ERR_ALIGN;
+            __half *xt = reinterpret_cast<__half *>(a.workspace);
+            const int st = launch_transpose_x(a.x, xt, (int)a.M, (int)a.K, Mp, a.stream);
+            if (st != ORTHO_B200_OK) return st;
+            p.xt = xt;
+        }
         if (a.plan && a.ortho.entries && a.plan->n_long > 0) {
+            // the long rows' pre-pass keeps its place behind the (in patch mode unused) transposed activations
             const int64_t lr = long_rows_workspace_bytes(a.plan, a.M);
-            if (a.workspace_bytes < prefill_xt_bytes(a.M, a.K) + lr) return ORTHO_B200_ERR_WORKSPACE;
-            const int st2 = launch_long_rows(a, xt, Mp, reinterpret_cast<unsigned char *>(a.workspace) + prefill_xt_bytes(a.M, a.K), &p.ol);
+            if (!a.workspace || a.workspace_bytes < prefill_xt_bytes(a.M, a.K) + lr) return ORTHO_B200_ERR_WORKSPACE;
+            if (((uintptr_t)a.workspace & 255u) != 0) return ORTHO_B200_ERR_ALIGN;
+            const int st2 = launch_long_rows(a, Mp, reinterpret_cast<unsigned char *>(a.workspace) + prefill_xt_bytes(a.M, a.K), &p.ol);
             if (st2 != ORTHO_B200_OK) return st2;
             p.hrow = a.plan->hrow; p.n_long = (int)a.plan->n_long; p.heavy = a.plan->heavy;
         }

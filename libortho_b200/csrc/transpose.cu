@@ -11,11 +11,12 @@
 namespace ob {
 
 // X[M][K] (FP16) -> Xt[K][Mp] (FP16), zero padded for m >= M.  64 x 64 tiles; 16-byte global loads
-// along k, 16-byte global stores along m, transposition through a padded shared tile.
+// along k, 16-byte global stores along m, transposition through a shared tile whose row pitch of 33 words keeps
+// both the scattered 2-byte writes (8 different k per quarter-warp) and the row reads free of bank conflicts.
 __global__ void __launch_bounds__(256)
 transpose_x_kernel(const __half *__restrict__ x, __half *__restrict__ xt, int M, int K, int Mp)
 {
-    __shared__ __half tile[64][72];                 // [k][m], row pitch 144 B keeps 16-byte alignment
+    __shared__ __half tile[64][66];                 // [k][m]
     const int k0 = blockIdx.x * 64, m0 = blockIdx.y * 64;
     const int t = threadIdx.x;
     for (int i = t; i < 64 * 8; i += 256) {         // 64 token rows x 8 chunks of 8 k
@@ -31,7 +32,10 @@ transpose_x_kernel(const __half *__restrict__ x, __half *__restrict__ xt, int M,
     for (int i = t; i < 64 * 8; i += 256) {         // 64 k rows x 8 chunks of 8 tokens
         const int r = i >> 3, ch = i & 7;
         const int k = k0 + r, m = m0 + ch * 8;
-        if (k < K && m < Mp) *reinterpret_cast<uint4 *>(xt + (size_t)k * Mp + m) = *reinterpret_cast<const uint4 *>(&tile[r][ch * 8]);
+        if (k < K && m < Mp) {
+            const uint32_t *src = reinterpret_cast<const uint32_t *>(&tile[r][ch * 8]);
+            *reinterpret_cast<uint4 *>(xt + (size_t)k * Mp + m) = make_uint4(src[0], src[1], src[2], src[3]);
+        }
     }
 }
 

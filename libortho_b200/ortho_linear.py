@@ -240,7 +240,10 @@ class OrthoLinear(nn.Module):
         return b
 
     # -- forward ---------------------------------------------------------------------------------
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """`out` (optional, not in the reference's signature): a contiguous FP16 CUDA tensor of `M * out_features`
+        elements that receives the result instead of a fresh allocation, e.g. a slice of a serving loop's
+        staging buffer."""
         if not x.is_cuda:
             raise RuntimeError("OrthoLinear (libortho_b200) runs on CUDA only; there is no CPU fallback")
         original_shape = x.shape
@@ -251,7 +254,13 @@ class OrthoLinear(nn.Module):
             x_flat = x_flat.contiguous()
         M = x_flat.shape[0]
         dev = x.device
-        output = torch.empty(M, self.out_features, device=dev, dtype=torch.float16)
+        if out is None:
+            output = torch.empty(M, self.out_features, device=dev, dtype=torch.float16)
+        else:
+            if (out.dtype != torch.float16 or out.device != dev or not out.is_contiguous()
+                    or out.numel() != M * self.out_features):
+                raise RuntimeError("out must be a contiguous FP16 tensor of M * out_features elements on the input's device")
+            output = out.view(M, self.out_features)
         fused_bias = False
         if M:
             alpha = float(self.alpha)

@@ -482,3 +482,63 @@ def test_tokens_as_m_kernel_against_oracle(oracle_mod, M, K, N, d, kind, alpha):
     finally:
         _lib.lib().ortho_b200_set_decode_config(-4, 0, 0, 0)
     assert torch.equal(y0, ye)
+
+
+def _force_gathers(on: bool):
+    """Tuning hook -6: k_split = 0 makes the tensor-core kernels gather the sparse term instead of folding it into
+    the weight tile."""
+    assert _lib.lib().ortho_b200_set_decode_config(-6, 0, 0, 0 if on else 1) == 0
+
+
+@pytest.mark.parametrize("K,N,M,d", [(1024, 520, 300, 0.01), (4096, 256, 513, 0.003), (2048, 384, 1500, 0.02)])
+def test_sparse_term_folded_into_the_weights_and_as_gathers(oracle_mod, K, N, M, d):
+    """With a plan whose rows are in column order the tensor-core kernel adds the sparse entries to its weight tile;
+    the same forward with that switched off gathers them from the transposed activations.  Both against the oracle,
+    and against each other within FP16 rounding of the weight tile."""
+    layer = wl.make_layer(K, N, d, seed=7)
+    assert _C_ops.Plan(*(t.to(DEV) for t in (layer.row_ptr, layer.col, layer.vals)), K, N).rows_ordered
+    x = wl.make_input(M, K, seed=7)
+    ref = layer_oracle(oracle_mod, layer, x, 0.75)
+    ya = run_layer(layer.to(DEV), x.to(DEV), 0.75)
+    try:
+        _force_gathers(True)
+        yb = run_layer(layer.to(DEV), x.to(DEV), 0.75)
+    finally:
+        _force_gathers(False)
+    assert _lib.lib().ortho_b200_query_kernel_status() == 0
+    assert_close(ya.float().cpu().numpy(), ref, f"folded {K}x{N} M={M}")
+    assert_close(yb.float().cpu().numpy(), ref, f"gathered {K}x{N} M={M}")
+    rel, mx = errors(ya.float().cpu().numpy(), yb.float().cpu().numpy())
+    assert rel <= 5e-4, rel
+
+
+def test_rows_that_cannot_be_folded_keep_the_gather_path(oracle_mod):
+    """Rows with a zero or tiny scale and large sparse values (v * alpha / scale outside FP16) are gathered by the
+    epilogue warps straight from X; rows with unordered columns make the whole plan take the gather path."""
+    K, N, M = 1024, 300, 260
+    layer = wl.make_layer(K, N, 0.01, seed=21)
+    scales = layer.base_scales.clone()
+    scales[5] = 0.0
+    scales[130] = 1e-6
+    scales[131] = 6e-8
+    scales[299] = 1e-6
+    layer = wl.Layer(K, N, layer.base_weight, scales, layer.row_ptr, layer.col, layer.vals, 1.0)
+    counts = layer.row_ptr[1:] - layer.row_ptr[:-1]
+    assert all(int(counts[r]) > 0 for r in (5, 130, 131, 299))
+    x = wl.make_input(M, K, seed=21)
+    ref = layer_oracle(oracle_mod, layer, x, 1.0)
+    y = run_layer(layer.to(DEV), x.to(DEV), 1.0)
+    assert _lib.lib().ortho_b200_query_kernel_status() == 0
+    assert bool(torch.isfinite(y).all())
+    assert_close(y.float().cpu().numpy(), ref, "rows outside the FP16 range of the weight tile")
+    # the same entries with every row's columns reversed: an unordered plan
+    col, vals = layer.col.clone(), layer.vals.clone()
+    rp = layer.row_ptr.tolist()
+    for n in range(N):
+        col[rp[n]:rp[n + 1]] = layer.col[rp[n]:rp[n + 1]].flip(0)
+        vals[rp[n]:rp[n + 1]] = layer.vals[rp[n]:rp[n + 1]].flip(0)
+    rev = wl.Layer(K, N, layer.base_weight, scales, layer.row_ptr, col, vals, 1.0)
+    assert not _C_ops.Plan(*(t.to(DEV) for t in (rev.row_ptr, rev.col, rev.vals)), K, N).rows_ordered
+    y2 = run_layer(rev.to(DEV), x.to(DEV), 1.0)
+    assert _lib.lib().ortho_b200_query_kernel_status() == 0
+    assert_close(y2.float().cpu().numpy(), ref, "plan with unordered rows")
