@@ -62,7 +62,7 @@ constexpr int STAGES = 4;
 constexpr int ASTAGES = 4;
 constexpr int X_BYTES = TM * KB * 2;     // 32 KB
 constexpr int WKB = 4;                   // k-blocks covered by one packed-weight load (128 bytes per row)
-constexpr int WSTAGES = 2;
+constexpr int WSTAGES = 3;
 constexpr int W_BYTES = TN * 128;        // 32 KB: 256 rows x 128 B (256 k), 128-byte swizzle
 constexpr int YS_PITCH = TH + 8;         // halves per staged token row (pad against bank conflicts)
 constexpr int YS_BYTES = 32 * YS_PITCH * 2;
@@ -284,16 +284,24 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                 if (e_cur + 2 < e_end) w2 = p.ov.entries[e_cur + 2];
                 if (e_cur + 3 < e_end) w3 = p.ov.entries[e_cur + 3];
             }
-            for (int kb = un.kb0; kb < un.kb1; kb++) {
-                const int sub = kb % WKB;                   // which 32-byte slice of the 128-byte weight row
-                if (sub == 0) wait(&sm->w_full[wsi], wph);
+            for (int kb4 = un.kb0; kb4 < un.kb1; kb4 += WKB) {
+                // one packed-weight stage = four k blocks (kb0 is a multiple of four): this thread's four 16-byte slices
+                // go to registers at once and the stage is handed back right away, so that its next load has the
+                // time of three more k blocks to arrive
+                wait(&sm->w_full[wsi], wph);
                 const unsigned char *wrow = ws + (size_t)wsi * W_BYTES + row * 128;
-                const uint4 wa = *reinterpret_cast<const uint4 *>(wrow + ((((uint32_t)(2 * sub + half)) ^ swz) << 4));
-                if (sub == WKB - 1 || kb == un.kb1 - 1) {   // last slice of this weight stage: hand it back
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&sm->w_empty[wsi]);
-                    if (++wsi == WSTAGES) { wsi = 0; wph ^= 1u; }
-                }
+                uint4 wq[WKB];
+#pragma unroll
+                for (int sub = 0; sub < WKB; sub++)
+                    wq[sub] = *reinterpret_cast<const uint4 *>(wrow + ((((uint32_t)(2 * sub + half)) ^ swz) << 4));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sm->w_empty[wsi]);
+                if (++wsi == WSTAGES) { wsi = 0; wph ^= 1u; }
+#pragma unroll
+                for (int sub = 0; sub < WKB; sub++) {
+                const int kb = kb4 + sub;
+                if (kb >= un.kb1) break;
+                const uint4 wa = wq[sub];
                 uint32_t hreg[16];
                 const uint32_t ww[4] = {wa.x, wa.y, wa.z, wa.w};
 #pragma unroll
@@ -348,6 +356,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                 tmem_st_32x32b_x16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(A_COL0 + as * A_STAGE_COLS + half * (KB / 4)), hreg);
                 pend_as = as;
                 if (++as == ASTAGES) { as = 0; aph ^= 1u; }
+                }
             }
         }
         if (pend_as >= 0) {
