@@ -242,7 +242,7 @@ int launch_routed(const FwdArgs &a);                      // api.cu: picks the k
 int launch_decode_multi(const FwdArgs *layers, int nl);   // decode.cu: one streaming launch for layers that share x
 int launch_prefill(const FwdArgs &a);
 int64_t long_rows_workspace_bytes(const Plan *pl, int64_t M);            // longrows.cu
-int launch_long_rows(const FwdArgs &a, int Mp, void *ws, const float **ol_out);
+int launch_long_rows(const FwdArgs &a, int Mp, void *ws, const float **part_out, int *nsplit_out);
 int plan_build_long_rows(Plan *pl, cudaStream_t st, bool *dup_out);      // longrows.cu; returns a cudaError_t
 int64_t prefill_workspace_bytes(int64_t M, int64_t K, int64_t N);
 int64_t min_workspace_bytes(int64_t M, int64_t K, int64_t N);

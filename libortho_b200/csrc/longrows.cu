@@ -11,8 +11,10 @@
 //     OL = HD * X^T        (tcgen05.mma kind::f16, both operands K-major from shared memory via TMA, FP32 in TMEM)
 //
 // tile = 128 long rows x 256 tokens, K cut into `nsplit` shares so that the few tiles fill the GPU; every share
-// leaves its FP32 sums in the workspace and a second kernel adds the shares in share order (no atomics: the result
-// does not depend on scheduling).  X is read in its own layout, the transposed copy is not needed here.
+// leaves its FP32 sums in the workspace and the main kernel adds the shares, in share order, when it picks a long
+// row's sums up (no atomics: the result does not depend on scheduling).  X is read in its own layout, the
+// transposed copy is not needed here.  The main kernel is launched as a programmatic dependent of this one: its
+// tensor-core pipeline starts while this kernel drains, only the warps that read the sums wait for it.
 // The reference walks every coordinate serially per token (src/ortho.c:384-398).
 #include <cstring>
 
@@ -66,6 +68,7 @@ long_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // the main kernel may start its own pipeline
     const uint32_t tmem = sm->tmem_base;
     bool dead = false;
     auto wait = [&](uint64_t *bar, uint32_t parity) {
@@ -134,27 +137,6 @@ long_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
     if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, TT); }
 }
 
-// OL[h][m] = sum over the K shares, in share order
-__global__ void __launch_bounds__(256)
-long_combine_kernel(const float *__restrict__ part, float *__restrict__ ol, int n_pad, int Mp, int nsplit)
-{
-    const int h = blockIdx.x;
-    const int m = blockIdx.y * 256 + threadIdx.x;
-    const float *src = part + (size_t)h * Mp + m;
-    const size_t sstride = (size_t)n_pad * Mp;
-    float acc = 0.f;
-    int s = 0;
-    for (; s + 4 <= nsplit; s += 4) {          // four loads in flight, added in share order
-        float t[4];
-#pragma unroll
-        for (int i = 0; i < 4; i++) t[i] = src[(size_t)(s + i) * sstride];
-#pragma unroll
-        for (int i = 0; i < 4; i++) acc += t[i];
-    }
-    for (; s < nsplit; s++) acc += src[(size_t)s * sstride];
-    ol[(size_t)h * Mp + m] = acc;
-}
-
 // ---- plan side: the dense copy of the long rows --------------------------------------------------------------
 // One CTA per long row: writes the row's entries into the (zeroed) dense row and marks every column in a
 // shared-memory bitmap; a column met twice (a CSR row that repeats a column, which the dense form cannot hold)
@@ -217,22 +199,22 @@ int plan_build_long_rows(Plan *pl, cudaStream_t st, bool *dup_out)
     return (int)e;
 }
 
-// [ OL : n_long * Mp floats ][ per-share sums : nsplit * n_pad * Mp floats ]
+// per-share sums: nsplit * n_pad * Mp floats
 int64_t long_rows_workspace_bytes(const Plan *pl, int64_t M)
 {
     if (!pl || pl->n_long == 0) return 0;
     const int64_t Mp = lr_mp(M);
-    return (((pl->n_long + (int64_t)long_rows_splits(pl, M) * pl->n_pad) * Mp * 4 + 255) / 256) * 256;
+    return (((int64_t)long_rows_splits(pl, M) * pl->n_pad * Mp * 4 + 255) / 256) * 256;
 }
 
-// ws: long_rows_workspace_bytes() bytes, 256-byte aligned; Mp = tokens rounded up to 256.  *ol_out = OL[n_long][Mp].
-int launch_long_rows(const FwdArgs &a, int Mp, void *ws, const float **ol_out)
+// ws: long_rows_workspace_bytes() bytes, 256-byte aligned; Mp = tokens rounded up to 256.  The sums of long row h for
+// token m are  sum over s < *nsplit_out of  (*part_out)[(s * n_pad + h) * Mp + m].
+int launch_long_rows(const FwdArgs &a, int Mp, void *ws, const float **part_out, int *nsplit_out)
 {
     using namespace lg;
     const Plan *pl = a.plan;
-    float *ol = reinterpret_cast<float *>(ws);
     Params p;
-    p.part = ol + (size_t)pl->n_long * Mp;
+    p.part = reinterpret_cast<float *>(ws);
     p.n_long = (int)pl->n_long; p.n_pad = (int)pl->n_pad; p.Mp = Mp;
     p.kblocks = (int)ceil_div(a.K, KB); p.nsplit = long_rows_splits(pl, a.M);
     p.status = kernel_status_word();
@@ -255,11 +237,8 @@ int launch_long_rows(const FwdArgs &a, int Mp, void *ws, const float **ol_out)
     long_gemm_kernel<<<g1, NWARPS * 32, kSmemBytes, a.stream>>>(amap, xmap, p);
     count_launch();
     OB_CUDA(cudaGetLastError());
-    dim3 g2((unsigned)pl->n_long, (unsigned)(Mp / 256));
-    long_combine_kernel<<<g2, 256, 0, a.stream>>>(p.part, ol, p.n_pad, Mp, p.nsplit);
-    count_launch();
-    OB_CUDA(cudaGetLastError());
-    *ol_out = ol;
+    *part_out = p.part;
+    *nsplit_out = p.nsplit;
     return ORTHO_B200_OK;
 }
 

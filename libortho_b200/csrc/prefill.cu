@@ -91,8 +91,9 @@ struct Params {
     int *status;
     // sparse term: CSR view (plan entries or raw arrays) and the transposed activations Xt[k][Mp] (zero for m >= M)
     OrthoView ov; const __half *xt; int Mp; float alpha; int has_ortho;
-    // long rows of the plan: their sums OL[h][Mp] (FP32) come from the pre-pass of longrows.cu
-    const float *ol; const int32_t *hrow; int n_long, heavy;
+    // long rows of the plan: the pre-pass of longrows.cu leaves their sums as ol_splits FP32 shares,
+    // ol[(s * ol_pad + h) * Mp + m] for share s, long row h, token m
+    const float *ol; int ol_splits, ol_pad; const int32_t *hrow; int n_long, heavy;
     // patch != 0 (a plan whose rows list their columns in ascending order): the converters add the sparse entries
     // to the weight tile itself (see the kernel's header); row_max[n] = largest |value| of row n, x = the
     // activations in their own layout for the rows that cannot be patched
@@ -367,6 +368,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         }
     } else if (warp < PUSH_WARP0) {
         // ================= epilogue: TMEM -> scale -> FP16 -> shared (transpose) -> global =================
+        // these warps alone read what the long-row pre-pass wrote: they wait for it here, the other warps do not
+        if (p.n_long > 0) asm volatile("griddepcontrol.wait;" ::: "memory");
         const int q = warp & 3;
         const int h = 0;                               // accumulator handled by this warp set (NH == 1)
         const int eset = (warp - EPI_WARP0) >> 2;      // which set of four warps: it drains chunks eset, eset + ESETS, ...
@@ -486,10 +489,25 @@ prefill_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                             }
                         }
                         if (li >= 0) {
-                            const float4 *src = reinterpret_cast<const float4 *>(p.ol + (size_t)li * p.Mp + (size_t)mt * TM + lane * 8);
-                            const float4 a0 = src[0], a1 = src[1];
-                            acc[0] = a0.x; acc[1] = a0.y; acc[2] = a0.z; acc[3] = a0.w;
-                            acc[4] = a1.x; acc[5] = a1.y; acc[6] = a1.z; acc[7] = a1.w;
+                            const float *src = p.ol + (size_t)li * p.Mp + (size_t)mt * TM + lane * 8;
+                            const size_t sstride = (size_t)p.ol_pad * p.Mp;
+                            for (int s2 = 0; s2 < p.ol_splits; s2 += 4) {             // four shares in flight, added in share order
+                                float4 a0[4], a1[4];
+#pragma unroll
+                                for (int i2 = 0; i2 < 4; i2++) {
+                                    if (s2 + i2 < p.ol_splits) {
+                                        const float4 *sp = reinterpret_cast<const float4 *>(src + (size_t)(s2 + i2) * sstride);
+                                        a0[i2] = __ldcg(sp); a1[i2] = __ldcg(sp + 1);
+                                    }
+                                }
+#pragma unroll
+                                for (int i2 = 0; i2 < 4; i2++) {
+                                    if (s2 + i2 < p.ol_splits) {
+                                        acc[0] += a0[i2].x; acc[1] += a0[i2].y; acc[2] += a0[i2].z; acc[3] += a0[i2].w;
+                                        acc[4] += a1[i2].x; acc[5] += a1[i2].y; acc[6] += a1[i2].z; acc[7] += a1[i2].w;
+                                    }
+                                }
+                            }
                         } else {
                             for (int eb = e0; eb < e1; eb += 32) {
                                 int cl = 0; float vl = 0.f;
@@ -715,9 +733,7 @@ int launch_prefill(const FwdArgs &a)
             const int64_t lr = long_rows_workspace_bytes(a.plan, a.M);
             if (!a.workspace || a.workspace_bytes < prefill_xt_bytes(a.M, a.K) + lr) return ORTHO_B200_ERR_WORKSPACE;
             if (((uintptr_t)a.workspace & 255u) != 0) return ORTHO_B200_ERR_ALIGN;
-            const int st2 = launch_long_rows(a, Mp, reinterpret_cast<unsigned char *>(a.workspace) + prefill_xt_bytes(a.M, a.K), &p.ol);
-            if (st2 != ORTHO_B200_OK) return st2;
-            p.hrow = a.plan->hrow; p.n_long = (int)a.plan->n_long; p.heavy = a.plan->heavy;
+            p.hrow = a.plan->hrow; p.n_long = (int)a.plan->n_long; p.heavy = a.plan->heavy; p.ol_pad = (int)a.plan->n_pad;
         }
     }
     CUtensorMap xmap, wmap;
@@ -765,7 +781,23 @@ int launch_prefill(const FwdArgs &a)
     }
     const int nunits = p.full_tiles + 2 * p.n_split;
     const int grid = nunits < num_sms ? nunits : num_sms;
-    prefill_kernel<<<grid, NWARPS * 32, kSmemBytes, a.stream>>>(xmap, wmap, p);
+    if (p.n_long > 0) {
+        // The pre-pass goes right in front of the main kernel, which is launched as its programmatic dependent: the
+        // main kernel's CTAs move in as the pre-pass's CTAs leave, and only its epilogue warps wait for the sums.
+        const int st2 = launch_long_rows(a, p.Mp, reinterpret_cast<unsigned char *>(a.workspace) + prefill_xt_bytes(a.M, a.K),
+                                         &p.ol, &p.ol_splits);
+        if (st2 != ORTHO_B200_OK) return st2;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3(NWARPS * 32); cfg.dynamicSmemBytes = kSmemBytes;
+        cfg.stream = a.stream; cfg.attrs = attr; cfg.numAttrs = 1;
+        OB_CUDA(cudaLaunchKernelEx(&cfg, prefill_kernel, xmap, wmap, p));
+    } else {
+        prefill_kernel<<<grid, NWARPS * 32, kSmemBytes, a.stream>>>(xmap, wmap, p);
+    }
     count_launch();
     OB_CUDA(cudaGetLastError());
     return ORTHO_B200_OK;
