@@ -257,6 +257,8 @@ def run_ours(args):
     if world > 1:
         exchange = args.exchange
         if exchange == "peer":
+            if args.per_cta_signal:
+                assert lib.ortho_b200_set_decode_config(-7, 0, 0, 1) == 0     # before the comms are created
             try:
                 comm = _C_ops.Comm(rank, world, 2 * region[max(wl.CFG3_M)], device=dev)
                 comm.connect_group()
@@ -518,6 +520,7 @@ def run_ours(args):
             "config": {"workload": WORKLOAD},
             "run": {"parallelism": f"N-sharded x{world} + output gather" if world > 1 else "single GPU",
                     "exchange": {"peer": "peer stores issued by the kernels (ortho_b200_forward_gather)" +
+                                         ("; every CTA signals the peers" if args.per_cta_signal else "") +
                                          ("" if args.no_deferred else "; each forward waits for its predecessor's flags, the step ends with a wait"),
                                  "nccl": "NCCL all_gather_into_tensor after the kernel", "none": None}[exchange],
                     "l2": f"rotation over {n_copies} distinct copies of the layers ({per_gpu_set * n_copies >> 20} MB per GPU) > 126 MB L2",
@@ -883,6 +886,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="multi-GPU output exchange: peer stores from the kernels, or an NCCL all-gather")
+    ap.add_argument("--per-cta-signal", action="store_true",
+                    help="peer exchange: every CTA signals the peers itself instead of the grid's last CTA")
     ap.add_argument("--no-deferred", action="store_true",
                     help="peer exchange: every forward waits for its own exchange instead of the next one waiting for it")
     ap.add_argument("--one", default=None, metavar="KxNxM", help="run a few forwards of one layer and exit (for profiling)")

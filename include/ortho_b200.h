@@ -319,7 +319,10 @@ ORTHO_B200_API int ortho_b200_query_kernel_status(void);
  *   row_groups == -6: k_split = 0 makes the tensor-core kernels compute the sparse term as gathers from the
  *                    transposed activations even when the plan's rows are in column order; 1 restores the
  *                    built-in behaviour (entries folded into the weight tile);
- *   row_groups == 0 : restore the built-in choice of kernel and tiling (not the -3 ... -6 settings).
+ *   row_groups == -7: k_split = 1 makes comms created after the call use per-CTA signalling in the peer exchange
+ *                    (every CTA adds itself to a counter on every peer once its stores are out) instead of one
+ *                    flag raised by the grid's last CTA; all ranks of a group must use the same setting;
+ *   row_groups == 0 : restore the built-in choice of kernel and tiling (not the -3 ... -7 settings).
  * Returns ERR_SHAPE for an unsupported tuple. */
 ORTHO_B200_API int ortho_b200_set_decode_config(int row_groups, int k_groups, int unroll, int k_split);
 

@@ -33,6 +33,7 @@ struct Comm {
     bool opened[kMaxRanks];
     bool connected;
     bool deferred;
+    bool per_cta;         // signalling form, fixed when the comm is created (the two forms count differently)
     long long timeout_ns;
 };
 
@@ -97,6 +98,7 @@ extern "C" int ortho_b200_comm_create(int rank, int world, int64_t bytes, ortho_
     cm->bytes = bytes;
     cm->ctrl_off = (bytes + 255) & ~(int64_t)255;
     cm->timeout_ns = 2000000000LL;
+    cm->per_cta = tuning_snapshot().gather_per_cta;
     cudaError_t e = cudaGetDevice(&cm->device);
     unsigned char *p = nullptr;
     if (e == cudaSuccess) e = cudaMalloc(&p, (size_t)cm->ctrl_off + 256);
@@ -176,6 +178,7 @@ extern "C" int ortho_b200_comm_wait(ortho_b200_comm *comm, void *stream)
     GatherView gv;
     memset(&gv, 0, sizeof(gv));
     gv.world = cm->world; gv.rank = cm->rank; gv.timeout_ns = cm->timeout_ns; gv.deferred = 1;
+    gv.per_cta = cm->per_cta ? 1 : 0;
     for (int r = 0; r < cm->world; r++) gv.ctrl[r] = reinterpret_cast<GatherCtrl *>(cm->base[r] + cm->ctrl_off);
     int *status = kernel_status_word();
     if (!status) return ORTHO_B200_ERR_CUDA;
@@ -225,6 +228,7 @@ extern "C" int ortho_b200_forward_gather(const void *q_weight, const void *q_sca
     memset(&gv, 0, sizeof(gv));
     gv.world = cm->world; gv.rank = cm->rank; gv.timeout_ns = cm->timeout_ns;
     gv.deferred = cm->deferred ? 1 : 0;
+    gv.per_cta = cm->per_cta ? 1 : 0;
     for (int r = 0; r < cm->world; r++) {
         gv.y[r] = reinterpret_cast<__half *>(cm->base[r] + y_offset_bytes) + n_offset;
         gv.ctrl[r] = reinterpret_cast<GatherCtrl *>(cm->base[r] + cm->ctrl_off);

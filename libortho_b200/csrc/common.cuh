@@ -47,6 +47,7 @@ struct Tuning {
     // hook, first (mid_first)
     int mid_lo = 24, mid_hi = 128;
     bool mid_first = false;
+    bool gather_per_cta = false;        // peer exchange: every CTA signals the peers itself instead of the grid's last CTA
     bool patch_weights = true;          // tensor-core kernels fold the sparse entries into the weight tile (plan with ordered rows)
     int long_row_min = 64;              // = kLongRowMin: a plan's long-row threshold is max(this, 4 x the mean row)
 };

@@ -326,6 +326,11 @@ int set_decode_config(int wr, int wk, int u, int s)
         else { t.mid_lo = u; t.mid_hi = s; t.mid_first = true; }
         return ORTHO_B200_OK;
     }
+    if (wr == -7) {       // s = 1: per-CTA signalling in the peer exchange (every rank of a group must use the same setting)
+        if (s != 0 && s != 1) return ORTHO_B200_ERR_SHAPE;
+        t.gather_per_cta = s == 1;
+        return ORTHO_B200_OK;
+    }
     if (wr == -6) {       // s = 0: the tensor-core kernels compute the sparse term as gathers even with an ordered plan
         if (s != 0 && s != 1) return ORTHO_B200_ERR_SHAPE;
         t.patch_weights = s == 1;

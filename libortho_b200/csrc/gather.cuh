@@ -16,7 +16,12 @@ struct GatherCtrl {
     int flag[kMaxRanks];     // flag[r] is written by rank r: the epoch of the last forward it finished
     int epoch;               // this rank's own count of finished gathers (device-side: survives graph replay)
     unsigned counter;        // CTAs of the running grid that have stored everything
+    unsigned arrive[kMaxRanks];   // per-CTA signalling: arrive[r] grows by kArriveUnit per finished forward of rank r
 };
+// Per-CTA signalling: every CTA of a forward adds 1 to its counter on every peer once its own stores are out, and the
+// grid's first CTA adds kArriveUnit - (CTAs of the grid) on top, so that a forward is complete on a peer exactly when
+// the counter has grown by kArriveUnit.  (Grids of this library have at most a few hundred CTAs.)
+constexpr unsigned kArriveUnit = 1u << 14;
 
 // what a kernel needs to publish its slice.  world == 1 and ctrl[*] == nullptr: plain local store.
 struct GatherView {
@@ -26,6 +31,8 @@ struct GatherView {
     long long timeout_ns;          // bound of the wait for the peers' flags
     int deferred;                  // 1: a kernel waits for the PREVIOUS exchange before it reads its input and
                                    // only signals its own; 0: it signals and waits for its own exchange
+    int per_cta;                   // 1: every CTA signals the peers itself (remote counters); 0: the grid's last CTA
+                                   // raises one flag per peer after a device-scope count
 };
 
 __device__ __forceinline__ void st_relaxed_sys(int *p, int v) {
@@ -42,6 +49,9 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
     return t;
 }
 
+__device__ __forceinline__ void red_add_relaxed_sys(unsigned *p, unsigned v) {
+    asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ int ld_acquire_sys(const int *p) {
     int v;
     asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -57,16 +67,22 @@ __device__ __forceinline__ bool gather_wait_flags(const GatherView &gv, int ep)
     const GatherCtrl *mine = gv.ctrl[gv.rank];
     bool ok = true;
     const unsigned long long t0 = global_timer_ns();
+    // what a peer's word must have reached: its flag the epoch, or its counter epoch * kArriveUnit (both compared
+    // as wrapped differences)
+    const int want = gv.per_cta ? (int)((unsigned)ep * kArriveUnit) : ep;
     for (int r = 0; r < gv.world; r++) {
         if (r == gv.rank) continue;
-        const int *f = &mine->flag[r];
+        const int *f = gv.per_cta ? reinterpret_cast<const int *>(&mine->arrive[r]) : &mine->flag[r];
         unsigned spins = 0;
-        while (ld_relaxed_sys(f) - ep < 0) {
+        while (ld_relaxed_sys(f) - want < 0) {
             if ((++spins & 63u) == 0 && (long long)(global_timer_ns() - t0) > gv.timeout_ns) { ok = false; break; }
         }
     }
-    for (int r = 0; r < gv.world; r++)
-        if (r != gv.rank && ld_acquire_sys(&mine->flag[r]) - ep < 0) ok = false;
+    for (int r = 0; r < gv.world; r++) {
+        if (r == gv.rank) continue;
+        const int *f = gv.per_cta ? reinterpret_cast<const int *>(&mine->arrive[r]) : &mine->flag[r];
+        if (ld_acquire_sys(f) - want < 0) ok = false;
+    }
     return ok;
 }
 
@@ -101,8 +117,24 @@ __device__ __forceinline__ bool gather_signal_and_wait(const GatherView &gv, uns
     if (gv.world <= 1) return true;
     __syncthreads();
     if (threadIdx.x != 0) return true;
-    fence_acq_rel_gpu();
     GatherCtrl *mine = gv.ctrl[gv.rank];
+    if (gv.per_cta) {
+        // this CTA's stores (ordered before this thread by the barrier) -> one system-scope fence -> one remote add
+        // per peer; the device-scope count below only elects the thread that keeps the epoch and, in the
+        // non-deferred mode, waits: no peer waits for it
+        fence_acq_rel_sys();
+        const bool first = (blockIdx.x | blockIdx.y | blockIdx.z) == 0;
+        const unsigned add = first ? kArriveUnit - total_ctas + 1u : 1u;
+        for (int r = 0; r < gv.world; r++)
+            if (r != gv.rank) red_add_relaxed_sys(&gv.ctrl[r]->arrive[gv.rank], add);
+        if (atomicAdd(&mine->counter, 1u) != total_ctas - 1) return true;
+        atomicExch(&mine->counter, 0u);
+        const int ep = mine->epoch + 1;
+        mine->epoch = ep;
+        if (gv.deferred) return true;
+        return gather_wait_flags(gv, ep);
+    }
+    fence_acq_rel_gpu();
     if (atomicAdd(&mine->counter, 1u) != total_ctas - 1) return true;
     fence_acq_rel_sys();
     atomicExch(&mine->counter, 0u);

@@ -19,6 +19,8 @@ def main():
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
     dev = torch.device("cuda", torch.cuda.current_device())
     dist.init_process_group("nccl", device_id=dev)
+    if os.environ.get("ORTHO_B200_TEST_PER_CTA") == "1":      # the signalling form is fixed when a comm is created
+        assert _lib.lib().ortho_b200_set_decode_config(-7, 0, 0, 1) == 0
     cases = [(4096, 2048, 1), (1024, 1056, 16), (512, 528, 40), (256, 1024, 200), (2048, 96, 4), (512, 1056, 300)]
     for K, N, M in cases:
         layer = wl.make_layer(K, N, 0.01, seed=K + N + M).to(dev)

@@ -67,12 +67,14 @@ def test_argument_errors():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_ranks_exchange_through_peer_memory(tmp_path):
+@pytest.mark.parametrize("per_cta", [0, 1])
+def test_two_ranks_exchange_through_peer_memory(tmp_path, per_cta):
     """Two processes, one per GPU: every rank must end up with the full output of each forward,
-    bit-identical to a single-GPU forward of the unsharded layer (checked inside the workers)."""
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    bit-identical to a single-GPU forward of the unsharded layer (checked inside the workers).  Both signalling
+    forms of the exchange: the grid's last CTA raises a flag (0), every CTA counts itself in on the peers (1)."""
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT, ORTHO_B200_TEST_PER_CTA=str(per_cta))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
-           "--master-addr", "127.0.0.1", "--master-port", "29741",
+           "--master-addr", "127.0.0.1", "--master-port", str(29741 + per_cta),
            os.path.join(ROOT, "tests", "peer_gather_worker.py"), str(tmp_path)]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=420)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
