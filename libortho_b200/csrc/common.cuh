@@ -101,6 +101,17 @@ __device__ __forceinline__ void ortho_entry(const OrthoView &ov, int e, int K, i
     }
 }
 
+// Scale of a row's weight corrections: a sparse entry v of row n enters the weight tile as v * alpha / scale[n]
+// (the epilogue multiplies the whole row by scale[n]).  Returns 0 when that cannot be represented safely in
+// FP16 next to the integer weights (tiny or zero scale, huge values, NaN): such a row keeps the gather path.
+// Converters and epilogue warps evaluate this independently and must agree, hence one function.
+__device__ __forceinline__ float patch_rscale(float alpha, float scale, float row_max)
+{
+    const float r = __fdiv_rn(alpha, scale);
+    const float top = __fmul_rn(row_max, fabsf(r));
+    return (top <= 16384.f && fabsf(r) <= 3.0e38f && r != 0.f) ? r : 0.f;     // NaN and infinity fail the comparisons
+}
+
 // ---- INT4 -> FP16 in registers ------------------------------------------------------------------
 // One 32-bit word holds 8 consecutive elements e0..e7 (e_i in bits [4i, 4i+4), low nibble = even
 // element; src/ortho.c:315-320).  A nibble r is a 4-bit two's complement integer s (:321-323);

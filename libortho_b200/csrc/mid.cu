@@ -26,8 +26,13 @@
 // reproducible), in its epilogue.  A share's only partial piece is processed first and the piece that collects
 // partials last, so the bounded flag wait does not normally wait at all.
 //
-// The sparse term is computed ahead into O[m][n] (token-major FP32, in the workspace) by ortho_tokens_kernel
-// from the once-transposed activations (a warp per 8 weight rows, lanes = tokens) and added in the FP32 epilogue.
+// The sparse term.  With a plan whose rows are in column order and that lists no long rows, the converters fold it
+// into the weight tile: each converter thread walks the entries of its row along K and adds v * alpha / scale[n] (FP16)
+// to the weights it has just written to shared memory, so the MMAs compute base and sparse term together; a row
+// whose corrections FP16 cannot hold (zero or tiny scale, huge values) is gathered from x by the epilogue thread of
+// each token (rare).  Otherwise it is computed ahead into O[m][n] (token-major FP32, in the workspace) by
+// ortho_tokens_kernel from the once-transposed activations (a warp per 8 weight rows, lanes = tokens) and added in
+// the FP32 epilogue.
 #include <cstring>
 
 #include "common.cuh"
@@ -73,6 +78,9 @@ struct Params {
     float *slots; int *flags;   // slots[2 * cta + which][mrows][256] (which = 0: sums handed to another CTA, 1: this
                                 // CTA's own sums of a tile it finishes), flags[cta]
     const float *o; float alpha; int has_ortho;    // O[m][n], row pitch N
+    // patch != 0 (a plan with ordered rows and no long rows): the converters add the sparse entries to the weight tile
+    // (v * alpha / scale[n], FP16) instead; rows that FP16 cannot hold are gathered from x by the epilogue
+    int patch; OrthoView ov; const float *row_max; const __half *x;
     int *status;
     int gather;
     GatherView gv;
@@ -85,6 +93,7 @@ struct Smem {
     uint64_t d_full[2], d_empty[2];
     uint32_t tmem_base;
     float sc[TN], bs[TN];
+    alignas(16) unsigned char fb[TN];    // patch mode: 1 = this row of the tile is gathered by the epilogue
 };
 constexpr size_t kSmemBytes = 1024 + (size_t)kSmemData + sizeof(Smem) + 256;
 
@@ -195,7 +204,44 @@ mid_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
         const uint32_t swz = (uint32_t)(row & 7);
         int wi = 0, bi = 0; uint32_t wph = 0, bph = 0;
         long long pos = r_begin; Seg sg;
+        // Patch mode: this thread walks the sparse entries of its weight row in column order along the k blocks (both
+        // threads of a row walk all of them, each applies those of its own 32 k), a window of four packed entries in
+        // registers.  Only a share's first piece can start inside a row (kb0 > 0): one binary search per CTA, under
+        // the ramp-up of the weight pipeline; the row's extent, scale and largest value for the next piece (the next
+        // tile) are fetched a piece ahead.
+        int nx_e0 = 0, nx_e1 = 0; float nx_sc = 0.f, nx_rm = 0.f;
+        auto fetch_row = [&](int t) {
+            nx_e0 = nx_e1 = 0; nx_sc = 0.f; nx_rm = 0.f;
+            const int n = t * TN + row;
+            if (t < p.tiles_n && n < p.N) {
+                nx_e0 = p.ov.row_ptr[n]; nx_e1 = p.ov.row_ptr[n + 1];
+                nx_sc = __half2float(p.scales[n]); nx_rm = p.row_max[n];
+            }
+        };
+        if (p.patch && r_begin < r_end) fetch_row((int)(r_begin / p.kblocks));
         while (next_seg(pos, sg)) {
+            int e_cur = 0, e_end = 0; float rsc = 0.f;
+            uint32_t q0 = 0, q1 = 0, q2 = 0, q3 = 0;
+            if (p.patch) {
+                if (nx_e1 > nx_e0) {
+                    rsc = patch_rscale(p.alpha, nx_sc, nx_rm);
+                    if (rsc != 0.f) { e_cur = nx_e0; e_end = nx_e1; }
+                }
+                fetch_row(sg.t + 1);
+                if (sg.kb0 > 0 && e_cur < e_end) {           // first entry at or past the piece's first column
+                    int lo = e_cur, hi = e_end;
+                    const uint32_t c0 = (uint32_t)(sg.kb0 * KB);
+                    while (lo < hi) {
+                        const int mid2 = (lo + hi) >> 1;
+                        if ((p.ov.entries[mid2] & 0xFFFFu) < c0) lo = mid2 + 1; else hi = mid2;
+                    }
+                    e_cur = lo;
+                }
+                if (e_cur < e_end) q0 = p.ov.entries[e_cur];
+                if (e_cur + 1 < e_end) q1 = p.ov.entries[e_cur + 1];
+                if (e_cur + 2 < e_end) q2 = p.ov.entries[e_cur + 2];
+                if (e_cur + 3 < e_end) q3 = p.ov.entries[e_cur + 3];
+            }
             for (int kb = sg.kb0; kb < sg.kb1; kb++) {
                 const int sub = kb % WKB;
                 if (sub == 0 || kb == sg.kb0) wait(&sm->w_full[wi], wph);
@@ -215,6 +261,21 @@ mid_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
 #pragma unroll
                 for (int j = 0; j < 4; j++)
                     *reinterpret_cast<uint4 *>(brow + ((((uint32_t)(4 * half + j)) ^ swz) << 4)) = make_uint4(o[j][0], o[j][1], o[j][2], o[j][3]);
+                if (p.patch) {
+                    // entries of this row inside the k block: w_int + v * alpha / scale, as FP16, in the tile just written
+                    const int kend = (kb + 1) * KB;
+                    while (e_cur < e_end && (int)(q0 & 0xFFFFu) < kend) {
+                        const uint32_t c = (q0 & 0xFFFFu) - (uint32_t)(kb * KB);
+                        if ((int)(c >> 5) == half) {
+                            __half *hp = reinterpret_cast<__half *>(brow + (((c >> 3) ^ swz) << 4)) + (c & 7u);
+                            const float d = __half2float(__ushort_as_half((unsigned short)(q0 >> 16))) * rsc;
+                            *hp = __hadd(*hp, __float2half_rn(d));
+                        }
+                        e_cur++;
+                        q0 = q1; q1 = q2; q2 = q3;
+                        q3 = (e_cur + 3 < e_end) ? p.ov.entries[e_cur + 3] : 0u;
+                    }
+                }
                 fence_proxy_async();                     // the tensor core reads shared memory through the async proxy
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sm->b_full[bi]);
@@ -229,6 +290,17 @@ mid_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
         const bool warp_on = q * 32 < p.M;               // this warp's lanes hold real tokens
         const bool vec_ok = (p.ldy % 8) == 0 && (reinterpret_cast<uintptr_t>(p.y) & 15u) == 0;
         const int nranks = p.gather ? p.gv.world : 1;
+        // patch mode, a row the converters could not fold: its sparse sum for one token, straight from x
+        auto gathered = [&](int n, int m) -> float {
+            float acc = 0.f;
+            const int e0 = p.ov.row_ptr[n], e1 = p.ov.row_ptr[n + 1];
+            for (int e = e0; e < e1; e++) {
+                int c; float v;
+                ortho_entry(p.ov, e, p.K, c, v);
+                acc = fmaf(v, __half2float(p.x[(size_t)m * p.K + c]), acc);
+            }
+            return acc;
+        };
         long long pos = r_begin; Seg sg; int it = 0;
         while (next_seg(pos, sg)) {
             const int a = it & 1;
@@ -244,8 +316,14 @@ mid_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
             if (owner) {
                 for (int i = et; i < TN; i += EPI_WARPS * 32) {
                     const int n = n0 + i;
-                    sm->sc[i] = n < p.N ? __half2float(p.scales[n]) : 0.f;
+                    const float scn = n < p.N ? __half2float(p.scales[n]) : 0.f;
+                    sm->sc[i] = scn;
                     sm->bs[i] = (p.bias && n < p.N) ? p.bias[n] : 0.f;
+                    unsigned char f = 0;
+                    if (p.patch && n < p.N && p.ov.row_ptr[n + 1] > p.ov.row_ptr[n] &&
+                        patch_rscale(p.alpha, scn, p.row_max[n]) == 0.f)
+                        f = 1;                       // the converters leave this row's entries alone: gathered below
+                    sm->fb[i] = f;
                 }
             }
             if (!dead) {                                 // a long wait (a whole piece of MMAs): poll with pauses
@@ -323,6 +401,11 @@ mid_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
                             for (int j = 0; j < 4; j++)
                                 if (n + j < p.N) v[j] = fmaf(p.alpha, p.o[(size_t)m * p.N + n + j], v[j]);
                         }
+                        if (p.patch && *reinterpret_cast<const uint32_t *>(&sm->fb[c4]) != 0u) {
+#pragma unroll
+                            for (int j = 0; j < 4; j++)
+                                if (sm->fb[c4 + j]) v[j] = fmaf(p.alpha, gathered(n + j, m), v[j]);
+                        }
                         const __half2 h01 = __floats2half2_rn(v[0], v[1]), h23 = __floats2half2_rn(v[2], v[3]);
                         const size_t at = (size_t)m * (size_t)p.ldy + n;
                         for (int rk = 0; rk < nranks; rk++) {
@@ -368,6 +451,15 @@ mid_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
 #pragma unroll
                                 for (int j = 0; j < 32; j++)
                                     if (nc + j < p.N) v[j] = fmaf(p.alpha, orow[j], v[j]);
+                            }
+                        }
+                        if (p.patch) {
+                            const uint4 *fw = reinterpret_cast<const uint4 *>(&sm->fb[c * 32]);
+                            const uint4 f0 = fw[0], f1 = fw[1];
+                            if ((f0.x | f0.y | f0.z | f0.w | f1.x | f1.y | f1.z | f1.w) != 0u) {
+#pragma unroll
+                                for (int j = 0; j < 32; j++)
+                                    if (sm->fb[c * 32 + j]) v[j] = fmaf(p.alpha, gathered(nc + j, tok), v[j]);
                             }
                         }
                         uint32_t h[16];
@@ -551,7 +643,11 @@ int launch_mid(const FwdArgs &a)
     p.alpha = a.alpha; p.has_ortho = 0; p.o = nullptr;
     p.status = kernel_status_word();
     if (!p.status) return ORTHO_B200_ERR_CUDA;
-    if (a.has_ortho) {
+    if (a.has_ortho && a.plan && a.ortho.entries && a.plan->ordered && a.plan->row_max && a.plan->n_long == 0 &&
+        tuning_snapshot().patch_weights) {
+        // the sparse entries are folded into the weight tile by the converters: no transposed activations, no O
+        p.patch = 1; p.ov = a.ortho; p.row_max = a.plan->row_max; p.x = a.x;
+    } else if (a.has_ortho) {
         const int Mp = (int)mid_mp(a.M);
         int st = launch_transpose_x(a.x, xt, (int)a.M, (int)a.K, Mp, a.stream);
         if (st != ORTHO_B200_OK) return st;

@@ -135,16 +135,6 @@ constexpr int DL_BYTES = TN * KB * 2;     // 16 KB: one row of 64 FP16 weight co
 constexpr size_t kSmemBytes = 1024 + (size_t)STAGES * X_BYTES + (size_t)WSTAGES * W_BYTES + NH * ESETS * YS_BYTES + DL_BYTES + sizeof(Smem) + 256;
 static_assert(kSmemBytes <= 232448, "shared memory per CTA");
 
-// Scale of a row's weight corrections: a sparse entry v of row n enters the weight tile as v * alpha / scale[n]
-// (the epilogue multiplies the whole row by scale[n]).  Returns 0 when that cannot be represented safely in
-// FP16 next to the integer weights (tiny or zero scale, huge values, NaN): such a row keeps the gather path.
-// Converters and epilogue warps evaluate this independently and must agree, hence one function.
-__device__ __forceinline__ float patch_rscale(float alpha, float scale, float row_max)
-{
-    const float r = __fdiv_rn(alpha, scale);
-    const float top = __fmul_rn(row_max, fabsf(r));
-    return (top <= 16384.f && fabsf(r) <= 3.0e38f && r != 0.f) ? r : 0.f;     // NaN and infinity fail the comparisons
-}
 }  // namespace pf
 
 __global__ void __launch_bounds__(pf::NWARPS * 32, 1)

@@ -542,3 +542,45 @@ def test_rows_that_cannot_be_folded_keep_the_gather_path(oracle_mod):
     y2 = run_layer(rev.to(DEV), x.to(DEV), 1.0)
     assert _lib.lib().ortho_b200_query_kernel_status() == 0
     assert_close(y2.float().cpu().numpy(), ref, "plan with unordered rows")
+
+
+@pytest.mark.parametrize("M,K,N,d", [(32, 1024, 520, 0.01), (100, 4096, 300, 0.003), (128, 2048, 1100, 0.02), (48, 8192, 2048, 0.003)])
+def test_tokens_as_m_kernel_folds_the_sparse_term(oracle_mod, M, K, N, d):
+    """25..128 tokens with a plan and a workspace: the tokens-as-M kernel adds the sparse entries to its weight tile
+    (one launch, shares that start inside a row), gathers the rows whose scale is zero or tiny in its epilogue, and
+    agrees with the oracle and with the gather form (transpose + sparse pre-pass + the MMA kernel)."""
+    layer = wl.make_layer(K, N, d, seed=900 + M)
+    scales = layer.base_scales.clone()
+    counts = layer.row_ptr[1:] - layer.row_ptr[:-1]
+    special = [r for r in (3, 255, 256, N - 1) if int(counts[r]) > 0]
+    assert special
+    for i, r in enumerate(special):
+        scales[r] = 0.0 if i % 2 == 0 else 1e-6
+    layer = wl.Layer(K, N, layer.base_weight, scales, layer.row_ptr, layer.col, layer.vals, 1.0)
+    ld = layer.to(DEV)
+    x = wl.make_input(M, K, seed=900 + M)
+    plan = _C_ops.Plan(ld.row_ptr, ld.col, ld.vals, K, N)
+    assert plan.rows_ordered
+    ws = torch.empty(_C_ops.workspace_bytes(M, K, N, plan), dtype=torch.uint8, device=DEV)
+    ref = layer_oracle(oracle_mod, layer, x, 0.75)
+
+    def run():
+        y = torch.empty(M, N, dtype=torch.float16, device=DEV)
+        n0 = _lib.lib().ortho_b200_launch_count()
+        _C_ops.forward(ld.base_weight, ld.base_scales, ld.vals, ld.col, ld.row_ptr, x.to(DEV), y, 0.75, plan=plan, workspace=ws)
+        torch.cuda.synchronize()
+        return y, _lib.lib().ortho_b200_launch_count() - n0
+
+    try:
+        assert _lib.lib().ortho_b200_set_decode_config(-4, 0, 0, 128) == 0
+        ya, la = run()
+        _force_gathers(True)
+        yb, lb = run()
+    finally:
+        _force_gathers(False)
+        _lib.lib().ortho_b200_set_decode_config(-4, 0, 0, 0)
+    assert _lib.lib().ortho_b200_query_kernel_status() == 0
+    assert (la, lb) == (1, 3)
+    assert bool(torch.isfinite(ya).all())
+    assert_close(ya.float().cpu().numpy(), ref, f"tokens-as-M folded M={M} {K}->{N}")
+    assert_close(yb.float().cpu().numpy(), ref, f"tokens-as-M gathered M={M} {K}->{N}")
