@@ -91,6 +91,7 @@ struct Smem {
     uint64_t x_full[XST_MAX], x_empty[XST_MAX];
     uint64_t b_full[BST], b_empty[BST];
     uint64_t d_full[2], d_empty[2];
+    uint64_t fin_bar;           // bulk copies of partial-sum slots into shared memory (the collecting piece)
     uint32_t tmem_base;
     float sc[TN], bs[TN];
     alignas(16) unsigned char fb[TN];    // patch mode: 1 = this row of the tile is gathered by the epilogue
@@ -120,6 +121,7 @@ mid_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
         for (int s = 0; s < XST_MAX; s++) { mbar_init(&sm->x_full[s], 1); mbar_init(&sm->x_empty[s], 1); }
         for (int s = 0; s < BST; s++) { mbar_init(&sm->b_full[s], CONV_WARPS); mbar_init(&sm->b_empty[s], 1); }
         for (int s = 0; s < 2; s++) { mbar_init(&sm->d_full[s], 1); mbar_init(&sm->d_empty[s], EPI_WARPS); }
+        mbar_init(&sm->fin_bar, 1);
         fence_mbar_init();
         prefetch_tensormap(&xmap);
         prefetch_tensormap(&wmap);
@@ -372,26 +374,56 @@ mid_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
                 } else {
                     // the tile's pieces are added in CTA order (this CTA's first) by all epilogue threads: a unit is
                     // one token x 4 consecutive weight rows, consecutive threads take consecutive units
-                    const int units = p.M * (TN / 4);
+                    // The slots (this CTA's own first, then the contributors') are brought into shared memory 32 token
+                    // rows at a time by bulk copies -- the pipeline stages are idle by now: the piece that collects
+                    // partial sums is the last of a CTA's share -- and added from there.
+                    const int ncon = c_last - c_first + 1;
+                    constexpr int kFinRows = 32;
+                    constexpr uint32_t kFinBytes = kFinRows * TN * 4;            // one slot, one group of rows: 32 KB
+                    const bool staged = (size_t)(1 + ncon) * kFinBytes <= (size_t)kSmemData && !dead;
+                    const float4 *fs4 = reinterpret_cast<const float4 *>(base);
+                    const size_t cstride = (size_t)2 * p.mrows * TN;
+                    for (int r0 = 0; r0 < p.mrows && r0 < p.M; r0 += kFinRows) {
+                    if (staged) {
+                        if (et == 0) {
+                            asm volatile("fence.proxy.async;" ::: "memory");   // the slots were written through the generic proxy
+                            mbar_arrive_expect_tx(&sm->fin_bar, (uint32_t)(1 + ncon) * kFinBytes);
+                            bulk_load_1d(base, p.slots + ((size_t)(2 * cta + 1) * p.mrows + r0) * TN, kFinBytes, &sm->fin_bar);
+                            for (int s2 = 0; s2 < ncon; s2++)
+                                bulk_load_1d(base + (size_t)(1 + s2) * kFinBytes,
+                                             p.slots + ((size_t)(2 * (c_first + s2)) * p.mrows + r0) * TN, kFinBytes, &sm->fin_bar);
+                        }
+                        wait(&sm->fin_bar, (uint32_t)((r0 / kFinRows) & 1));
+                    }
+                    const int rows_here = p.M - r0 < kFinRows ? p.M - r0 : kFinRows;
+                    const int units = rows_here * (TN / 4);
                     for (int u = et; u < units; u += EPI_WARPS * 32) {
-                        const int m = u / (TN / 4), c4 = (u % (TN / 4)) * 4;
+                        const int m = r0 + u / (TN / 4), c4 = (u % (TN / 4)) * 4;
                         const int n = n0 + c4;
                         if (n >= p.N) continue;
-                        const float *mine = p.slots + ((size_t)(2 * cta + 1) * p.mrows + m) * TN + c4;
-                        const float *theirs = p.slots + ((size_t)(2 * cta) * p.mrows + m) * TN + c4;     // + (cc - cta) * cstride
-                        const size_t cstride = (size_t)2 * p.mrows * TN;
-                        float4 acc = __ldcg(reinterpret_cast<const float4 *>(mine));
-                        int cc = c_first;
-                        for (; cc + 3 <= c_last; cc += 4) {            // four loads in flight, added in CTA order
-                            float4 t4[4];
+                        float4 acc;
+                        if (staged) {
+                            acc = fs4[u];
+                            for (int s2 = 0; s2 < ncon; s2++) {                  // added in CTA order
+                                const float4 t4 = fs4[(size_t)(1 + s2) * (kFinBytes / 16) + u];
+                                acc.x += t4.x; acc.y += t4.y; acc.z += t4.z; acc.w += t4.w;
+                            }
+                        } else {
+                            const float *mine = p.slots + ((size_t)(2 * cta + 1) * p.mrows + m) * TN + c4;
+                            const float *theirs = p.slots + ((size_t)(2 * cta) * p.mrows + m) * TN + c4;     // + (cc - cta) * cstride
+                            acc = __ldcg(reinterpret_cast<const float4 *>(mine));
+                            int cc = c_first;
+                            for (; cc + 3 <= c_last; cc += 4) {            // four loads in flight, added in CTA order
+                                float4 t4[4];
 #pragma unroll
-                            for (int i = 0; i < 4; i++) t4[i] = __ldcg(reinterpret_cast<const float4 *>(theirs + (size_t)(cc + i - cta) * cstride));
+                                for (int i = 0; i < 4; i++) t4[i] = __ldcg(reinterpret_cast<const float4 *>(theirs + (size_t)(cc + i - cta) * cstride));
 #pragma unroll
-                            for (int i = 0; i < 4; i++) { acc.x += t4[i].x; acc.y += t4[i].y; acc.z += t4[i].z; acc.w += t4[i].w; }
-                        }
-                        for (; cc <= c_last; cc++) {
-                            const float4 t4 = __ldcg(reinterpret_cast<const float4 *>(theirs + (size_t)(cc - cta) * cstride));
-                            acc.x += t4.x; acc.y += t4.y; acc.z += t4.z; acc.w += t4.w;
+                                for (int i = 0; i < 4; i++) { acc.x += t4[i].x; acc.y += t4[i].y; acc.z += t4[i].z; acc.w += t4[i].w; }
+                            }
+                            for (; cc <= c_last; cc++) {
+                                const float4 t4 = __ldcg(reinterpret_cast<const float4 *>(theirs + (size_t)(cc - cta) * cstride));
+                                acc.x += t4.x; acc.y += t4.y; acc.z += t4.z; acc.w += t4.w;
+                            }
                         }
                         float v[4] = {acc.x, acc.y, acc.z, acc.w};
 #pragma unroll
@@ -418,6 +450,8 @@ mid_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
                                 for (int j = 0; j < 4 && n + j < p.N; j++) dst[j] = hs[j];
                             }
                         }
+                    }
+                    if (staged) named_bar_sync(1, EPI_WARPS * 32);     // before the next rows overwrite the staging area
                     }
                 }
                 named_bar_sync(1, EPI_WARPS * 32);       // the staged scales are rewritten by the next piece
