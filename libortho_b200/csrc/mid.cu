@@ -52,7 +52,7 @@ constexpr int WKB = 4;                  // k blocks covered by one packed-weight
 constexpr int W_BYTES = TN * 128;       // 32 KB
 constexpr int X_BYTES = TMK * KB * 2;   // 16 KB: a full token stage (fewer tokens use smaller stages, see Params::xstage)
 constexpr int B_BYTES = TN * KB * 2;    // 32 KB
-constexpr int BST = 2;                  // converted-weight stages (the converters work one k block ahead of the MMAs)
+constexpr int BST = 3;                  // converted-weight stages (the converters work one k block ahead of the MMAs)
 constexpr int WST_MAX = 4, XST_MAX = 12;
 // The packed weights come from HBM: at the rate the tensor pipe can consume them (8 KB per ~0.4 us and SM) and a
 // loaded latency of 2-3 us, two 32 KB stages in flight per SM are the least that keeps the pipe fed, so the
