@@ -136,6 +136,15 @@ mid_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
         if (dead) return;
         if (!mbar_wait(bar, parity, 1u << 24)) { dead = true; atomicExch(p.status, 1); }
     };
+    // A converter warp waits with one polling lane (the warp shuffle hands the result and the ordering on to the
+    // others) when it has nothing else in flight: 6-7 % faster than 512 threads polling one word.  With the sparse
+    // entries folded in (their loads in flight across the wait) all lanes polling measured 5 % faster, so that form
+    // keeps it.
+    auto wait_warp = [&](uint64_t *bar, uint32_t parity) {
+        if (p.patch) { wait(bar, parity); return; }
+        if (lane == 0) wait(bar, parity);
+        dead = __shfl_sync(0xffffffffu, (int)dead, 0) != 0;
+    };
     // the pieces of this CTA's share, in order: (row tile, k blocks [kb0, kb1))
     auto next_seg = [&](long long &pos, Seg &sg) -> bool {
         if (pos >= r_end) return false;
@@ -246,7 +255,7 @@ mid_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
             }
             for (int kb = sg.kb0; kb < sg.kb1; kb++) {
                 const int sub = kb % WKB;
-                if (sub == 0 || kb == sg.kb0) wait(&sm->w_full[wi], wph);
+                if (sub == 0 || kb == sg.kb0) wait_warp(&sm->w_full[wi], wph);
                 const unsigned char *wrow = ws + (size_t)wi * W_BYTES + row * 128;
                 const uint4 w0 = *reinterpret_cast<const uint4 *>(wrow + ((((uint32_t)(2 * sub + half)) ^ swz) << 4));
                 if (sub == WKB - 1 || kb == sg.kb1 - 1) {
@@ -258,7 +267,7 @@ mid_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
                 uint32_t o[4][4];
 #pragma unroll
                 for (int j = 0; j < 4; j++) int4x8_to_half2x4_natural(ww[j], o[j]);
-                wait(&sm->b_empty[bi], bph ^ 1u);
+                wait_warp(&sm->b_empty[bi], bph ^ 1u);
                 unsigned char *brow = bsm + (size_t)bi * B_BYTES + row * 128;
 #pragma unroll
                 for (int j = 0; j < 4; j++)
