@@ -389,23 +389,43 @@ mid_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
                     const int ncon = c_last - c_first + 1;
                     constexpr int kFinRows = 32;
                     constexpr uint32_t kFinBytes = kFinRows * TN * 4;            // one slot, one group of rows: 32 KB
-                    const bool staged = (size_t)(1 + ncon) * kFinBytes <= (size_t)kSmemData && !dead;
-                    const float4 *fs4 = reinterpret_cast<const float4 *>(base);
+                    // (a tile cut into more pieces than fit takes several passes: the running sums stay in the first
+                    // buffer, every pass brings the next contributors in beside it)
+                    constexpr int kGroup = kSmemData / (int)kFinBytes - 1;       // contributors per pass
+                    const bool staged = !dead;
+                    float4 *fs4 = reinterpret_cast<float4 *>(base);
                     const size_t cstride = (size_t)2 * p.mrows * TN;
+                    uint32_t fin_phase = 0;
                     for (int r0 = 0; r0 < p.mrows && r0 < p.M; r0 += kFinRows) {
-                    if (staged) {
-                        if (et == 0) {
-                            asm volatile("fence.proxy.async;" ::: "memory");   // the slots were written through the generic proxy
-                            mbar_arrive_expect_tx(&sm->fin_bar, (uint32_t)(1 + ncon) * kFinBytes);
-                            bulk_load_1d(base, p.slots + ((size_t)(2 * cta + 1) * p.mrows + r0) * TN, kFinBytes, &sm->fin_bar);
-                            for (int s2 = 0; s2 < ncon; s2++)
-                                bulk_load_1d(base + (size_t)(1 + s2) * kFinBytes,
-                                             p.slots + ((size_t)(2 * (c_first + s2)) * p.mrows + r0) * TN, kFinBytes, &sm->fin_bar);
-                        }
-                        wait(&sm->fin_bar, (uint32_t)((r0 / kFinRows) & 1));
-                    }
                     const int rows_here = p.M - r0 < kFinRows ? p.M - r0 : kFinRows;
                     const int units = rows_here * (TN / 4);
+                    int nb = ncon;                                               // contributors beside the running sums in this pass
+                    if (staged) {
+                        for (int done = 0;; done += nb) {
+                            nb = ncon - done < kGroup ? ncon - done : kGroup;
+                            if (et == 0) {
+                                asm volatile("fence.proxy.async;" ::: "memory");   // the slots were written through the generic proxy
+                                mbar_arrive_expect_tx(&sm->fin_bar, (uint32_t)((done == 0 ? 1 : 0) + nb) * kFinBytes);
+                                if (done == 0)
+                                    bulk_load_1d(base, p.slots + ((size_t)(2 * cta + 1) * p.mrows + r0) * TN, kFinBytes, &sm->fin_bar);
+                                for (int s2 = 0; s2 < nb; s2++)
+                                    bulk_load_1d(base + (size_t)(1 + s2) * kFinBytes,
+                                                 p.slots + ((size_t)(2 * (c_first + done + s2)) * p.mrows + r0) * TN, kFinBytes, &sm->fin_bar);
+                            }
+                            wait(&sm->fin_bar, fin_phase & 1u);
+                            fin_phase++;
+                            if (done + nb >= ncon) break;                          // the last pass is finished off below
+                            for (int u = et; u < units; u += EPI_WARPS * 32) {
+                                float4 acc = fs4[u];
+                                for (int s2 = 0; s2 < nb; s2++) {                  // added in CTA order
+                                    const float4 t4 = fs4[(size_t)(1 + s2) * (kFinBytes / 16) + u];
+                                    acc.x += t4.x; acc.y += t4.y; acc.z += t4.z; acc.w += t4.w;
+                                }
+                                fs4[u] = acc;
+                            }
+                            named_bar_sync(1, EPI_WARPS * 32);                     // before the next pass overwrites the contributors
+                        }
+                    }
                     for (int u = et; u < units; u += EPI_WARPS * 32) {
                         const int m = r0 + u / (TN / 4), c4 = (u % (TN / 4)) * 4;
                         const int n = n0 + c4;
@@ -413,7 +433,7 @@ mid_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
                         float4 acc;
                         if (staged) {
                             acc = fs4[u];
-                            for (int s2 = 0; s2 < ncon; s2++) {                  // added in CTA order
+                            for (int s2 = 0; s2 < nb; s2++) {                    // added in CTA order
                                 const float4 t4 = fs4[(size_t)(1 + s2) * (kFinBytes / 16) + u];
                                 acc.x += t4.x; acc.y += t4.y; acc.z += t4.z; acc.w += t4.w;
                             }
@@ -720,8 +740,13 @@ int launch_mid(const FwdArgs &a)
         OB_CUDA(cudaFuncSetAttribute(mid_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
         attr_set[dev] = true;
     }
-    long long grid = p.total < num_sms ? p.total : num_sms;
+    // every CTA gets at least kMinShare k blocks: a narrow layer cut into shares of a few k blocks would spend its time
+    // adding dozens of partial tiles
+    constexpr long long kMinShare = 16;
+    long long grid = (p.total + kMinShare - 1) / kMinShare;
+    if (grid > num_sms) grid = num_sms;
     if (grid > kMidMaxSms) grid = kMidMaxSms;
+    if (grid < 1) grid = 1;
     OB_CUDA(cudaMemsetAsync(flags, 0, (size_t)grid * sizeof(int), a.stream));
     mid_kernel<<<(unsigned)grid, NWARPS * 32, kSmemBytes, a.stream>>>(xmap, wmap, p);
     count_launch();
