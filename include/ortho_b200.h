@@ -108,16 +108,19 @@ ORTHO_B200_API int ortho_b200_dequant_dump(const void *q_weight, const void *q_s
  * torch_bind/ortho_linear.py:142-151); same argument order and meaning, plus explicit sizes,
  * the optional plan, a caller-owned workspace and the stream.
  *
- *   M <= 24   : memory-bound streaming kernels (ORTHO_B200_DECODE_MAX_M is the most they accept);
- *               also M <= 32 with N <= 4096 and M <= 64 with N <= 1024 while N * K <= 4096 * 8192 (too few
- *               row tiles to fill the GPU with a tensor-core kernel).  No global scratch.
+ *   M <= 24   : memory-bound streaming kernels (ORTHO_B200_DECODE_MAX_M is the most they accept); also
+ *               M <= 32 on layers of at most 4096 x 4096 weights, and, for calls without a workspace, M <= 32 with
+ *               N <= 4096 and M <= 64 with N <= 1024 while N * K <= 4096 * 8192.  No global scratch.
  *   25 .. 128 : tcgen05 kernel with the token block as the MMA's M operand (256 weight rows per instruction),
  *               taken when the call brings ortho_b200_workspace_bytes(M, K, N) bytes of workspace, whatever alpha
- *               is; without it the call runs the kernel of the neighbouring regime.
+ *               is; without it the call runs the kernel of the neighbouring regime.  With a plan whose rows are in
+ *               column order and that lists no long rows, the sparse entries are folded into its weight tile.
  *   larger M  : tcgen05 / TMEM prefill kernel (weight tile as the M operand).  With an active ortho term
- *               (alpha > 0 and nnz > 0) it needs the workspace (transposed activations; with a plan, the sums of
- *               its long rows) and returns ERR_WORKSPACE without; otherwise the workspace is optional (split-K
- *               of the last wave).
+ *               (alpha > 0 and nnz > 0) and a plan whose rows are in column order the entries are folded into the
+ *               weight tile, and the workspace only has to hold the tensor-core pre-pass sums of the plan's long
+ *               rows, if it lists any; without such a plan the kernel gathers the term and needs the workspace for
+ *               the transposed activations.  Missing workspace that is needed: ERR_WORKSPACE.  Otherwise the
+ *               workspace is optional (split-K of the last wave).
  * Size the workspace with ortho_b200_workspace_bytes / ortho_b200_plan_workspace_bytes and pass it, 256-byte
  * aligned, whenever that is not 0.  The first forward of a kernel variant on a device sets function attributes:
  * issue it outside any stream capture.
