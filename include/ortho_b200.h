@@ -117,10 +117,10 @@ ORTHO_B200_API int ortho_b200_dequant_dump(const void *q_weight, const void *q_s
  *               column order and that lists no long rows, the sparse entries are folded into its weight tile.
  *   larger M  : tcgen05 / TMEM prefill kernel (weight tile as the M operand).  With an active ortho term
  *               (alpha > 0 and nnz > 0) and a plan whose rows are in column order the entries are folded into the
- *               weight tile, and the workspace only has to hold the tensor-core pre-pass sums of the plan's long
- *               rows, if it lists any; without such a plan the kernel gathers the term and needs the workspace for
- *               the transposed activations.  Missing workspace that is needed: ERR_WORKSPACE.  Otherwise the
- *               workspace is optional (split-K of the last wave).
+ *               weight tile, and the workspace is needed only when the plan lists long rows (their tensor-core
+ *               pre-pass sums; same size and layout as below); without such a plan the kernel gathers the term and
+ *               needs the workspace for the transposed activations.  Missing workspace that is needed:
+ *               ERR_WORKSPACE.  Otherwise the workspace is optional (split-K of the last wave).
  * Size the workspace with ortho_b200_workspace_bytes / ortho_b200_plan_workspace_bytes and pass it, 256-byte
  * aligned, whenever that is not 0.  The first forward of a kernel variant on a device sets function attributes:
  * issue it outside any stream capture.
