@@ -64,6 +64,7 @@ class ShardedOrthoLinear(nn.Module):
         self._comm = None
         self._comm_max_m = 0
         self._slot = 0
+        self._peer_bound = {}
 
     @classmethod
     def from_full(cls, full: OrthoLinear, group=None, align: int = 16, local_forward=None) -> "ShardedOrthoLinear":
@@ -90,27 +91,68 @@ class ShardedOrthoLinear(nn.Module):
                 comm.connect_group(self.group)
             offset_bytes = 0
         self._comm, self._comm_off, self._comm_max_m = comm, offset_bytes, max_tokens
+        self._peer_bound = {}
 
     @staticmethod
     def peer_gather_bytes(max_tokens: int, out_features: int) -> int:
         return 2 * ((2 * max_tokens * out_features + 255) // 256 * 256)
 
     def _forward_peer(self, x2: torch.Tensor) -> torch.Tensor:
+        """The shard's forward with the peer-store exchange.  Everything that does not change from call to call (buffer
+        pointers, plan, workspace, the two output views) is bound once per token count and reused, like
+        ``OrthoLinear`` does for its own forward."""
         from . import _C_ops as _C
+        from . import _lib
+        from .ortho_linear import _SharedWorkspace, _current_stream_handle
         M = x2.shape[0]
         if M > self._comm_max_m:
             raise ValueError(f"peer gather was sized for {self._comm_max_m} tokens, got {M}")
+        if not x2.is_cuda:
+            raise RuntimeError("libortho_b200 has no CPU path: the input must be a CUDA tensor")
         if x2.dtype != torch.float16:
             x2 = x2.to(torch.float16)
-        off = self._comm_off + self._slot * self._region
-        self._slot ^= 1
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
         loc = self.local
-        has = loc.alpha > 0 and loc.ortho_values.numel() > 0
-        return _C.forward_gather(loc.base_weight, loc.base_scales, loc.ortho_values, loc.ortho_col_indices,
-                                 loc.ortho_row_ptr, x2.contiguous(), loc.alpha, self._comm, off,
-                                 self.out_features, self.n0,
-                                 plan=loc._get_plan() if has else None,
-                                 workspace=loc._get_workspace(M) if self.n1 > self.n0 else None)
+        dev = x2.device
+        alpha = float(loc.alpha)
+        b = self._peer_bound.get(M)
+        if b is None or b["key"] != (alpha > 0, loc._versions(), id(self._comm), self._comm_off) or b["ws_gen"] != b["ws"].gen:
+            rows = self.n1 - self.n0
+            nnz = int(loc.ortho_values.numel())
+            if rows and (loc.base_weight.dtype != torch.uint8 or loc.base_scales.dtype != torch.float16
+                         or tuple(loc.base_weight.shape) != (rows, self.in_features // 2)):
+                raise ValueError("the shard's base_weight / base_scales do not match its rows")
+            plan = loc._get_plan() if (alpha > 0 and nnz > 0) else None
+            need = _C.workspace_bytes(M, self.in_features, rows, plan) if rows else 0
+            ws = _SharedWorkspace.get(dev, need)
+            b = {
+                "key": (alpha > 0, loc._versions(), id(self._comm), self._comm_off), "ws": ws, "ws_gen": ws.gen,
+                "head": (loc.base_weight.data_ptr() if rows else None, loc.base_scales.data_ptr() if rows else None,
+                         loc.ortho_values.data_ptr() if nnz else None, loc.ortho_col_indices.data_ptr() if nnz else None,
+                         loc.ortho_row_ptr.data_ptr() if nnz else None, nnz),
+                "tail": (plan.handle if plan is not None else None, ws.tensor.data_ptr() if need else None,
+                         ws.tensor.numel() if need else 0, self._comm.handle),
+                "plan": plan,
+                "off": [self._comm_off + s * self._region for s in (0, 1)],
+                "out": [self._comm.output(self._comm_off + s * self._region, M, self.out_features) for s in (0, 1)],
+            }
+            if len(self._peer_bound) > 32:
+                self._peer_bound.clear()
+            self._peer_bound[M] = b
+        slot = self._slot
+        self._slot ^= 1
+        fwd = _lib.lib().ortho_b200_forward_gather
+        args = (*b["head"], x2.data_ptr(), M, self.in_features, self.n1 - self.n0, alpha, *b["tail"],
+                b["off"][slot], self.out_features, self.n0)
+        if torch.cuda.current_device() == dev.index:
+            st = fwd(*args, _current_stream_handle(dev))
+        else:
+            with torch.cuda.device(dev):
+                st = fwd(*args, _current_stream_handle(dev))
+        if st:
+            _lib.check(st, "ortho_b200_forward_gather")
+        return b["out"][slot]
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         lead = x.shape[:-1]
