@@ -42,7 +42,7 @@
 namespace ob {
 
 int *kernel_status_word();
-int launch_transpose_x(const __half *x, __half *xt, int M, int K, int Mp, cudaStream_t stream);   // spmm.cu
+int launch_transpose_x(const __half *x, __half *xt, int M, int K, int Mp, cudaStream_t stream);   // transpose.cu
 
 namespace md {
 constexpr int TN = 256;                 // weight rows per tile (MMA N)

@@ -267,7 +267,7 @@ def test_tensor_core_path_base_only_against_oracle(oracle_mod, K, N, M):
 
 
 @pytest.mark.parametrize("kind,K,N,M,d,alpha,plan", [
-    ("zipf", 2048, 384, 300, 0.02, 0.5, True),      # rows longer than the SpMM's cooperative threshold
+    ("zipf", 2048, 384, 300, 0.02, 0.5, True),      # rows long enough for the plan's tensor-core pre-pass
     ("zipf", 2048, 384, 300, 0.02, 0.5, False),     # same through raw CSR (no plan)
     ("gauss", 1024, 520, 129, 0.01, 1.0, True),
     ("gauss", 4096, 256, 513, 0.003, 0.25, True),
@@ -298,7 +298,7 @@ def test_tensor_core_path_with_sparse_term_against_oracle(oracle_mod, kind, K, N
 @pytest.mark.parametrize("M", wl.CFG2_M)
 def test_prefill_configuration_at_its_own_shape(oracle_mod, M):
     """8192 x 8192, 0.1 % ortho with Zipf(1.2) row loads, alpha = 0.5, exactly as the benchmark builds it, with
-    plan and full workspace (long-row segments and the split-K of the last wave are both live): the longest
+    plan and full workspace (the long rows' tensor-core pre-pass and the split-K of the last wave are both live): the longest
     rows, tile-edge rows and a seeded row sample against the oracle for a seeded token sample."""
     K, N = wl.CFG2_SHAPE
     layer = wl.make_zipf_layer(K, N, wl.CFG2_DENSITY, seed=0, device=DEV, alpha=wl.CFG2_ALPHA)
@@ -584,3 +584,20 @@ def test_tokens_as_m_kernel_folds_the_sparse_term(oracle_mod, M, K, N, d):
     assert bool(torch.isfinite(ya).all())
     assert_close(ya.float().cpu().numpy(), ref, f"tokens-as-M folded M={M} {K}->{N}")
     assert_close(yb.float().cpu().numpy(), ref, f"tokens-as-M gathered M={M} {K}->{N}")
+
+
+def test_forward_into_a_caller_buffer():
+    """``OrthoLinear.forward(x, out=...)`` writes into the given FP16 buffer (a slice of a larger one) and returns a
+    view of it; the values equal the allocating call's."""
+    layer = wl.make_layer(1024, 272, 0.01, seed=5).to(DEV)
+    m = layer.to_module()
+    x = wl.make_input(7, 1024, seed=5).to(DEV)
+    big = torch.zeros(3 * 7 * 272, dtype=torch.float16, device=DEV)
+    out = big[7 * 272: 2 * 7 * 272]
+    y = m(x, out=out)
+    torch.cuda.synchronize()
+    assert y.data_ptr() == out.data_ptr() and tuple(y.shape) == (7, 272)
+    assert torch.equal(y, m(x))
+    assert float(big[:7 * 272].abs().max()) == 0.0 and float(big[2 * 7 * 272:].abs().max()) == 0.0
+    with pytest.raises(RuntimeError, match="out must be"):
+        m(x, out=big[:10])
