@@ -108,10 +108,10 @@ ORTHO_B200_API int ortho_b200_dequant_dump(const void *q_weight, const void *q_s
  * torch_bind/ortho_linear.py:142-151); same argument order and meaning, plus explicit sizes,
  * the optional plan, a caller-owned workspace and the stream.
  *
- *   M <= 24   : memory-bound streaming kernels (ORTHO_B200_DECODE_MAX_M is the most they accept); also
- *               M <= 32 on layers of at most 4096 x 4096 weights, and, for calls without a workspace, M <= 32 with
- *               N <= 4096 and M <= 64 with N <= 1024 while N * K <= 4096 * 8192.  No global scratch.
- *   25 .. 128 : tcgen05 kernel with the token block as the MMA's M operand (256 weight rows per instruction),
+ *   M <= 16   : memory-bound streaming kernels; also M <= 32 on layers of at most 4096 x 4096 weights, and, for
+ *               calls without a workspace, M <= 24, M <= 32 with N <= 4096 and M <= 64 with N <= 1024 while
+ *               N * K <= 4096 * 8192 (ORTHO_B200_DECODE_MAX_M is the most these kernels accept).  No global scratch.
+ *   17 .. 128 : tcgen05 kernel with the token block as the MMA's M operand (256 weight rows per instruction),
  *               taken when the call brings ortho_b200_workspace_bytes(M, K, N) bytes of workspace, whatever alpha
  *               is; without it the call runs the kernel of the neighbouring regime.  With a plan whose rows are in
  *               column order and that lists no long rows, the sparse entries are folded into its weight tile.

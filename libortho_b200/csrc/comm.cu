@@ -8,7 +8,7 @@
 //     ranks' buffers and its last CTA exchanges the completion flags -- one launch;
 //   * M > 24 (tcgen05 kernel): its epilogue stores every finished output tile into all ranks'
 //     buffers while the MMAs of the next tiles run, and its last CTA exchanges the flags -- one launch;
-//   * what is left (17..24 tokens, K not a multiple of 256): the compute kernel writes the local
+//   * what is left (17..32 tokens on small layers or without a workspace, K not a multiple of 256): the compute kernel writes the local
 //     buffer, gather_push_kernel copies the slice to the peers and exchanges the flags.
 // Peer memory is only ever touched by plain loads / stores of these kernels.
 // The reference has no multi-device path; the layer-level partition this serves is the row

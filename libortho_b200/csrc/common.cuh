@@ -43,9 +43,9 @@ struct Tuning {
     int stream_s = 0, stream_stages = 0;
     int prefill_above = 24;             // forwards with more tokens than this use the tensor-core kernels
     // forwards with mid_lo < tokens <= mid_hi use the tokens-as-M tensor-core kernel when they bring its workspace:
-    // built in, after the streaming kernels have had their pick (up to 24 tokens, and narrow layers); through the
+    // built in, above the streaming kernel's 16 tokens except on small layers up to 32 tokens; through the
     // hook, first (mid_first)
-    int mid_lo = 24, mid_hi = 128;
+    int mid_lo = 16, mid_hi = 128;
     bool mid_first = false;
     bool gather_per_cta = false;        // peer exchange: every CTA signals the peers itself instead of the grid's last CTA
     bool patch_weights = true;          // tensor-core kernels fold the sparse entries into the weight tile (plan with ordered rows)

@@ -296,13 +296,17 @@ bool mid_token_range(int64_t M)
 // Measured on one B200 (us, 0.3 % ortho, alpha = 1, folded sparse term): 32 tokens on 8192->8192 / 8192->10240 /
 // 8192->57344 / 28672->8192 take 49 / 54 / 183 / 107 with the tokens-as-M kernel against 95 / 108 / 370 / 218 with the
 // 128 x 256-token tile of prefill.cu; at 16 tokens the streaming kernel is level on the largest layer (205) and ahead
-// on K = 4096 layers (33 against 68 on 4096->22016), hence the built-in range (24, 128].
+// on K = 4096 layers (33 against 68 on 4096->22016).  From 17 tokens on the mma.sync kernel of this file falls behind
+// quickly (20 / 24 tokens: 8192->10240 113 / 147 against 51 / 52, 8192->57344 497 / 797 against 182, 11008->4096 50 / 54
+// against 43 / 44), hence the built-in range (16, 128].
 // Narrow layers (a GPU's shard of a layer, say), tokens-as-M kernel against the mma.sync kernel of this file:
 //   32 tokens: 8192->1024 39 / 25, 8192->1280 39 / 25, 4096->2048 34 / 17, 4096->4096 35 / 33, 11008->512 41 / 25, but
 //              8192->2560 40 / 48, 8192->4096 42 / 52, 28672->1024 66 / 107, 28672->2048 64 / 86;
 //   64 tokens: 8192->1024 53 / 63, 8192->1280 53 / 166, 8192->2560 54 / 109, 4096->4096 45 / 80, 4096->2048 44 / 117,
 //              28672->1024 98 / 175 (only 4096->1024 loses: 43 / 38).
-// So with its workspace the tokens-as-M kernel takes everything above 24 tokens except up to 32 tokens on layers of at
+//   17 .. 24 tokens on layers of at most 4096 x 4096 weights: the mma.sync kernel stays ahead (4096->4096 25-27 against
+//              31-33, 8192->2048 19-21 against 35-37, 4096->1024 13-14 against 31).
+// So with its workspace the tokens-as-M kernel takes everything above 16 tokens except up to 32 tokens on layers of at
 // most 4096 x 4096 weights; without the workspace the older rule between the mma.sync kernel and the prefill tile
 // (decode_regime_of) stands.
 Route route_of(int64_t M, int64_t N, int64_t K, const void *workspace, int64_t workspace_bytes)
@@ -311,7 +315,6 @@ Route route_of(int64_t M, int64_t N, int64_t K, const void *workspace, int64_t w
     const bool mid_ok = M > t.mid_lo && M <= t.mid_hi && M <= 128 && workspace && ((uintptr_t)workspace & 255u) == 0 &&
                         workspace_bytes >= mid_workspace_bytes(M, K, N);
     if (mid_ok && t.mid_first) return kRouteMid;
-    if (M <= t.prefill_above) return kRouteDecode;
     if (mid_ok) {
         if (t.prefill_above == kPrefillAboveBuiltin && M <= 32 && N * K <= (int64_t)4096 * 4096) return kRouteDecode;
         return kRouteMid;
@@ -335,7 +338,7 @@ int set_decode_config(int wr, int wk, int u, int s)
     if (wr == -4) {       // forwards with u < tokens <= s (s <= 128) use the tokens-as-M tensor-core kernel whatever the
                           // other rules say (u == s: never); u == s == 0 restores the built-in rule
         if (u < 0 || s < 0 || s > 128 || u > s) return ORTHO_B200_ERR_SHAPE;
-        if (u == 0 && s == 0) { t.mid_lo = 24; t.mid_hi = 128; t.mid_first = false; }
+        if (u == 0 && s == 0) { t.mid_lo = 16; t.mid_hi = 128; t.mid_first = false; }
         else { t.mid_lo = u; t.mid_hi = s; t.mid_first = true; }
         return ORTHO_B200_OK;
     }

@@ -546,7 +546,7 @@ def test_rows_that_cannot_be_folded_keep_the_gather_path(oracle_mod):
 
 @pytest.mark.parametrize("M,K,N,d", [(32, 1024, 520, 0.01), (100, 4096, 300, 0.003), (128, 2048, 1100, 0.02), (48, 8192, 2048, 0.003)])
 def test_tokens_as_m_kernel_folds_the_sparse_term(oracle_mod, M, K, N, d):
-    """25..128 tokens with a plan and a workspace: the tokens-as-M kernel adds the sparse entries to its weight tile
+    """17..128 tokens with a plan and a workspace: the tokens-as-M kernel adds the sparse entries to its weight tile
     (one launch, shares that start inside a row), gathers the rows whose scale is zero or tiny in its epilogue, and
     agrees with the oracle and with the gather form (transpose + sparse pre-pass + the MMA kernel)."""
     layer = wl.make_layer(K, N, d, seed=900 + M)
