@@ -490,7 +490,8 @@ def _force_gathers(on: bool):
     assert _lib.lib().ortho_b200_set_decode_config(-6, 0, 0, 0 if on else 1) == 0
 
 
-@pytest.mark.parametrize("K,N,M,d", [(1024, 520, 300, 0.01), (4096, 256, 513, 0.003), (2048, 384, 1500, 0.02)])
+@pytest.mark.parametrize("K,N,M,d", [(1024, 520, 300, 0.01), (4096, 256, 513, 0.003), (2048, 384, 1500, 0.02),
+                                     (1184, 210, 300, 0.02), (96, 130, 257, 0.05)])
 def test_sparse_term_folded_into_the_weights_and_as_gathers(oracle_mod, K, N, M, d):
     """With a plan whose rows are in column order the tensor-core kernel adds the sparse entries to its weight tile;
     the same forward with that switched off gathers them from the transposed activations.  Both against the oracle,
@@ -544,7 +545,8 @@ def test_rows_that_cannot_be_folded_keep_the_gather_path(oracle_mod):
     assert_close(y2.float().cpu().numpy(), ref, "plan with unordered rows")
 
 
-@pytest.mark.parametrize("M,K,N,d", [(32, 1024, 520, 0.01), (100, 4096, 300, 0.003), (128, 2048, 1100, 0.02), (48, 8192, 2048, 0.003)])
+@pytest.mark.parametrize("M,K,N,d", [(32, 1024, 520, 0.01), (100, 4096, 300, 0.003), (128, 2048, 1100, 0.02), (48, 8192, 2048, 0.003),
+                                     (100, 1184, 210, 0.02), (17, 96, 130, 0.05)])
 def test_tokens_as_m_kernel_folds_the_sparse_term(oracle_mod, M, K, N, d):
     """17..128 tokens with a plan and a workspace: the tokens-as-M kernel adds the sparse entries to its weight tile
     (one launch, shares that start inside a row), gathers the rows whose scale is zero or tiny in its epilogue, and
@@ -552,7 +554,7 @@ def test_tokens_as_m_kernel_folds_the_sparse_term(oracle_mod, M, K, N, d):
     layer = wl.make_layer(K, N, d, seed=900 + M)
     scales = layer.base_scales.clone()
     counts = layer.row_ptr[1:] - layer.row_ptr[:-1]
-    special = [r for r in (3, 255, 256, N - 1) if int(counts[r]) > 0]
+    special = [r for r in (3, 255, 256, N - 1) if r < N and int(counts[r]) > 0]
     assert special
     for i, r in enumerate(special):
         scales[r] = 0.0 if i % 2 == 0 else 1e-6
